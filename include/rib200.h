@@ -1,0 +1,257 @@
+/* rib200 - B200 (sm_100a) attention and gated-delta kernels behind RAFTInfer's kernel-launcher API.
+ *
+ * C ABI of librib200.so.  Plain pointers and sizes only.  Every entry point returns a status
+ * {code, message}; `message` points into a thread-local buffer that stays valid until the next
+ * call on the same thread.  Enum values are RAFTInfer's own
+ * (cpp/include/raftinfer/tensor.h:10-15, cpp/include/raftinfer/status.h:7-20,
+ * cpp/execution/qwen35_execution_policy.hpp:7-27) so the reference's structs convert field by field.
+ *
+ * Ownership and threading follow the reference launchers (cpp/kernels/qwen35_delta.cuh:76-86):
+ * the caller owns every buffer (inputs, outputs, KV cache, gated-delta states, workspace); a call
+ * only enqueues work on `stream`, never allocates, never creates a stream and never synchronises.
+ * `stream` must be a real stream handle (NULL is rejected, as in cpp/kernels/qwen35_attention.cu:430).
+ * Calls are re-entrant across different streams and buffers.
+ *
+ * There is no CPU fallback and no second backend: a signature these kernels do not cover returns
+ * RIB200_STATUS_UNSUPPORTED.
+ */
+#ifndef RIB200_H
+#define RIB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* cpp/include/raftinfer/status.h:7-20 */
+enum {
+  RIB200_STATUS_OK = 0,
+  RIB200_STATUS_INVALID_ARGUMENT = 1,
+  RIB200_STATUS_UNAVAILABLE = 2,
+  RIB200_STATUS_CUDA_ERROR = 3,
+  RIB200_STATUS_INTERNAL = 4,
+  RIB200_STATUS_UNSUPPORTED = 5,
+  RIB200_STATUS_RESOURCE_EXHAUSTED = 6
+};
+
+typedef struct Rib200Status {
+  int32_t code;
+  const char *message; /* "" when code == RIB200_STATUS_OK */
+} Rib200Status;
+
+/* cpp/include/raftinfer/tensor.h:10-15 */
+enum { RIB200_DTYPE_F32 = 1, RIB200_DTYPE_F16 = 2, RIB200_DTYPE_BF16 = 3 };
+/* cpp/execution/qwen35_execution_policy.hpp:7-27 */
+enum { RIB200_ATTENTION_MATERIALIZED_REFERENCE = 0, RIB200_ATTENTION_ONLINE_TILED = 1 };
+enum { RIB200_DECODE_AUTO_SELECT = 0, RIB200_DECODE_SINGLE_BLOCK = 1, RIB200_DECODE_SPLIT_K_256 = 2,
+       RIB200_DECODE_SPLIT_K_512 = 3 };
+enum { RIB200_KV_CACHE_F32 = 0, RIB200_KV_CACHE_BF16 = 1 };
+enum { RIB200_KV_LAYOUT_TOKEN_MAJOR = 0, RIB200_KV_LAYOUT_HEAD_MAJOR = 1 };
+/* cpp/kernels/qwen35_delta.cuh:31-35 */
+enum { RIB200_DELTA_SCHEDULE_CURRENT = 0, RIB200_DELTA_SCHEDULE_PREFILL_SM120 = 1,
+       RIB200_DELTA_SCHEDULE_DECODE_SM120 = 2 };
+
+/* Bits of the device status word (rib200_device_status).  They replace the device-side trap of
+ * cpp/kernels/qwen35_online_attention.cu:714-717: the kernel records the condition and returns. */
+enum {
+  RIB200_DEVICE_DECODE_CAPACITY_EXCEEDED = 1u << 0, /* live context needs more partitions than the plan holds */
+  RIB200_DEVICE_POSITION_OUT_OF_RANGE = 1u << 1,    /* *device_position >= max_context_tokens */
+  RIB200_DEVICE_WAIT_TIMED_OUT = 1u << 2            /* a bounded on-device wait gave up */
+};
+
+/* cpp/kernels/qwen35_attention.cuh:14-21 */
+typedef struct Rib200AttentionShape {
+  size_t tokens;
+  size_t query_heads;
+  size_t kv_heads;
+  size_t head_dim;
+  size_t max_context_tokens;
+  size_t past_tokens;
+} Rib200AttentionShape;
+
+/* cpp/kernels/qwen35_attention.cuh:23-27 */
+typedef struct Rib200AttentionLaunchPolicy {
+  uint8_t implementation;
+  uint8_t kv_cache_dtype;
+  uint8_t kv_cache_layout;
+} Rib200AttentionLaunchPolicy;
+
+/* cpp/kernels/qwen35_online_attention.cuh:12-21 */
+typedef struct Rib200OnlineDecodePlan {
+  uint8_t resolved_mode;
+  size_t partition_tokens;
+  size_t split_k_threshold_tokens;
+  size_t context_bucket_tokens;
+  size_t active_partition_capacity;
+} Rib200OnlineDecodePlan;
+
+/* cpp/kernels/qwen35_online_attention.cuh:23-31 */
+typedef struct Rib200OnlineDecodeWorkspaceLayout {
+  size_t partial_count;
+  size_t max_offset_bytes;
+  size_t sum_offset_bytes;
+  size_t value_offset_bytes;
+  size_t bytes;
+} Rib200OnlineDecodeWorkspaceLayout;
+
+/* cpp/kernels/qwen35_delta.cuh:20-29 */
+typedef struct Rib200GatedDeltaShape {
+  size_t tokens;
+  size_t hidden_size;
+  size_t key_heads;
+  size_t value_heads;
+  size_t key_dim;
+  size_t value_dim;
+  size_t conv_width;
+  float epsilon;
+} Rib200GatedDeltaShape;
+
+/* cpp/kernels/qwen35_delta.cuh:37-41 */
+typedef struct Rib200GatedDeltaLaunchPolicy {
+  uint8_t schedule;
+  uint32_t warps_per_block;
+  uint8_t transposed_boundary_state;
+} Rib200GatedDeltaLaunchPolicy;
+
+/* cpp/kernels/qwen35_delta.cuh:43-60 (rejection_reason as a fixed buffer) */
+typedef struct Rib200GatedDeltaScheduleDiagnostic {
+  size_t bucket_tokens;
+  size_t key_dim;
+  size_t value_dim;
+  uint8_t candidate_schedule;
+  uint8_t schedule;
+  uint32_t warps_per_block;
+  uint8_t transposed_boundary_state;
+  uint8_t candidate_accepted;
+  uint8_t correctness_passed;
+  float current_median_ms;
+  float candidate_median_ms;
+  char rejection_reason[32];
+} Rib200GatedDeltaScheduleDiagnostic;
+
+/* ---- sizes and plans (host only; no CUDA call) ------------------------------------------- */
+
+/* qwen35_attention_workspace_floats, cpp/kernels/qwen35_attention.cuh:29 (cpp/kernels/qwen35_attention.cu).
+ * Size of the logits buffer of the reference's materialized path: tokens * query_heads * context floats. */
+Rib200Status rib200_attention_workspace_floats(const Rib200AttentionShape *shape, size_t *floats);
+/* qwen35_attention_cache_bytes, cpp/kernels/qwen35_attention.cuh:31-32 (cpp/kernels/qwen35_attention.cu:417-428). */
+Rib200Status rib200_attention_cache_bytes(const Rib200AttentionShape *shape, Rib200AttentionLaunchPolicy policy,
+                                          size_t *bytes);
+/* qwen35_attention_workspace_bytes (policy overload), cpp/kernels/qwen35_attention.cuh:33-35
+ * (cpp/kernels/qwen35_attention.cu:430-443). */
+Rib200Status rib200_attention_workspace_bytes(const Rib200AttentionShape *shape, Rib200AttentionLaunchPolicy policy,
+                                              size_t *bytes);
+/* qwen35_online_decode_plan, cpp/kernels/qwen35_online_attention.cuh:33-35
+ * (cpp/kernels/qwen35_online_attention.cu:1071-1109). */
+Rib200Status rib200_online_decode_plan(const Rib200AttentionShape *shape, uint8_t requested_mode,
+                                       size_t context_tokens, Rib200OnlineDecodePlan *plan);
+/* qwen35_online_decode_workspace_layout, cpp/kernels/qwen35_online_attention.cuh:37-38
+ * (cpp/kernels/qwen35_online_attention.cu:1111-1143). */
+Rib200Status rib200_online_decode_workspace_layout(const Rib200AttentionShape *shape, uint8_t resolved_mode,
+                                                   Rib200OnlineDecodeWorkspaceLayout *layout);
+/* qwen35_online_attention_prefill_supported, cpp/kernels/qwen35_online_attention.cuh:40-42.
+ * Writes 1 when rib200_online_attention_prefill accepts the signature, else 0; never fails. */
+Rib200Status rib200_online_attention_prefill_supported(const Rib200AttentionShape *shape, int32_t activation_dtype,
+                                                       Rib200AttentionLaunchPolicy policy, int32_t *supported);
+/* qwen35_online_attention_workspace_bytes, cpp/kernels/qwen35_online_attention.cuh:44-45 (always 0). */
+Rib200Status rib200_online_attention_workspace_bytes(const Rib200AttentionShape *shape, size_t *bytes);
+/* qwen35_gated_delta_workspace_bytes, cpp/kernels/qwen35_delta.cuh:65 (cpp/kernels/qwen35_delta.cu:755-757). */
+Rib200Status rib200_gated_delta_workspace_bytes(const Rib200GatedDeltaShape *shape, size_t *bytes);
+/* qwen35_gated_delta_select_policy, cpp/kernels/qwen35_delta.cuh:70-72. */
+Rib200Status rib200_gated_delta_select_policy(const Rib200GatedDeltaShape *shape, size_t bucket_tokens,
+                                              Rib200GatedDeltaLaunchPolicy *policy);
+/* qwen35_gated_delta_schedule_diagnostic, cpp/kernels/qwen35_delta.cuh:74-76. */
+Rib200Status rib200_gated_delta_schedule_diagnostic(const Rib200GatedDeltaShape *shape, size_t bucket_tokens,
+                                                    Rib200GatedDeltaScheduleDiagnostic *diagnostic);
+
+/* ---- launchers ---------------------------------------------------------------------------- */
+
+/* qwen35_causal_attention (policy overload), cpp/kernels/qwen35_attention.cuh:37-44
+ * (cpp/kernels/qwen35_attention.cu:565-613).  tokens == 1 runs single-block decode, tokens > 1 the
+ * online prefill; a workspace is forbidden on the online path. */
+Rib200Status rib200_causal_attention(const void *query, const void *key, const void *value, const void *gate,
+                                     void *output, void *kv_cache, size_t kv_cache_bytes, void *workspace,
+                                     size_t workspace_bytes, const Rib200AttentionShape *shape,
+                                     int32_t activation_dtype, Rib200AttentionLaunchPolicy policy, void *stream);
+
+/* qwen35_online_attention_prefill, cpp/kernels/qwen35_online_attention.cuh:47-53
+ * (cpp/kernels/qwen35_online_attention.cu:1161-1218).  Appends this chunk's K,V to the cache at
+ * past_tokens.. and writes out[t][h] = softmax_{j <= past+t}(q.k_j / sqrt(D)) . v * sigmoid(gate).
+ * query, gate, output are [tokens][query_heads][head_dim]; key, value [tokens][kv_heads][head_dim]. */
+Rib200Status rib200_online_attention_prefill(const void *query, const void *key, const void *value,
+                                             const void *gate, void *output, void *kv_cache, size_t kv_cache_bytes,
+                                             const Rib200AttentionShape *shape, int32_t activation_dtype,
+                                             uint8_t cache_dtype, uint8_t cache_layout, void *stream);
+
+/* qwen35_online_attention_decode (plan overload), cpp/kernels/qwen35_online_attention.cuh:55-63
+ * (cpp/kernels/qwen35_online_attention.cu:1220-1314).  One token: append K,V at the position
+ * (*device_position when non-NULL, else shape->past_tokens), then attend over 0..position.
+ * With a split-k plan the partials (max, sum, acc) land in `workspace` in the layout of
+ * rib200_online_decode_workspace_layout.  Safe to capture in a CUDA graph: the position is read
+ * on the device and the grid is sized by plan->active_partition_capacity. */
+Rib200Status rib200_online_attention_decode(const void *query, const void *key, const void *value,
+                                            const void *gate, void *output, void *kv_cache, size_t kv_cache_bytes,
+                                            void *workspace, size_t workspace_bytes,
+                                            const Rib200AttentionShape *shape, int32_t activation_dtype,
+                                            uint8_t cache_dtype, uint8_t cache_layout,
+                                            const Rib200OnlineDecodePlan *plan, const uint32_t *device_position,
+                                            void *stream);
+
+/* qwen35_gated_delta (policy overload), cpp/kernels/qwen35_delta.cuh:95-102
+ * (cpp/kernels/qwen35_delta.cu:811-897).  Packed input per token [q | k | v | b | a | z]. */
+Rib200Status rib200_gated_delta(const void *input, const void *conv_weight, const void *recurrent_a,
+                                const void *dt_bias, const void *output_norm_weight, void *output,
+                                float *convolution_state, float *recurrent_state, void *workspace,
+                                size_t workspace_bytes, const Rib200GatedDeltaShape *shape,
+                                Rib200GatedDeltaLaunchPolicy policy, int32_t dtype, int32_t weight_dtype,
+                                void *stream);
+
+/* ---- additive entry points (no counterpart in the reference) ------------------------------ */
+
+/* Gated delta-rule recurrence alone (the loop body of cpp/kernels/qwen35_delta.cu:482-576 /
+ * cpp/reference/qwen35.cpp:459-518) on operands that are already convolved and normalised:
+ * q, k [tokens][key_heads][key_dim] (q carries 1/sqrt(key_dim)), v [tokens][value_heads][value_dim], all of
+ * qkv_dtype (RIB200_DTYPE_BF16 or RIB200_DTYPE_F32); beta and log_decay FP32 [tokens][value_heads]
+ * (beta in (0,1), decay = exp(log_decay)); state FP32 [value_heads][key_dim][value_dim] updated in place;
+ * out FP32 [tokens][value_heads][value_dim] (the vector before the output norm).  The key head of value
+ * head h is h % key_heads.  tokens < 64 run the recurrent kernel (one pass over the state per token);
+ * longer runs use the chunk-64 WY-form prefill and need rib200_gdn_core_workspace_bytes of scratch.
+ * key_dim == value_dim == 128 only. */
+Rib200Status rib200_gdn_core_workspace_bytes(size_t tokens, size_t key_heads, size_t value_heads, size_t key_dim,
+                                             size_t value_dim, size_t *bytes);
+Rib200Status rib200_gdn_core(const void *q, const void *k, const void *v, const float *beta,
+                             const float *log_decay, float *state, float *out, void *workspace,
+                             size_t workspace_bytes, size_t tokens, size_t key_heads, size_t value_heads,
+                             size_t key_dim, size_t value_dim, int32_t qkv_dtype, void *stream);
+
+/* One decode step for a batch of independent sequences (ragged contexts), one launch per stage.
+ * Per sequence i: kv_caches[i] is its BF16 head-major cache of max_context_tokens[i] rows, positions[i]
+ * the row the new token is appended at; query/gate/output are [batch][16][256], key/value [batch][4][256]
+ * (BF16).  Arrays of pointers and sizes live in device memory.  workspace holds the split-k partials of
+ * every sequence back to back; rib200_batched_decode_workspace_bytes sizes it for the largest context. */
+Rib200Status rib200_batched_decode_workspace_bytes(size_t batch, size_t max_context_tokens, size_t *bytes);
+Rib200Status rib200_batched_decode_attention(const void *query, const void *key, const void *value,
+                                             const void *gate, void *output, void *const *kv_caches,
+                                             const uint32_t *max_context_tokens, const uint32_t *positions,
+                                             size_t batch, size_t largest_max_context_tokens, void *workspace,
+                                             size_t workspace_bytes, void *stream);
+/* Recurrent gated-delta decode step for a batch of sequences: states[i] FP32 [value_heads][128][128]
+ * (array of device pointers, itself in device memory); q,k BF16 [batch][key_heads][128], v BF16
+ * [batch][value_heads][128], beta/log_decay FP32 [batch][value_heads], out FP32 [batch][value_heads][128]. */
+Rib200Status rib200_batched_gdn_decode(const void *q, const void *k, const void *v, const float *beta,
+                                       const float *log_decay, float *const *states, float *out, size_t batch,
+                                       size_t key_heads, size_t value_heads, void *stream);
+
+/* Reads and clears the status word the kernels of this library set on the current device.  It
+ * synchronises `stream` first, so it is not for use inside a graph capture. */
+Rib200Status rib200_device_status(void *stream, uint32_t *bits);
+
+/* "rib200 <version> sm_100a" */
+const char *rib200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RIB200_H */

@@ -1,0 +1,181 @@
+"""Timings of the other kernels of the path, reported next to the headline decode number (bench.py "extra").
+
+Each entry is the median of `reps` CUDA-event timings after warm-up, inputs resident in HBM, with the
+algorithmic bytes or flops the figure is computed from.  Buffers are rotated or larger than L2 where the
+working set would otherwise be served from L2.
+"""
+from __future__ import annotations
+
+import statistics
+
+import torch
+
+from . import kernels as K
+
+HQ, HKV, D = 16, 4, 256
+HK, HV, DK = 16, 32, 128
+
+
+def _median_ms(fn, stream, warmup=5, reps=20):
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    times = []
+    for i in range(reps):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        fn(i)
+        b.record(stream)
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    return statistics.median(times), (statistics.pstdev(times) / statistics.mean(times) if len(times) > 1 else 0.0)
+
+
+def _bf16(gen, dev, *shape):
+    return torch.randn(*shape, device=dev, generator=gen, dtype=torch.float32).to(torch.bfloat16)
+
+
+def decode_contexts(dev, stream, hbm_peak, contexts=(4096, 131072)):
+    out = {}
+    gen = torch.Generator(device=dev).manual_seed(11)
+    for ctx in contexts:
+        rotation = max(2, min(16, -(-600_000_000 // (4096 * ctx))))
+        shape = K.Qwen35AttentionShape(1, HQ, HKV, D, ctx, ctx - 1)
+        plan = K.qwen35_online_decode_plan(shape, K.SPLIT_K_256, ctx)
+        layout = K.qwen35_online_decode_workspace_layout(shape, plan.resolved_mode)
+        caches = [_bf16(gen, dev, 2, HKV, ctx, D) for _ in range(rotation)]
+        q, gate, k, v = _bf16(gen, dev, HQ, D), _bf16(gen, dev, HQ, D), _bf16(gen, dev, HKV, D), _bf16(gen, dev, HKV, D)
+        o = torch.zeros(HQ, D, device=dev, dtype=torch.bfloat16)
+        ws = torch.zeros(layout.bytes // 4, device=dev)
+
+        def fn(i):
+            K.qwen35_online_attention_decode(q, k, v, gate, o, caches[i % rotation], caches[0].numel() * 2, ws,
+                                             layout.bytes, shape, K.DTYPE_BF16, K.KV_BF16, K.HEAD_MAJOR, plan, None,
+                                             stream)
+
+        ms, cv = _median_ms(fn, stream)
+        nbytes = 4096 * ctx + 24576
+        out[f"decode_ctx{ctx}"] = {"ms": ms, "cv": cv, "bytes": nbytes, "GB/s": nbytes / ms / 1e6,
+                                   "frac_of_measured_hbm": nbytes / ms / 1e6 / hbm_peak, "caches_rotated": rotation}
+        del caches
+    return out
+
+
+def batched_serving_decode(dev, stream, hbm_peak, batch=64, lo=1024, hi=32768, seed=0xB2000004):
+    """64 ragged sequences: one attention decode step + one gated-delta decode step per sequence."""
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    cpu_gen = torch.Generator().manual_seed(seed)
+    lengths = torch.randint(lo, hi + 1, (batch,), generator=cpu_gen).tolist()
+    caps = [-(-n // 256) * 256 for n in lengths]
+    largest = max(caps)
+    caches = [_bf16(gen, dev, 2, HKV, c, D) for c in caps]
+    ptrs = torch.tensor([c.data_ptr() for c in caches], device=dev, dtype=torch.int64)
+    dcaps = torch.tensor(caps, device=dev, dtype=torch.int32)
+    dpos = torch.tensor([n - 1 for n in lengths], device=dev, dtype=torch.int32)
+    q, gate = _bf16(gen, dev, batch, HQ, D), _bf16(gen, dev, batch, HQ, D)
+    k, v = _bf16(gen, dev, batch, HKV, D), _bf16(gen, dev, batch, HKV, D)
+    o = torch.zeros(batch, HQ, D, device=dev, dtype=torch.bfloat16)
+    ws_bytes = K.batched_decode_workspace_bytes(batch, largest)
+    ws = torch.zeros(ws_bytes // 4, device=dev)
+    states = [torch.zeros(HV, DK, DK, device=dev) for _ in range(batch)]
+    sptrs = torch.tensor([s.data_ptr() for s in states], device=dev, dtype=torch.int64)
+    gq = torch.nn.functional.normalize(torch.randn(batch, HK, DK, device=dev, generator=gen), dim=-1)
+    gk = torch.nn.functional.normalize(torch.randn(batch, HK, DK, device=dev, generator=gen), dim=-1)
+    gq, gk = (gq / DK ** 0.5).to(torch.bfloat16), gk.to(torch.bfloat16)
+    gv = _bf16(gen, dev, batch, HV, DK)
+    beta = torch.sigmoid(torch.randn(batch, HV, device=dev, generator=gen))
+    logd = -torch.nn.functional.softplus(torch.randn(batch, HV, device=dev, generator=gen))
+    go = torch.zeros(batch, HV, DK, device=dev)
+
+    def attn(i):
+        K.batched_decode_attention(q, k, v, gate, o, ptrs, dcaps, dpos, batch, largest, ws, ws_bytes, stream)
+
+    def gdn(i):
+        K.batched_gdn_decode(gq, gk, gv, beta, logd, sptrs, go, batch, HK, HV, stream)
+
+    def both(i):
+        attn(i)
+        gdn(i)
+
+    attn_bytes = sum(4096 * n + 24576 for n in lengths)
+    gdn_bytes = batch * 2 * HV * DK * DK * 4
+    res = {"sequences": batch, "total_context_tokens": sum(lengths)}
+    for name, fn, nbytes in (("attention", attn, attn_bytes), ("gdn_decode", gdn, gdn_bytes),
+                             ("attention+gdn_decode", both, attn_bytes + gdn_bytes)):
+        ms, cv = _median_ms(fn, stream, warmup=3, reps=10)
+        res[name] = {"ms": ms, "cv": cv, "bytes": nbytes, "GB/s": nbytes / ms / 1e6,
+                     "frac_of_measured_hbm": nbytes / ms / 1e6 / hbm_peak}
+    return res
+
+
+def gdn_layer(dev, stream, hbm_peak, tensor_peak, tokens=4096, decode_steps=128):
+    """configs[3]: chunked prefill over `tokens`, then `decode_steps` recurrent steps on the same state."""
+    gen = torch.Generator(device=dev).manual_seed(13)
+    total = tokens + decode_steps
+    q = torch.nn.functional.normalize(torch.randn(total, HK, DK, device=dev, generator=gen), dim=-1)
+    k = torch.nn.functional.normalize(torch.randn(total, HK, DK, device=dev, generator=gen), dim=-1)
+    q, k = (q / DK ** 0.5).to(torch.bfloat16), k.to(torch.bfloat16)
+    v = _bf16(gen, dev, total, HV, DK)
+    beta = torch.sigmoid(torch.randn(total, HV, device=dev, generator=gen))
+    logd = -torch.nn.functional.softplus(torch.randn(total, HV, device=dev, generator=gen))
+    state = torch.zeros(HV, DK, DK, device=dev)
+    out = torch.zeros(total, HV, DK, device=dev)
+    ws_bytes = K.gdn_core_workspace_bytes(tokens, HK, HV, DK, DK)
+    ws = torch.zeros(max(ws_bytes // 4, 4), device=dev)
+
+    def prefill(i):
+        state.zero_()
+        K.gdn_core(q, k, v, beta, logd, state, out, ws, ws_bytes, tokens, HK, HV, DK, DK, K.DTYPE_BF16, stream)
+
+    def decode(i):
+        t = tokens + (i % decode_steps)
+        K.gdn_core(q[t], k[t], v[t], beta[t], logd[t], state, out[t], None, 0, 1, HK, HV, DK, DK, K.DTYPE_BF16, stream)
+
+    chunk = 64
+    flops = (tokens // chunk) * HV * (2 * chunk * chunk * (3 * DK + 2 * DK) + 6 * chunk * DK * DK)
+    ms, cv = _median_ms(prefill, stream, warmup=3, reps=10)
+    res = {"prefill": {"tokens": tokens, "ms": ms, "cv": cv, "flops": flops, "TFLOP/s": flops / ms / 1e9,
+                       "frac_of_measured_bf16_peak": flops / ms / 1e9 / tensor_peak,
+                       "note": "time includes a 2 MiB state memset"}}
+    ms, cv = _median_ms(decode, stream, warmup=5, reps=decode_steps)
+    nbytes = 2 * HV * DK * DK * 4
+    res["decode_step"] = {"ms": ms, "cv": cv, "bytes": nbytes, "effective GB/s": nbytes / ms / 1e6,
+                          "note": "single sequence: the 2 MiB state is L2-resident, this is latency not HBM bandwidth"}
+    return res
+
+
+def prefill_attention(dev, stream, tensor_peak, token_counts=(128, 512, 4096)):
+    gen = torch.Generator(device=dev).manual_seed(17)
+    res = {}
+    cases = [(t, 0) for t in token_counts] + [(512, 3584)]
+    for tokens, past in cases:
+        max_ctx = past + tokens
+        shape = K.Qwen35AttentionShape(tokens, HQ, HKV, D, max_ctx, past)
+        q, gate = _bf16(gen, dev, tokens, HQ, D), _bf16(gen, dev, tokens, HQ, D)
+        k, v = _bf16(gen, dev, tokens, HKV, D), _bf16(gen, dev, tokens, HKV, D)
+        o = torch.zeros(tokens, HQ, D, device=dev, dtype=torch.bfloat16)
+        cache = _bf16(gen, dev, 2, HKV, max_ctx, D)
+
+        def fn(i):
+            K.qwen35_online_attention_prefill(q, k, v, gate, o, cache, cache.numel() * 2, shape, K.DTYPE_BF16, K.KV_BF16,
+                                              K.HEAD_MAJOR, stream)
+
+        ms, cv = _median_ms(fn, stream, warmup=3, reps=10)
+        flops = 4 * HQ * D * (tokens * past + tokens * (tokens + 1) // 2)
+        res[f"T{tokens}_past{past}"] = {"ms": ms, "cv": cv, "flops": flops, "TFLOP/s": flops / ms / 1e9,
+                                        "frac_of_measured_bf16_peak": flops / ms / 1e9 / tensor_peak}
+    return res
+
+
+def run(dev, stream, hbm_peak, tensor_peak):
+    extra = {}
+    for name, fn in (("decode_attention", lambda: decode_contexts(dev, stream, hbm_peak)),
+                     ("batched_serving_decode", lambda: batched_serving_decode(dev, stream, hbm_peak)),
+                     ("gated_delta", lambda: gdn_layer(dev, stream, hbm_peak, tensor_peak)),
+                     ("prefill_attention", lambda: prefill_attention(dev, stream, tensor_peak))):
+        try:
+            extra[name] = fn()
+        except (K.Qwen35PrimitiveError, K.Qwen35DeltaError) as err:
+            extra[name] = {"unavailable": str(err)}
+        torch.cuda.empty_cache()
+    return extra

@@ -1,0 +1,634 @@
+// Split-k GQA decode attention over the BF16 head-major KV cache, for 16 query heads / 4 KV heads /
+// head_dim 256 (the only decode signature RAFTInfer accepts,
+// cpp/kernels/qwen35_online_attention.cu:96-104).
+//
+// It replaces the four launches of cpp/kernels/qwen35_online_attention.cu:925-1015 (append, single
+// block, partition, merge) by two: a partition kernel that also appends the new token, and a combine
+// kernel.  The partial (max, sum, acc) contract and the workspace layout of
+// cpp/kernels/qwen35_online_attention.cu:603-691,1111-1143 are kept.
+//
+// Bandwidth plan.  One CTA serves one (partition, KV head) and all four query heads of the group, so
+// every K and V byte is read from HBM once (the reference streams each KV head four times).  Each warp
+// owns 16-token steps of the partition and keeps three of them (16 KiB each) in flight through a private
+// cp.async ring in shared memory: a lane copies exactly the 16-byte pieces it will later consume as
+// tensor-core fragments, so the ring needs no barrier and no swizzle and reads back conflict-free.
+// 4 warps x 3 stages x 16 KiB = 192 KiB in flight per SM.
+//
+// Arithmetic plan.  Tokens are the M dimension of mma.sync.m16n8k16 (BF16 in, FP32 accumulate) and the
+// eight N columns carry the four query heads twice: column 2h holds the BF16 high part and column 2h+1
+// the BF16 residual of head h, for q in the score product and for the probabilities in the value
+// product.  Both products therefore see ~16 mantissa bits although the tensor cores run in BF16, at no
+// extra cost (N = 8 is the minimum tile).  Softmax runs in FP32 with exp2f.
+
+#include "common.hpp"
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <mutex>
+
+namespace rib200 {
+namespace {
+
+constexpr int kHeadDim = 256;
+constexpr int kQueryHeads = 16;
+constexpr int kKvHeads = 4;
+constexpr int kGroup = kQueryHeads / kKvHeads;
+constexpr int kWarps = 4;
+constexpr int kStages = 3;
+constexpr int kStepTokens = 16;
+constexpr int kStageBytes = 2 * kStepTokens * kHeadDim * 2; // K + V of one step: 16 KiB
+constexpr int kRingBytes = kWarps * kStages * kStageBytes;  // 192 KiB
+constexpr int kMergeFloats = kWarps * (kGroup * kHeadDim + 2 * kGroup);
+constexpr int kSmemBytes = kRingBytes + kMergeFloats * 4;
+constexpr float kLog2e = 1.4426950408889634F;
+
+struct DecodeParams {
+  const void *query;
+  const void *key;
+  const void *value;
+  const void *gate;
+  void *output;
+  __nv_bfloat16 *cache;               // single sequence
+  void *const *caches;                // batched
+  const std::uint32_t *max_ctx_array; // batched
+  const std::uint32_t *pos_array;     // batched, or the device position of a single sequence
+  std::uint32_t max_ctx;
+  std::uint32_t host_pos;
+  std::uint32_t partition_tokens;
+  std::uint32_t threshold_tokens;
+  std::uint32_t capacity;
+  std::uint32_t max_partitions;
+  float *partial_max;
+  float *partial_sum;
+  float *partial_value;
+  std::size_t partial_stride; // floats between sequences in partial_max / partial_sum (batched)
+  unsigned int *status;
+};
+
+__device__ __forceinline__ std::uint32_t smem_address(const void *p) {
+  return static_cast<std::uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void cp_async_16(std::uint32_t dst, const void *src, bool valid) {
+  const int bytes = valid ? 16 : 0; // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ uint4 lds128(std::uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
+__device__ __forceinline__ void sts128(std::uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], std::uint32_t a0, std::uint32_t a1, std::uint32_t a2,
+                                         std::uint32_t a3, std::uint32_t b0, std::uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+               "{%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ std::uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const std::uint32_t *>(&v);
+}
+
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+// high part (part == 0) or residual (part == 1) of the two-term BF16 split of x
+__device__ __forceinline__ float split_part(float x, int part) {
+  const float hi = bf16_round(x);
+  return part == 0 ? hi : x - hi;
+}
+
+template <bool F32> __device__ __forceinline__ void load8(const void *base, std::size_t index, float (&out)[8]) {
+  if constexpr (F32) {
+    const float4 a = *reinterpret_cast<const float4 *>(static_cast<const float *>(base) + index);
+    const float4 b = *reinterpret_cast<const float4 *>(static_cast<const float *>(base) + index + 4);
+    out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w;
+    out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+  } else {
+    const uint4 raw = *reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(base) + index);
+    const std::uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      out[2 * i] = __uint_as_float(w[i] << 16);
+      out[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000U);
+    }
+  }
+}
+
+template <bool F32> __device__ __forceinline__ void store8(void *base, std::size_t index, const float (&v)[8]) {
+  if constexpr (F32) {
+    *reinterpret_cast<float4 *>(static_cast<float *>(base) + index) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4 *>(static_cast<float *>(base) + index + 4) = make_float4(v[4], v[5], v[6], v[7]);
+  } else {
+    uint4 raw;
+    raw.x = pack_bf16(v[0], v[1]);
+    raw.y = pack_bf16(v[2], v[3]);
+    raw.z = pack_bf16(v[4], v[5]);
+    raw.w = pack_bf16(v[6], v[7]);
+    *reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(base) + index) = raw;
+  }
+}
+
+template <bool F32> __device__ __forceinline__ uint4 load8_as_bf16(const void *base, std::size_t index) {
+  float v[8];
+  load8<F32>(base, index, v);
+  uint4 raw;
+  raw.x = pack_bf16(v[0], v[1]);
+  raw.y = pack_bf16(v[2], v[3]);
+  raw.z = pack_bf16(v[4], v[5]);
+  raw.w = pack_bf16(v[6], v[7]);
+  return raw;
+}
+
+// Partition kernel.  grid = (partition capacity, 4 KV heads, sequences), 128 threads.
+template <bool F32, bool Batched>
+__global__ void __launch_bounds__(kWarps * 32, 1) decode_partition_kernel(const DecodeParams p) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  // The combine kernel is launched with programmatic stream serialisation: let it become resident now;
+  // it blocks in griddepcontrol.wait until this whole grid has finished and flushed.
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+
+  const int seq = Batched ? static_cast<int>(blockIdx.z) : 0;
+  const std::uint32_t max_ctx = Batched ? p.max_ctx_array[seq] : p.max_ctx;
+  const std::uint32_t pos = p.pos_array != nullptr ? p.pos_array[seq] : p.host_pos;
+  if (pos >= max_ctx) {
+    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) {
+      atomicOr(p.status, static_cast<unsigned int>(RIB200_DEVICE_POSITION_OUT_OF_RANGE));
+    }
+    return;
+  }
+  const std::uint32_t ctx = pos + 1;
+  const bool direct = p.partition_tokens == 0 || ctx < p.threshold_tokens;
+  std::uint32_t begin = 0;
+  std::uint32_t end = ctx;
+  if (direct) {
+    if (blockIdx.x != 0) {
+      return;
+    }
+  } else {
+    begin = blockIdx.x * p.partition_tokens;
+    if (begin >= ctx) {
+      return;
+    }
+    end = min(ctx, begin + p.partition_tokens);
+  }
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int g = lane >> 2;
+  const int t = lane & 3;
+  const int kvh = blockIdx.y;
+  __nv_bfloat16 *cache = Batched ? static_cast<__nv_bfloat16 *>(p.caches[seq]) : p.cache;
+  __nv_bfloat16 *k_plane = cache + static_cast<std::size_t>(kvh) * max_ctx * kHeadDim;
+  __nv_bfloat16 *v_plane = k_plane + static_cast<std::size_t>(kKvHeads) * max_ctx * kHeadDim;
+  const std::size_t act_seq = static_cast<std::size_t>(seq);
+  const std::size_t kv_in_base = (act_seq * kKvHeads + kvh) * kHeadDim;
+
+  // Query fragments (the B operand of the score product): lane (g, t) holds, for every 32-dim block j,
+  // dims 32j + 8t .. +8 of N column g = (head g>>1, split part g&1), pre-scaled by 1/sqrt(256).
+  std::uint32_t qf[32];
+  {
+    const int head = kvh * kGroup + (g >> 1);
+    const int part = g & 1;
+    const std::size_t q_base = (act_seq * kQueryHeads + head) * kHeadDim;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float v[8];
+      load8<F32>(p.query, q_base + 32 * j + 8 * t, v);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        qf[4 * j + e] = pack_bf16(split_part(v[2 * e] * 0.0625F, part), split_part(v[2 * e + 1] * 0.0625F, part));
+      }
+    }
+  }
+
+  const std::uint32_t total_steps = (end - begin + kStepTokens - 1) / kStepTokens;
+  const std::uint32_t my_steps =
+      total_steps > static_cast<std::uint32_t>(warp) ? (total_steps - warp + kWarps - 1) / kWarps : 0;
+  const std::uint32_t ring = smem_address(smem) + warp * kStages * kStageBytes + lane * 16;
+
+  // Copies step `i` of this warp into ring stage i % kStages.  The row of the token being appended is
+  // not in the cache yet: its owner lane converts it from the key/value inputs, feeds the ring and
+  // writes the cache row.
+  auto issue = [&](std::uint32_t i) {
+    const std::uint32_t tok0 = begin + (warp + i * kWarps) * kStepTokens;
+    const std::uint32_t stage = ring + (i % kStages) * kStageBytes;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const std::uint32_t tok = tok0 + g + 8 * r;
+      const bool valid = tok < end;
+      const std::size_t row = static_cast<std::size_t>(valid ? tok : end - 1) * kHeadDim;
+      if (tok == pos) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint4 raw = load8_as_bf16<F32>(p.key, kv_in_base + 32 * j + 8 * t);
+          sts128(stage + (2 * j + r) * 512, raw);
+          *reinterpret_cast<uint4 *>(k_plane + row + 32 * j + 8 * t) = raw;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          cp_async_16(stage + (2 * j + r) * 512, k_plane + row + 32 * j + 8 * t, valid);
+        }
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const std::uint32_t tok = tok0 + 2 * t + (q & 1) + 8 * (q >> 1);
+      const bool valid = tok < end;
+      const std::size_t row = static_cast<std::size_t>(valid ? tok : end - 1) * kHeadDim;
+      if (tok == pos) {
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+          const uint4 raw = load8_as_bf16<F32>(p.value, kv_in_base + 8 * (8 * s + g));
+          sts128(stage + 8192 + (4 * s + q) * 512, raw);
+          *reinterpret_cast<uint4 *>(v_plane + row + 8 * (8 * s + g)) = raw;
+        }
+      } else {
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+          cp_async_16(stage + 8192 + (4 * s + q) * 512, v_plane + row + 8 * (8 * s + g), valid);
+        }
+      }
+    }
+  };
+
+  float oacc[16][4];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.0F;
+  }
+  float run_max = -INFINITY; // head t, identical in the eight lanes that share t
+  float run_sum = 0.0F;      // this lane's share of the row sum of head t
+
+#pragma unroll
+  for (int s = 0; s < kStages - 1; ++s) {
+    if (static_cast<std::uint32_t>(s) < my_steps) {
+      issue(s);
+    }
+    cp_async_commit();
+  }
+
+  for (std::uint32_t i = 0; i < my_steps; ++i) {
+    if (i + kStages - 1 < my_steps) {
+      issue(i + kStages - 1);
+    }
+    cp_async_commit();
+    cp_async_wait<kStages - 1>();
+
+    const std::uint32_t tok0 = begin + (warp + i * kWarps) * kStepTokens;
+    const std::uint32_t stage = ring + (i % kStages) * kStageBytes;
+
+    // scores: S[token][column] = K[token][:] . Q[column][:]
+    float s0[4] = {0.0F, 0.0F, 0.0F, 0.0F};
+    float s1[4] = {0.0F, 0.0F, 0.0F, 0.0F};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint4 ka = lds128(stage + (2 * j) * 512);
+      const uint4 kb = lds128(stage + (2 * j + 1) * 512);
+      mma_bf16(s0, ka.x, kb.x, ka.y, kb.y, qf[4 * j + 0], qf[4 * j + 1]);
+      mma_bf16(s1, ka.z, kb.z, ka.w, kb.w, qf[4 * j + 2], qf[4 * j + 3]);
+    }
+    // lane (g, t): head t, tokens tok0 + g and tok0 + g + 8 (high part + residual columns)
+    float score_a = (s0[0] + s1[0]) + (s0[1] + s1[1]);
+    float score_b = (s0[2] + s1[2]) + (s0[3] + s1[3]);
+    if (tok0 + g >= end) {
+      score_a = -INFINITY;
+    }
+    if (tok0 + g + 8 >= end) {
+      score_b = -INFINITY;
+    }
+    float step_max = fmaxf(score_a, score_b);
+    step_max = fmaxf(step_max, __shfl_xor_sync(0xFFFFFFFFU, step_max, 4));
+    step_max = fmaxf(step_max, __shfl_xor_sync(0xFFFFFFFFU, step_max, 8));
+    step_max = fmaxf(step_max, __shfl_xor_sync(0xFFFFFFFFU, step_max, 16));
+    const float new_max = fmaxf(run_max, step_max); // finite: the step holds at least one live token
+    const float rescale = exp2f((run_max - new_max) * kLog2e);
+    const float prob_a = exp2f((score_a - new_max) * kLog2e);
+    const float prob_b = exp2f((score_b - new_max) * kLog2e);
+    run_sum = run_sum * rescale + (prob_a + prob_b);
+    run_max = new_max;
+#pragma unroll
+    for (int m = 0; m < 16; ++m) {
+      oacc[m][0] *= rescale;
+      oacc[m][1] *= rescale;
+      oacc[m][2] *= rescale;
+      oacc[m][3] *= rescale;
+    }
+
+    // probabilities as the B operand of the value product: lane (g, t) needs column g = (head g>>1,
+    // part g&1) for tokens 2t, 2t+1, 2t+8, 2t+9; lane (token, head) holds them after the softmax.
+    const int src0 = (2 * t) * 4 + (g >> 1);
+    const int src1 = (2 * t + 1) * 4 + (g >> 1);
+    const float p0 = __shfl_sync(0xFFFFFFFFU, prob_a, src0);
+    const float p1 = __shfl_sync(0xFFFFFFFFU, prob_a, src1);
+    const float p2 = __shfl_sync(0xFFFFFFFFU, prob_b, src0);
+    const float p3 = __shfl_sync(0xFFFFFFFFU, prob_b, src1);
+    const int part = g & 1;
+    const std::uint32_t pb0 = pack_bf16(split_part(p0, part), split_part(p1, part));
+    const std::uint32_t pb1 = pack_bf16(split_part(p2, part), split_part(p3, part));
+
+    // values: O[dim][column] += V[token][dim] * P[token][column]
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      const uint4 l0 = lds128(stage + 8192 + (4 * s + 0) * 512);
+      const uint4 l1 = lds128(stage + 8192 + (4 * s + 1) * 512);
+      const uint4 l2 = lds128(stage + 8192 + (4 * s + 2) * 512);
+      const uint4 l3 = lds128(stage + 8192 + (4 * s + 3) * 512);
+      const std::uint32_t w0[4] = {l0.x, l0.y, l0.z, l0.w};
+      const std::uint32_t w1[4] = {l1.x, l1.y, l1.z, l1.w};
+      const std::uint32_t w2[4] = {l2.x, l2.y, l2.z, l2.w};
+      const std::uint32_t w3[4] = {l3.x, l3.y, l3.z, l3.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const std::uint32_t a0 = __byte_perm(w0[e], w1[e], 0x5410);
+        const std::uint32_t a1 = __byte_perm(w0[e], w1[e], 0x7632);
+        const std::uint32_t a2 = __byte_perm(w2[e], w3[e], 0x5410);
+        const std::uint32_t a3 = __byte_perm(w2[e], w3[e], 0x7632);
+        mma_bf16(oacc[4 * s + e], a0, a1, a2, a3, pb0, pb1);
+      }
+    }
+  }
+  cp_async_wait<0>();
+
+  run_sum += __shfl_xor_sync(0xFFFFFFFFU, run_sum, 4);
+  run_sum += __shfl_xor_sync(0xFFFFFFFFU, run_sum, 8);
+  run_sum += __shfl_xor_sync(0xFFFFFFFFU, run_sum, 16);
+
+  // cross-warp combine through shared memory
+  float *merge = reinterpret_cast<float *>(smem + kRingBytes);
+  float *warp_max = merge;                       // [kWarps][4]
+  float *warp_sum = merge + kWarps * kGroup;     // [kWarps][4]
+  float *warp_out = merge + 2 * kWarps * kGroup; // [kWarps][4][256]
+  if (g == 0) {
+    warp_max[warp * kGroup + t] = run_max;
+    warp_sum[warp * kGroup + t] = run_sum;
+  }
+#pragma unroll
+  for (int s = 0; s < 4; ++s) {
+    float *dst = warp_out + (warp * kGroup + t) * kHeadDim + 8 * (8 * s + g);
+    float4 lo;
+    float4 hi;
+    lo.x = oacc[4 * s + 0][0] + oacc[4 * s + 0][1];
+    lo.y = oacc[4 * s + 0][2] + oacc[4 * s + 0][3];
+    lo.z = oacc[4 * s + 1][0] + oacc[4 * s + 1][1];
+    lo.w = oacc[4 * s + 1][2] + oacc[4 * s + 1][3];
+    hi.x = oacc[4 * s + 2][0] + oacc[4 * s + 2][1];
+    hi.y = oacc[4 * s + 2][2] + oacc[4 * s + 2][3];
+    hi.z = oacc[4 * s + 3][0] + oacc[4 * s + 3][1];
+    hi.w = oacc[4 * s + 3][2] + oacc[4 * s + 3][3];
+    *reinterpret_cast<float4 *>(dst) = lo;
+    *reinterpret_cast<float4 *>(dst + 4) = hi;
+  }
+  __syncthreads();
+
+  const int head_in_group = threadIdx.x >> 5;
+  const int dim0 = (threadIdx.x & 31) * 8;
+  float block_max = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w) {
+    block_max = fmaxf(block_max, warp_max[w * kGroup + head_in_group]);
+  }
+  float block_sum = 0.0F;
+  float acc[8] = {0.0F, 0.0F, 0.0F, 0.0F, 0.0F, 0.0F, 0.0F, 0.0F};
+#pragma unroll
+  for (int w = 0; w < kWarps; ++w) {
+    const float weight = exp2f((warp_max[w * kGroup + head_in_group] - block_max) * kLog2e);
+    block_sum += warp_sum[w * kGroup + head_in_group] * weight;
+    const float *src = warp_out + (w * kGroup + head_in_group) * kHeadDim + dim0;
+    const float4 a = *reinterpret_cast<const float4 *>(src);
+    const float4 b = *reinterpret_cast<const float4 *>(src + 4);
+    acc[0] += a.x * weight; acc[1] += a.y * weight; acc[2] += a.z * weight; acc[3] += a.w * weight;
+    acc[4] += b.x * weight; acc[5] += b.y * weight; acc[6] += b.z * weight; acc[7] += b.w * weight;
+  }
+
+  const int head = kvh * kGroup + head_in_group;
+  if (direct) {
+    const std::size_t out_index = (act_seq * kQueryHeads + head) * kHeadDim + dim0;
+    float gate[8];
+    load8<F32>(p.gate, out_index, gate);
+    float result[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      result[e] = (acc[e] / block_sum) / (1.0F + expf(-gate[e]));
+    }
+    store8<F32>(p.output, out_index, result);
+    return;
+  }
+  const std::size_t partial = static_cast<std::size_t>(head) * p.max_partitions + blockIdx.x;
+  float *pmax = p.partial_max + act_seq * p.partial_stride;
+  float *psum = p.partial_sum + act_seq * p.partial_stride;
+  float *pval = p.partial_value + act_seq * p.partial_stride * kHeadDim;
+  if ((threadIdx.x & 31) == 0) {
+    pmax[partial] = block_max;
+    psum[partial] = block_sum;
+  }
+  float *dst = pval + partial * kHeadDim + dim0;
+  *reinterpret_cast<float4 *>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+  *reinterpret_cast<float4 *>(dst + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+}
+
+// Combine kernel.  grid = (16 query heads, 4 dim quarters, sequences), 256 threads: sixteen partition
+// groups of sixteen lanes, a lane owning four consecutive dims of the quarter.
+template <bool F32, bool Batched>
+__global__ void __launch_bounds__(256) decode_combine_kernel(const DecodeParams p) {
+  __shared__ float red[8];
+  __shared__ float group_sum[16];
+  __shared__ float group_acc[16][64];
+
+  // wait until the partition grid has completed and its partials are visible
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
+
+  const int seq = Batched ? static_cast<int>(blockIdx.z) : 0;
+  const std::uint32_t max_ctx = Batched ? p.max_ctx_array[seq] : p.max_ctx;
+  const std::uint32_t pos = p.pos_array != nullptr ? p.pos_array[seq] : p.host_pos;
+  if (pos >= max_ctx) {
+    return;
+  }
+  const std::uint32_t ctx = pos + 1;
+  if (p.partition_tokens == 0 || ctx < p.threshold_tokens) {
+    return; // served directly by the partition kernel
+  }
+  const std::uint32_t parts = (ctx + p.partition_tokens - 1) / p.partition_tokens;
+  if (parts > p.capacity) {
+    // The captured grid cannot cover this context.  Record it and leave the output untouched.
+    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) {
+      atomicOr(p.status, static_cast<unsigned int>(RIB200_DEVICE_DECODE_CAPACITY_EXCEEDED));
+    }
+    return;
+  }
+  const std::size_t act_seq = static_cast<std::size_t>(seq);
+  const int head = blockIdx.x;
+  const int quarter = blockIdx.y;
+  const float *pmax = p.partial_max + act_seq * p.partial_stride + static_cast<std::size_t>(head) * p.max_partitions;
+  const float *psum = p.partial_sum + act_seq * p.partial_stride + static_cast<std::size_t>(head) * p.max_partitions;
+  const float *pval = p.partial_value +
+                      (act_seq * p.partial_stride + static_cast<std::size_t>(head) * p.max_partitions) * kHeadDim;
+
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  float local_max = -INFINITY;
+  for (std::uint32_t i = threadIdx.x; i < parts; i += 256) {
+    local_max = fmaxf(local_max, pmax[i]);
+  }
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) {
+    local_max = fmaxf(local_max, __shfl_xor_sync(0xFFFFFFFFU, local_max, offset));
+  }
+  if (lane == 0) {
+    red[warp] = local_max;
+  }
+  __syncthreads();
+  float total_max = red[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) {
+    total_max = fmaxf(total_max, red[w]);
+  }
+
+  const int group = threadIdx.x >> 4;
+  const int sub = threadIdx.x & 15;
+  float sum = 0.0F;
+  float4 acc = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+  for (std::uint32_t i = group; i < parts; i += 16) {
+    const float weight = exp2f((pmax[i] - total_max) * kLog2e);
+    sum += psum[i] * weight;
+    const float4 v = *reinterpret_cast<const float4 *>(pval + static_cast<std::size_t>(i) * kHeadDim + quarter * 64 + sub * 4);
+    acc.x += v.x * weight;
+    acc.y += v.y * weight;
+    acc.z += v.z * weight;
+    acc.w += v.w * weight;
+  }
+  if (sub == 0) {
+    group_sum[group] = sum;
+  }
+  *reinterpret_cast<float4 *>(&group_acc[group][sub * 4]) = acc;
+  __syncthreads();
+  if (threadIdx.x < 64) {
+    float total_sum = 0.0F;
+    float total = 0.0F;
+#pragma unroll
+    for (int gidx = 0; gidx < 16; ++gidx) {
+      total_sum += group_sum[gidx];
+      total += group_acc[gidx][threadIdx.x];
+    }
+    const std::size_t out_index = (act_seq * kQueryHeads + head) * kHeadDim + quarter * 64 + threadIdx.x;
+    if constexpr (F32) {
+      const float gate = static_cast<const float *>(p.gate)[out_index];
+      static_cast<float *>(p.output)[out_index] = (total / total_sum) / (1.0F + expf(-gate));
+    } else {
+      const float gate = __bfloat162float(static_cast<const __nv_bfloat16 *>(p.gate)[out_index]);
+      static_cast<__nv_bfloat16 *>(p.output)[out_index] =
+          __float2bfloat16_rn((total / total_sum) / (1.0F + expf(-gate)));
+    }
+  }
+}
+
+template <bool F32, bool Batched> void configure_once() {
+  static std::once_flag flags[64];
+  int device = 0;
+  cuda_ok(cudaGetDevice(&device), "cudaGetDevice");
+  require(device >= 0 && device < 64, "device ordinal out of range", RIB200_STATUS_INTERNAL);
+  std::call_once(flags[device], [] {
+    cuda_ok(cudaFuncSetAttribute(decode_partition_kernel<F32, Batched>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
+            "decode attention shared-memory opt-in");
+  });
+}
+
+template <bool F32, bool Batched>
+void launch_pair(const DecodeParams &params, dim3 partition_grid, dim3 combine_grid, bool combine,
+                 cudaStream_t stream) {
+  configure_once<F32, Batched>();
+  decode_partition_kernel<F32, Batched><<<partition_grid, kWarps * 32, kSmemBytes, stream>>>(params);
+  cuda_ok(cudaGetLastError(), "decode attention partition launch");
+  if (!combine) {
+    return;
+  }
+  cudaLaunchConfig_t config{};
+  config.gridDim = combine_grid;
+  config.blockDim = dim3(256, 1, 1);
+  config.dynamicSmemBytes = 0;
+  config.stream = stream;
+  cudaLaunchAttribute attribute{};
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  cuda_ok(cudaLaunchKernelEx(&config, decode_combine_kernel<F32, Batched>, params),
+          "decode attention combine launch");
+}
+
+} // namespace
+
+void launch_decode_attention(const DecodeArgs &a, cudaStream_t stream) {
+  DecodeParams params{};
+  params.query = a.query;
+  params.key = a.key;
+  params.value = a.value;
+  params.gate = a.gate;
+  params.output = a.output;
+  params.cache = static_cast<__nv_bfloat16 *>(a.kv_cache);
+  params.pos_array = a.device_position;
+  params.max_ctx = a.max_context_tokens;
+  params.host_pos = a.host_position;
+  params.partition_tokens = a.partition_tokens;
+  params.threshold_tokens = a.threshold_tokens;
+  params.capacity = a.partition_capacity;
+  params.max_partitions = a.max_partitions;
+  params.partial_max = a.partial_max;
+  params.partial_sum = a.partial_sum;
+  params.partial_value = a.partial_value;
+  params.partial_stride = 0;
+  params.status = device_status_word();
+  const bool split = a.partition_tokens != 0;
+  const dim3 partition_grid(split ? a.partition_capacity : 1, kKvHeads, 1);
+  const dim3 combine_grid(kQueryHeads, 4, 1);
+  if (a.activations_f32) {
+    launch_pair<true, false>(params, partition_grid, combine_grid, split, stream);
+  } else {
+    launch_pair<false, false>(params, partition_grid, combine_grid, split, stream);
+  }
+}
+
+void launch_batched_decode_attention(const BatchedDecodeArgs &a, cudaStream_t stream) {
+  DecodeParams params{};
+  params.query = a.query;
+  params.key = a.key;
+  params.value = a.value;
+  params.gate = a.gate;
+  params.output = a.output;
+  params.caches = a.kv_caches;
+  params.max_ctx_array = a.max_context_tokens;
+  params.pos_array = a.positions;
+  params.partition_tokens = 256;
+  params.threshold_tokens = 256;
+  params.capacity = a.partition_capacity;
+  params.max_partitions = a.partition_capacity;
+  const std::size_t partials = static_cast<std::size_t>(kQueryHeads) * a.partition_capacity;
+  params.partial_stride = partials;
+  params.partial_max = a.workspace;
+  params.partial_sum = a.workspace + static_cast<std::size_t>(a.batch) * partials;
+  params.partial_value = a.workspace + 2 * static_cast<std::size_t>(a.batch) * partials;
+  params.status = device_status_word();
+  const dim3 partition_grid(a.partition_capacity, kKvHeads, a.batch);
+  const dim3 combine_grid(kQueryHeads, 4, a.batch);
+  launch_pair<false, true>(params, partition_grid, combine_grid, true, stream);
+}
+
+} // namespace rib200

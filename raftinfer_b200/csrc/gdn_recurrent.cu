@@ -1,0 +1,156 @@
+// Recurrent gated delta-rule update (cpp/kernels/qwen35_delta.cu:482-576, CPU form
+// cpp/reference/qwen35.cpp:459-518) for key_dim = value_dim = 128.
+//
+// Per value head the FP32 state S[128][128] is read once and written once per token:
+//   a = S^T k, b = S^T q            (one pass, both products together)
+//   delta = (v - decay * a) * beta
+//   out   = decay * b + delta * (k . q)
+//   S     = decay * S + k delta^T
+// which is the reference's "decay, read, correct, write, read again" sequence folded into one pass.
+//
+// A CTA owns 64 state columns of one head; a warp owns 8 of them and a lane 4 state rows, so a lane's
+// slice (4 x 8 floats) stays in registers across tokens, every load is a full 32-byte sector and the two
+// reductions over the 128 rows are warp shuffles: the kernel has no block-level barrier at all.  For a
+// batch of decoding sequences the grid is (2, value_heads, sequences) and the step is bound by HBM.
+
+#include "common.hpp"
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+namespace rib200 {
+namespace {
+
+constexpr int kDim = 128;
+
+struct RecurrentParams {
+  const void *q, *k, *v;
+  std::size_t q_stride, k_stride, v_stride;
+  const float *beta;
+  const float *log_decay;
+  float *state;
+  float *const *states;
+  float *out;
+  std::uint32_t tokens;
+  std::uint32_t key_heads;
+  std::uint32_t value_heads;
+};
+
+template <bool F32> __device__ __forceinline__ void load4(const void *base, std::size_t index, float (&o)[4]) {
+  if constexpr (F32) {
+    const float4 v = *reinterpret_cast<const float4 *>(static_cast<const float *>(base) + index);
+    o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+  } else {
+    const uint2 raw = *reinterpret_cast<const uint2 *>(static_cast<const __nv_bfloat16 *>(base) + index);
+    o[0] = __uint_as_float(raw.x << 16);
+    o[1] = __uint_as_float(raw.x & 0xFFFF0000U);
+    o[2] = __uint_as_float(raw.y << 16);
+    o[3] = __uint_as_float(raw.y & 0xFFFF0000U);
+  }
+}
+
+template <bool F32>
+__global__ void __launch_bounds__(256) gdn_recurrent_kernel(const RecurrentParams p) {
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const std::uint32_t head = blockIdx.y;
+  const std::uint32_t seq = blockIdx.z;
+  const std::uint32_t key_head = head % p.key_heads;
+  const int col0 = blockIdx.x * 64 + warp * 8;
+  const int row0 = lane * 4;
+  float *state = (p.states != nullptr ? p.states[seq] : p.state) + static_cast<std::size_t>(head) * kDim * kDim;
+
+  float s[4][8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float4 lo = *reinterpret_cast<const float4 *>(state + (row0 + i) * kDim + col0);
+    const float4 hi = *reinterpret_cast<const float4 *>(state + (row0 + i) * kDim + col0 + 4);
+    s[i][0] = lo.x; s[i][1] = lo.y; s[i][2] = lo.z; s[i][3] = lo.w;
+    s[i][4] = hi.x; s[i][5] = hi.y; s[i][6] = hi.z; s[i][7] = hi.w;
+  }
+
+  for (std::uint32_t tok = 0; tok < p.tokens; ++tok) {
+    const std::size_t item = static_cast<std::size_t>(seq) * p.tokens + tok;
+    float kk[4];
+    float qq[4];
+    float vlo[4];
+    float vhi[4];
+    load4<F32>(p.k, item * p.k_stride + key_head * kDim + row0, kk);
+    load4<F32>(p.q, item * p.q_stride + key_head * kDim + row0, qq);
+    load4<F32>(p.v, item * p.v_stride + head * kDim + col0, vlo);
+    load4<F32>(p.v, item * p.v_stride + head * kDim + col0 + 4, vhi);
+    const float beta = p.beta[item * p.value_heads + head];
+    const float decay = expf(p.log_decay[item * p.value_heads + head]);
+
+    float red[17];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      red[c] = s[0][c] * kk[0] + s[1][c] * kk[1] + s[2][c] * kk[2] + s[3][c] * kk[3];
+      red[8 + c] = s[0][c] * qq[0] + s[1][c] * qq[1] + s[2][c] * qq[2] + s[3][c] * qq[3];
+    }
+    red[16] = kk[0] * qq[0] + kk[1] * qq[1] + kk[2] * qq[2] + kk[3] * qq[3];
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+#pragma unroll
+      for (int c = 0; c < 17; ++c) {
+        red[c] += __shfl_xor_sync(0xFFFFFFFFU, red[c], offset);
+      }
+    }
+    float delta[8];
+    float o[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const float vc = c < 4 ? vlo[c] : vhi[c - 4];
+      delta[c] = (vc - decay * red[c]) * beta;
+      o[c] = decay * red[8 + c] + delta[c] * red[16];
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        s[i][c] = decay * s[i][c] + kk[i] * delta[c];
+      }
+    }
+    if (lane == 0) {
+      float *dst = p.out + (item * p.value_heads + head) * kDim + col0;
+      *reinterpret_cast<float4 *>(dst) = make_float4(o[0], o[1], o[2], o[3]);
+      *reinterpret_cast<float4 *>(dst + 4) = make_float4(o[4], o[5], o[6], o[7]);
+    }
+  }
+
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    *reinterpret_cast<float4 *>(state + (row0 + i) * kDim + col0) = make_float4(s[i][0], s[i][1], s[i][2], s[i][3]);
+    *reinterpret_cast<float4 *>(state + (row0 + i) * kDim + col0 + 4) =
+        make_float4(s[i][4], s[i][5], s[i][6], s[i][7]);
+  }
+}
+
+} // namespace
+
+void launch_gdn_recurrent(const GdnCoreArgs &a, cudaStream_t stream) {
+  RecurrentParams p{};
+  p.q = a.q;
+  p.k = a.k;
+  p.v = a.v;
+  p.q_stride = a.q_stride;
+  p.k_stride = a.k_stride;
+  p.v_stride = a.v_stride;
+  p.beta = a.beta;
+  p.log_decay = a.log_decay;
+  p.state = a.state;
+  p.states = a.states;
+  p.out = a.out;
+  p.tokens = a.tokens;
+  p.key_heads = a.key_heads;
+  p.value_heads = a.value_heads;
+  const dim3 grid(2, a.value_heads, a.sequences);
+  if (a.qkv_f32) {
+    gdn_recurrent_kernel<true><<<grid, 256, 0, stream>>>(p);
+  } else {
+    gdn_recurrent_kernel<false><<<grid, 256, 0, stream>>>(p);
+  }
+  cuda_ok(cudaGetLastError(), "gated-delta recurrent launch");
+}
+
+} // namespace rib200

@@ -1,0 +1,253 @@
+"""Split-k / single-block GQA decode attention on the GPU against the CPU oracle, through the C ABI.
+
+Cases follow the reference's decode tests (cpp/tests/qwen35_cuda_attention_test.cu:768-1101: boundary contexts,
+two consecutive steps through a device-side position, appended cache rows, split-k partials, untouched workspace
+below the threshold) and extend them to N(0,1) operands and to the 4K / 32K / 128K contexts.  Tolerance for BF16
+outputs against the fp32-accumulated oracle: max abs <= 3e-2 and relative L2 <= 1e-2; FP32 outputs are held to
+1e-3 / 1e-4, which the two-term BF16 operand split is expected to meet."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import bindings as ob
+from raftinfer_b200 import kernels as K
+from raftinfer_b200 import synth
+
+from gpu_util import (D, HKV, HQ, NAN_BITS, act_tensor, cache_bits_of, cache_to_device, compare, decode_operands,
+                      dev, gate_bf16_outputs, make_cache, to_numpy_f32)
+
+pytestmark = pytest.mark.gpu
+SENTINEL = -12345.0
+
+
+def run_decode(ctx, max_ctx, mode, dtype, seed, device_position=False, q_scale=1.0, check_partials=True):
+    pos = ctx - 1
+    q, gate, k, v = decode_operands(seed, ctx, q_scale)
+    shape = K.Qwen35AttentionShape(1, HQ, HKV, D, max_ctx, 0 if device_position else pos)
+    plan = K.qwen35_online_decode_plan(shape, mode, ctx)
+    layout = K.qwen35_online_decode_workspace_layout(shape, plan.resolved_mode)
+    cache = cache_to_device(make_cache(k, v, max_ctx, pos))
+    dq, dg = act_tensor(q, dtype), act_tensor(gate, dtype)
+    dk, dv = act_tensor(k[pos], dtype), act_tensor(v[pos], dtype)
+    out = torch.full((HQ, D), 7.0, device=dev(), dtype=torch.float32 if dtype == K.DTYPE_F32 else torch.bfloat16)
+    ws = torch.full((max(layout.bytes // 4, 1),), SENTINEL, device=dev(), dtype=torch.float32)
+    dpos = torch.tensor([pos], device=dev(), dtype=torch.int32) if device_position else None
+    stream = torch.cuda.current_stream()
+    K.qwen35_online_attention_decode(dq, dk, dv, dg, out, cache, cache.numel() * 2, ws if layout.bytes else None,
+                                     layout.bytes, shape, dtype, K.KV_BF16, K.HEAD_MAJOR, plan, dpos, stream)
+    torch.cuda.synchronize()
+    assert K.device_status(stream) == 0
+
+    full = make_cache(k, v, max_ctx, ctx)
+    got_cache = cache_bits_of(cache).reshape(full.shape)
+    assert np.array_equal(got_cache, full), "cache rows: appended row must be the rounded input, others untouched"
+    want = ob.attention_core_cache(q[None], gate[None], full, max_ctx, pos)[0]
+    metrics = compare(to_numpy_f32(out), want)
+    if dtype == K.DTYPE_F32:
+        assert metrics["nonfinite"] == 0 and metrics["max_abs"] <= 1.0e-3 and metrics["rel_l2"] <= 1.0e-4, metrics
+    else:
+        gate_bf16_outputs(metrics)
+        assert metrics["rel_l2"] <= 4.0e-3, metrics
+
+    host_ws = ws.cpu().numpy()
+    split = plan.partition_tokens != 0 and ctx >= plan.split_k_threshold_tokens
+    if layout.bytes and not split:
+        assert (host_ws == SENTINEL).all(), "workspace must stay untouched below the split-k threshold"
+    if split and check_partials:
+        pc = layout.partial_count
+        max_parts = pc // HQ
+        parts = -(-ctx // plan.partition_tokens)
+        pmax = host_ws[:pc].reshape(HQ, max_parts)
+        psum = host_ws[pc:2 * pc].reshape(HQ, max_parts)
+        pval = host_ws[2 * pc:2 * pc + pc * D].reshape(HQ, max_parts, D)
+        wmax, wsum, wval = ob.decode_partials(q, full, max_ctx, ctx, plan.partition_tokens)
+        assert np.abs(pmax[:, :parts] - wmax[:, :parts]).max() <= 1.0e-4
+        assert np.abs(psum[:, :parts] / wsum[:, :parts] - 1.0).max() <= 1.0e-4
+        assert np.abs(pval[:, :parts] - wval[:, :parts]).max() <= 2.0e-3 * max(1.0, np.abs(wval[:, :parts]).max())
+        assert (pmax[:, parts:] == SENTINEL).all() and (pval[:, parts:] == SENTINEL).all()
+    return metrics
+
+
+@pytest.mark.parametrize("ctx", [1, 2, 15, 16, 17, 255, 256, 257, 511, 512, 513, 777, 1024])
+@pytest.mark.parametrize("dtype", [K.DTYPE_BF16, K.DTYPE_F32])
+def test_split_k_256_boundary_contexts(ctx, dtype):
+    run_decode(ctx, 1024, K.SPLIT_K_256, dtype, seed=0xB2000100 + ctx)
+
+
+@pytest.mark.parametrize("ctx", [1, 511, 512, 513, 777, 1024])
+def test_split_k_512(ctx):
+    run_decode(ctx, 1024, K.SPLIT_K_512, K.DTYPE_BF16, seed=0xB2000200 + ctx)
+
+
+@pytest.mark.parametrize("ctx", [1, 32, 128, 129, 300, 1000])
+@pytest.mark.parametrize("dtype", [K.DTYPE_BF16, K.DTYPE_F32])
+def test_single_block(ctx, dtype):
+    run_decode(ctx, 1024, K.SINGLE_BLOCK, dtype, seed=0xB2000300 + ctx)
+
+
+def test_cache_capacity_not_a_partition_multiple():
+    run_decode(700, 777, K.SPLIT_K_256, K.DTYPE_BF16, seed=0xB2000310)
+    run_decode(777, 777, K.SPLIT_K_256, K.DTYPE_F32, seed=0xB2000311)
+
+
+@pytest.mark.parametrize("ctx", [4096, 32768, 131072])
+def test_long_contexts(ctx):
+    metrics = run_decode(ctx, ctx, K.SPLIT_K_256, K.DTYPE_BF16, seed=0xB2000400 + ctx, device_position=True,
+                         check_partials=ctx <= 32768)
+    assert metrics["rel_l2"] <= 4.0e-3
+
+
+def test_large_logits_stay_finite():
+    # scores of order +-80: the running-max rescale must neither overflow nor lose the dominant key
+    run_decode(600, 1024, K.SPLIT_K_256, K.DTYPE_F32, seed=0xB2000500, q_scale=80.0)
+    run_decode(200, 1024, K.SINGLE_BLOCK, K.DTYPE_BF16, seed=0xB2000501, q_scale=80.0)
+
+
+def test_two_steps_through_a_device_position_and_plan_less_overload():
+    max_ctx, ctx0 = 1024, 300
+    q, gate, k, v = decode_operands(0xB2000600, ctx0 + 2)
+    shape = K.Qwen35AttentionShape(1, HQ, HKV, D, max_ctx, 0)
+    plan = K.qwen35_online_decode_plan(shape, K.SPLIT_K_256, ctx0 + 2)
+    layout = K.qwen35_online_decode_workspace_layout(shape, plan.resolved_mode)
+    cache = cache_to_device(make_cache(k, v, max_ctx, ctx0))
+    ws = torch.zeros(layout.bytes // 4, device=dev())
+    dpos = torch.tensor([ctx0], device=dev(), dtype=torch.int32)
+    stream = torch.cuda.current_stream()
+    outs = []
+    for step in range(2):
+        pos = ctx0 + step
+        out = torch.zeros(HQ, D, device=dev(), dtype=torch.bfloat16)
+        K.qwen35_online_attention_decode(act_tensor(q, K.DTYPE_BF16), act_tensor(k[pos], K.DTYPE_BF16),
+                                         act_tensor(v[pos], K.DTYPE_BF16), act_tensor(gate, K.DTYPE_BF16), out, cache,
+                                         cache.numel() * 2, ws, layout.bytes, shape, K.DTYPE_BF16, K.KV_BF16,
+                                         K.HEAD_MAJOR, plan, dpos, stream)
+        dpos += 1
+        outs.append(out)
+    torch.cuda.synchronize()
+    full = make_cache(k, v, max_ctx, ctx0 + 2)
+    assert np.array_equal(cache_bits_of(cache).reshape(full.shape), full)
+    for step, out in enumerate(outs):
+        want = ob.attention_core_cache(q[None], gate[None], full, max_ctx, ctx0 + step)[0]
+        gate_bf16_outputs(compare(to_numpy_f32(out), want))
+    # the plan-less overload (cpp/kernels/qwen35_online_attention.cuh:65-68) and the dispatcher with tokens == 1
+    shape3 = K.Qwen35AttentionShape(1, HQ, HKV, D, max_ctx, ctx0 + 1)
+    for call in ("decode", "dispatch"):
+        out = torch.zeros(HQ, D, device=dev(), dtype=torch.bfloat16)
+        args = (act_tensor(q, K.DTYPE_BF16), act_tensor(k[ctx0 + 1], K.DTYPE_BF16),
+                act_tensor(v[ctx0 + 1], K.DTYPE_BF16), act_tensor(gate, K.DTYPE_BF16), out, cache, cache.numel() * 2)
+        if call == "decode":
+            K.qwen35_online_attention_decode(*args, None, 0, shape3, K.DTYPE_BF16, K.KV_BF16, K.HEAD_MAJOR, None, None,
+                                             stream)
+        else:
+            K.qwen35_causal_attention(*args, None, 0, shape3, K.DTYPE_BF16,
+                                      K.Qwen35AttentionLaunchPolicy(K.ONLINE_TILED, K.KV_BF16, K.HEAD_MAJOR), stream)
+        torch.cuda.synchronize()
+        want = ob.attention_core_cache(q[None], gate[None], full, max_ctx, ctx0 + 1)[0]
+        gate_bf16_outputs(compare(to_numpy_f32(out), want))
+
+
+def test_capacity_guard_sets_a_status_bit_instead_of_trapping():
+    """The reference traps when a replayed position needs more partitions than the captured plan holds
+    (cpp/kernels/qwen35_online_attention.cu:714-717).  Here the combine kernel records the condition in the
+    device status word, leaves the output alone, and the context stays usable."""
+    max_ctx = 2048
+    q, gate, k, v = decode_operands(0xB2000700, 601)
+    shape = K.Qwen35AttentionShape(1, HQ, HKV, D, max_ctx, 0)
+    plan = K.qwen35_online_decode_plan(shape, K.SPLIT_K_256, 400)  # bucket 512 -> capacity 2
+    assert plan.active_partition_capacity == 2
+    layout = K.qwen35_online_decode_workspace_layout(shape, plan.resolved_mode)
+    cache = cache_to_device(make_cache(k, v, max_ctx, 600))
+    ws = torch.zeros(layout.bytes // 4, device=dev())
+    out = torch.full((HQ, D), 3.0, device=dev(), dtype=torch.bfloat16)
+    stream = torch.cuda.current_stream()
+    dpos = torch.tensor([600], device=dev(), dtype=torch.int32)  # context 601 needs 3 partitions
+    K.qwen35_online_attention_decode(act_tensor(q, K.DTYPE_BF16), act_tensor(k[600], K.DTYPE_BF16),
+                                     act_tensor(v[600], K.DTYPE_BF16), act_tensor(gate, K.DTYPE_BF16), out, cache,
+                                     cache.numel() * 2, ws, layout.bytes, shape, K.DTYPE_BF16, K.KV_BF16, K.HEAD_MAJOR,
+                                     plan, dpos, stream)
+    assert K.device_status(stream) == K.DEVICE_DECODE_CAPACITY_EXCEEDED
+    assert (out.float() == 3.0).all()
+    assert K.device_status(stream) == 0  # reading clears it
+    dpos.fill_(max_ctx)  # a position outside the cache
+    K.qwen35_online_attention_decode(act_tensor(q, K.DTYPE_BF16), act_tensor(k[600], K.DTYPE_BF16),
+                                     act_tensor(v[600], K.DTYPE_BF16), act_tensor(gate, K.DTYPE_BF16), out, cache,
+                                     cache.numel() * 2, ws, layout.bytes, shape, K.DTYPE_BF16, K.KV_BF16, K.HEAD_MAJOR,
+                                     plan, dpos, stream)
+    assert K.device_status(stream) == K.DEVICE_POSITION_OUT_OF_RANGE
+    assert (out.float() == 3.0).all()
+
+
+def test_decode_replays_inside_a_cuda_graph():
+    """One captured graph serves every position of its context bucket (the reference's decode-graph contract,
+    cpp/execution/qwen35_executor.cu:2191-2225): position, query and the new K/V row live in device buffers."""
+    max_ctx, ctx0, steps = 1024, 520, 3
+    q, gate, k, v = decode_operands(0xB2000800, ctx0 + steps)
+    shape = K.Qwen35AttentionShape(1, HQ, HKV, D, max_ctx, 0)
+    plan = K.qwen35_online_decode_plan(shape, K.SPLIT_K_256, ctx0 + steps)
+    layout = K.qwen35_online_decode_workspace_layout(shape, plan.resolved_mode)
+    cache = cache_to_device(make_cache(k, v, max_ctx, ctx0))
+    ws = torch.zeros(layout.bytes // 4, device=dev())
+    dq, dg = act_tensor(q, K.DTYPE_BF16), act_tensor(gate, K.DTYPE_BF16)
+    dk = torch.zeros(HKV, D, device=dev(), dtype=torch.bfloat16)
+    dv = torch.zeros(HKV, D, device=dev(), dtype=torch.bfloat16)
+    out = torch.zeros(HQ, D, device=dev(), dtype=torch.bfloat16)
+    dpos = torch.tensor([ctx0], device=dev(), dtype=torch.int32)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+
+    def call(stream):
+        K.qwen35_online_attention_decode(dq, dk, dv, dg, out, cache, cache.numel() * 2, ws, layout.bytes, shape,
+                                         K.DTYPE_BF16, K.KV_BF16, K.HEAD_MAJOR, plan, dpos, stream)
+
+    with torch.cuda.stream(side):
+        dk.copy_(act_tensor(k[ctx0], K.DTYPE_BF16))
+        dv.copy_(act_tensor(v[ctx0], K.DTYPE_BF16))
+        call(side)  # warm-up outside capture (first call sets the shared-memory attribute)
+        side.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            call(side)
+    full = make_cache(k, v, max_ctx, ctx0 + steps)
+    for step in range(steps):
+        pos = ctx0 + step
+        dk.copy_(act_tensor(k[pos], K.DTYPE_BF16))
+        dv.copy_(act_tensor(v[pos], K.DTYPE_BF16))
+        dpos.fill_(pos)
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+        want = ob.attention_core_cache(q[None], gate[None], full, max_ctx, pos)[0]
+        gate_bf16_outputs(compare(to_numpy_f32(out), want))
+    assert np.array_equal(cache_bits_of(cache).reshape(full.shape), full)
+
+
+def test_batched_ragged_decode():
+    """Five independent sequences with ragged contexts in one launch pair (the batched serving entry point)."""
+    contexts = [1, 200, 256, 1000, 2049]
+    batch = len(contexts)
+    rng_seed = 0xB2000900
+    caps = [-(-c // 256) * 256 for c in contexts]
+    largest = max(caps)
+    qs, gs, ks, vs, caches, fulls = [], [], [], [], [], []
+    for i, ctx in enumerate(contexts):
+        q, gate, k, v = decode_operands(rng_seed + i, ctx)
+        qs.append(q), gs.append(gate), ks.append(k[ctx - 1]), vs.append(v[ctx - 1])
+        caches.append(cache_to_device(make_cache(k, v, caps[i], ctx - 1)))
+        fulls.append(make_cache(k, v, caps[i], ctx))
+    dq, dg = act_tensor(np.stack(qs), K.DTYPE_BF16), act_tensor(np.stack(gs), K.DTYPE_BF16)
+    dk, dv = act_tensor(np.stack(ks), K.DTYPE_BF16), act_tensor(np.stack(vs), K.DTYPE_BF16)
+    out = torch.zeros(batch, HQ, D, device=dev(), dtype=torch.bfloat16)
+    ptrs = torch.tensor([c.data_ptr() for c in caches], device=dev(), dtype=torch.int64)
+    dcaps = torch.tensor(caps, device=dev(), dtype=torch.int32)
+    dpos = torch.tensor([c - 1 for c in contexts], device=dev(), dtype=torch.int32)
+    ws_bytes = K.batched_decode_workspace_bytes(batch, largest)
+    ws = torch.zeros(ws_bytes // 4, device=dev())
+    stream = torch.cuda.current_stream()
+    K.batched_decode_attention(dq, dk, dv, dg, out, ptrs, dcaps, dpos, batch, largest, ws, ws_bytes, stream)
+    torch.cuda.synchronize()
+    assert K.device_status(stream) == 0
+    got = to_numpy_f32(out)
+    for i, ctx in enumerate(contexts):
+        assert np.array_equal(cache_bits_of(caches[i]).reshape(fulls[i].shape), fulls[i])
+        want = ob.attention_core_cache(qs[i][None], gs[i][None], fulls[i], caps[i], ctx - 1)[0]
+        gate_bf16_outputs(compare(got[i], want))

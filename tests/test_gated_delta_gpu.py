@@ -1,0 +1,199 @@
+"""Gated delta-rule kernels on the GPU against the CPU oracle, through the C ABI.
+
+Cases follow cpp/tests/qwen35_cuda_delta_test.cu (T in {1,2,4,17}, decode after prefill, continued prefill, launches
+sharing device state without a sync, saturation edges, mixed weight dtypes, the dk = dv = 128 model shape) with
+N(0,1) operands.  Operands are quantised identically on both sides (cpp/tests/qwen35_cuda_delta_test.cu:257-270).
+Tolerances: outputs max abs <= 3e-2 and relative L2 <= 1e-2; FP32 state relative L2 <= 1e-3."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import bindings as ob
+from raftinfer_b200 import kernels as K
+from raftinfer_b200 import synth
+
+from gpu_util import act_tensor, bf16_tensor, compare, dev, to_numpy_f32
+
+pytestmark = pytest.mark.gpu
+HK, HV, DK = 16, 32, 128
+
+
+def core_operands(seed, tokens, hk=HK, hv=HV, quantise=True):
+    q = synth.round_bf16(synth.normal(seed, 0, (tokens, hk, DK)))
+    k = synth.round_bf16(synth.normal(seed, 1, (tokens, hk, DK)))
+    v = synth.round_bf16(synth.normal(seed, 2, (tokens, hv, DK)))
+    q = q / np.sqrt((q.astype(np.float64) ** 2).sum(-1, keepdims=True) + 1e-6) / np.sqrt(DK)
+    k = k / np.sqrt((k.astype(np.float64) ** 2).sum(-1, keepdims=True) + 1e-6)
+    q, k = q.astype(np.float32), k.astype(np.float32)
+    if quantise:
+        q, k = synth.round_bf16(q), synth.round_bf16(k)
+    beta = synth.sigmoid(synth.normal(seed, 3, (tokens, hv)))
+    g = (-synth.softplus(synth.normal(seed, 4, (tokens, hv)))).astype(np.float32)
+    return q, k, v, beta, g
+
+
+def run_core(tokens, dtype, seed, hk=HK, hv=HV, state0=None):
+    q, k, v, beta, g = core_operands(seed, tokens, hk, hv, quantise=dtype == K.DTYPE_BF16)
+    if state0 is None:
+        state0 = (0.05 * synth.normal(seed, 5, (hv, DK, DK))).astype(np.float32)
+    state = torch.from_numpy(state0.copy()).to(dev())
+    out = torch.zeros(tokens, hv, DK, device=dev())
+    ws_bytes = K.gdn_core_workspace_bytes(tokens, hk, hv, DK, DK)
+    ws = torch.zeros(max(ws_bytes // 4, 4), device=dev())
+    K.gdn_core(act_tensor(q, dtype), act_tensor(k, dtype), act_tensor(v, dtype),
+               torch.from_numpy(beta).to(dev()), torch.from_numpy(g).to(dev()), state, out, ws, ws_bytes, tokens, hk, hv,
+               DK, DK, dtype, torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    want_out, want_state = ob.gdn_core(q, k, v, beta, np.exp(g), state0)
+    m_out = compare(to_numpy_f32(out), want_out)
+    m_state = compare(to_numpy_f32(state), want_state)
+    return m_out, m_state
+
+
+@pytest.mark.parametrize("tokens", [1, 2, 4, 17, 63])
+@pytest.mark.parametrize("dtype", [K.DTYPE_BF16, K.DTYPE_F32])
+def test_recurrent_core(tokens, dtype):
+    m_out, m_state = run_core(tokens, dtype, seed=0xB2001000 + tokens)
+    assert m_out["nonfinite"] == 0 and m_out["max_abs"] <= 1.0e-4 and m_out["rel_l2"] <= 1.0e-4, m_out
+    assert m_state["nonfinite"] == 0 and m_state["rel_l2"] <= 1.0e-5, m_state
+
+
+def test_recurrent_core_small_head_counts():
+    m_out, m_state = run_core(3, K.DTYPE_F32, seed=0xB2001100, hk=2, hv=4)
+    assert m_out["rel_l2"] <= 1.0e-4 and m_state["rel_l2"] <= 1.0e-5
+
+
+def test_batched_decode_step():
+    batch = 6
+    seed = 0xB2001200
+    q, k, v, beta, g = core_operands(seed, batch)  # one token per sequence
+    states0 = [(0.05 * synth.normal(seed, 10 + i, (HV, DK, DK))).astype(np.float32) for i in range(batch)]
+    states = [torch.from_numpy(s.copy()).to(dev()) for s in states0]
+    ptrs = torch.tensor([s.data_ptr() for s in states], device=dev(), dtype=torch.int64)
+    out = torch.zeros(batch, HV, DK, device=dev())
+    K.batched_gdn_decode(bf16_tensor(q), bf16_tensor(k), bf16_tensor(v), torch.from_numpy(beta).to(dev()),
+                         torch.from_numpy(g).to(dev()), ptrs, out, batch, HK, HV, torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    got = to_numpy_f32(out)
+    for i in range(batch):
+        want_out, want_state = ob.gdn_core(q[i:i + 1], k[i:i + 1], v[i:i + 1], beta[i:i + 1], np.exp(g[i:i + 1]),
+                                           states0[i])
+        assert compare(got[i], want_out[0])["rel_l2"] <= 1.0e-4
+        assert compare(to_numpy_f32(states[i]), want_state)["rel_l2"] <= 1.0e-5
+
+
+# ---- whole layer (packed input) -------------------------------------------------------------------
+def layer_operands(seed, tokens, hk, hv, width, scale=1.0):
+    hidden = hv * DK
+    conv_dim = 2 * hk * DK + hidden
+    stride = conv_dim + 2 * hv + hidden
+    inp = synth.round_bf16(scale * synth.normal(seed, 0, (tokens, stride)))
+    conv_w = synth.round_bf16(0.3 * synth.normal(seed, 1, (conv_dim, width)))
+    rec_a = (-np.exp(0.3 * synth.normal(seed, 2, (hv,)))).astype(np.float32)
+    dt_bias = (0.5 * synth.normal(seed, 3, (hv,))).astype(np.float32)
+    norm_w = (1.0 + 0.1 * synth.normal(seed, 4, (DK,))).astype(np.float32)
+    conv_state = (0.5 * synth.normal(seed, 5, (conv_dim, width - 1))).astype(np.float32)
+    rec_state = (0.05 * synth.normal(seed, 6, (hv, DK, DK))).astype(np.float32)
+    return inp, conv_w, rec_a, dt_bias, norm_w, conv_state, rec_state
+
+
+class LayerRun:
+    """Device-side layer state carried across calls, with the oracle run in lock step."""
+
+    def __init__(self, seed, hk, hv, width, dtype, wdtype, tokens_total, scale=1.0):
+        self.hk, self.hv, self.width, self.dtype, self.wdtype = hk, hv, width, dtype, wdtype
+        ops = layer_operands(seed, tokens_total, hk, hv, width, scale)
+        self.inp, self.conv_w, self.rec_a, self.dt_bias, self.norm_w, self.cs, self.rs = ops
+        if wdtype != K.DTYPE_F32:
+            self.rec_a, self.dt_bias, self.norm_w = (synth.round_bf16(x) for x in (self.rec_a, self.dt_bias, self.norm_w))
+        self.d_conv_w = act_tensor(self.conv_w, wdtype)
+        self.d_rec_a = act_tensor(self.rec_a, wdtype)
+        self.d_dt = act_tensor(self.dt_bias, wdtype)
+        self.d_norm = act_tensor(self.norm_w, wdtype)
+        self.d_cs = torch.from_numpy(self.cs.copy()).to(dev())
+        self.d_rs = torch.from_numpy(self.rs.copy()).to(dev())
+        self.done = 0
+
+    def step(self, tokens, sync=True):
+        hidden = self.hv * DK
+        shape = K.GatedDeltaShape(tokens, hidden, self.hk, self.hv, DK, DK, self.width, 1.0e-6)
+        chunk = self.inp[self.done:self.done + tokens]
+        self.done += tokens
+        ws_bytes = K.qwen35_gated_delta_workspace_bytes(shape)
+        ws = torch.zeros(ws_bytes // 4, device=dev())
+        out = torch.zeros(tokens, hidden, device=dev(),
+                          dtype=torch.float32 if self.dtype == K.DTYPE_F32 else torch.bfloat16)
+        d_in = act_tensor(chunk, self.dtype)
+        K.qwen35_gated_delta(d_in, self.d_conv_w, self.d_rec_a, self.d_dt, self.d_norm, out, self.d_cs, self.d_rs, ws,
+                             ws_bytes, shape, self.dtype, self.wdtype, torch.cuda.current_stream())
+        if sync:
+            torch.cuda.synchronize()
+        want, self.cs, self.rs = ob.gated_delta_layer(chunk, self.conv_w, self.rec_a, self.dt_bias, self.norm_w, self.cs,
+                                                      self.rs, (tokens, hidden, self.hk, self.hv, DK, DK, self.width,
+                                                                1.0e-6))
+        return out, want, (d_in, ws)
+
+    def check(self, out, want):
+        m = compare(to_numpy_f32(out), want)
+        assert m["nonfinite"] == 0 and m["max_abs"] <= 3.0e-2 and m["rel_l2"] <= 1.0e-2, m
+        if self.dtype == K.DTYPE_F32:
+            assert m["max_abs"] <= 2.0e-3 and m["rel_l2"] <= 2.0e-4, m
+        cs = compare(to_numpy_f32(self.d_cs).reshape(-1), self.cs.reshape(-1))
+        assert cs["max_abs"] == 0.0, cs
+        rs = compare(to_numpy_f32(self.d_rs).reshape(-1), self.rs.reshape(-1))
+        assert rs["nonfinite"] == 0 and rs["rel_l2"] <= 1.0e-3, rs
+
+
+@pytest.mark.parametrize("tokens", [1, 2, 4, 17])
+@pytest.mark.parametrize("dtype,wdtype", [(K.DTYPE_BF16, K.DTYPE_F32), (K.DTYPE_F32, K.DTYPE_F32),
+                                          (K.DTYPE_BF16, K.DTYPE_BF16), (K.DTYPE_F32, K.DTYPE_BF16)])
+def test_layer_small_heads(tokens, dtype, wdtype):
+    run = LayerRun(0xB2002000 + tokens, 2, 4, 3, dtype, wdtype, tokens)
+    out, want, _ = run.step(tokens)
+    run.check(out, want)
+
+
+def test_layer_model_shape_prefill_then_decode_then_continued_prefill():
+    run = LayerRun(0xB2002100, HK, HV, 4, K.DTYPE_BF16, K.DTYPE_F32, 3 + 1 + 1 + 5)
+    for tokens in (3, 1, 1, 5):
+        out, want, _ = run.step(tokens)
+        run.check(out, want)
+
+
+def test_layer_three_launches_share_device_state_without_a_sync():
+    run = LayerRun(0xB2002200, 2, 4, 4, K.DTYPE_F32, K.DTYPE_F32, 6)
+    results = [run.step(2, sync=False) for _ in range(3)]
+    torch.cuda.synchronize()
+    for out, want, _ in results[:-1]:
+        m = compare(to_numpy_f32(out), want)
+        assert m["max_abs"] <= 2.0e-3 and m["rel_l2"] <= 2.0e-4, m
+    run.check(results[-1][0], results[-1][1])
+
+
+def test_layer_conv_width_one_and_wide():
+    for width in (1, 2, 6):
+        run = LayerRun(0xB2002300 + width, 2, 4, width, K.DTYPE_F32, K.DTYPE_F32, 5)
+        if width == 1:
+            run.d_cs = torch.zeros(4, device=dev())
+            run.cs = np.zeros((run.cs.shape[0], 0), dtype=np.float32)
+        out, want, _ = run.step(5)
+        m = compare(to_numpy_f32(out), want)
+        assert m["max_abs"] <= 2.0e-3 and m["rel_l2"] <= 2.0e-4, (width, m)
+
+
+def test_layer_saturation_edges_stay_finite():
+    """Extreme gate inputs (cpp/tests/qwen35_cuda_delta_test.cu:568-603): A from -12 to -0.001, dt_bias -25..5,
+    b = +-30, z = +-18.  Everything must stay finite and match the oracle."""
+    hk, hv, width, tokens = 2, 4, 4, 4
+    run = LayerRun(0xB2002400, hk, hv, width, K.DTYPE_F32, K.DTYPE_F32, tokens)
+    hidden = hv * DK
+    conv_dim = 2 * hk * DK + hidden
+    run.rec_a = np.array([-12.0, -1.0, -0.05, -0.001], dtype=np.float32)
+    run.dt_bias = np.array([-25.0, -3.0, 0.5, 5.0], dtype=np.float32)
+    run.d_rec_a, run.d_dt = act_tensor(run.rec_a, K.DTYPE_F32), act_tensor(run.dt_bias, K.DTYPE_F32)
+    run.inp[:, conv_dim:conv_dim + hv] = np.array([30.0, -30.0, 30.0, -30.0], dtype=np.float32)
+    run.inp[:, conv_dim + 2 * hv::2] = 18.0
+    run.inp[:, conv_dim + 2 * hv + 1::2] = -18.0
+    out, want, _ = run.step(tokens)
+    assert np.isfinite(to_numpy_f32(out)).all() and np.isfinite(to_numpy_f32(run.d_rs)).all()
+    run.check(out, want)
