@@ -179,6 +179,7 @@ def main():
     warmup = max(3, args.warmup)
     steps = max(1, args.steps)
     ctx = args.context
+    torch.cuda.set_stream(torch.cuda.Stream(device=dev))  # the library rejects the NULL stream
     stream = torch.cuda.current_stream()
 
     gen = torch.Generator(device=dev)

@@ -15,3 +15,18 @@ def pytest_configure(config):
 @pytest.fixture(scope="session")
 def golden_dir():
     return os.path.join(ROOT, "tests", "golden")
+
+
+@pytest.fixture(autouse=True, scope="session")
+def _non_default_cuda_stream():
+    """The library rejects the NULL (legacy default) stream, as the reference does
+    (cpp/kernels/qwen35_attention.cu:430), so GPU tests make a real stream current."""
+    try:
+        import torch
+    except ImportError:
+        yield
+        return
+    if torch.cuda.is_available():
+        torch.cuda.set_device(0)
+        torch.cuda.set_stream(torch.cuda.Stream())
+    yield
