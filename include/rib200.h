@@ -244,6 +244,30 @@ Rib200Status rib200_batched_gdn_decode(const void *q, const void *k, const void 
                                        const float *log_decay, float *const *states, float *out, size_t batch,
                                        size_t key_heads, size_t value_heads, void *stream);
 
+/* No counterpart in the reference.  The same split-k decode step as rib200_online_attention_decode (partition
+ * size 256, grid sized for the whole cache so one launch shape serves every position), for hosts that may
+ * not allocate device memory on the decode path and have no workspace to hand over: a runtime that gave all
+ * of its device memory to a pool at start-up and treats any later allocation as a bug (RAFTInfer's executor
+ * asserts zero allocations after construction, cpp/tests/qwen35_executor_test.cu:1426-1441), a plugin that is
+ * only given the tensors of the operator it replaces, or a latency-critical serving thread for which the
+ * implicit device synchronisation of cudaMalloc is not acceptable.  The partials go to an array built into the
+ * library (2 113 536 bytes of device memory per GPU that loads it, held until the process exits), so:
+ *   - shape->max_context_tokens may be at most 32768; larger caches are refused with
+ *     RIB200_STATUS_INVALID_ARGUMENT (use the workspace entry point for those);
+ *   - the call allocates nothing and frees nothing;
+ *   - the first call on each device looks up the array's device address; make that first call outside any
+ *     stream capture;
+ *   - all calls on a device share the one array, which keeps whatever the previous call left in it.  Nothing
+ *     in it needs clearing (every partial that is read was written by the same call), but two calls whose
+ *     kernels overlap on the GPU (different streams, or graphs launched concurrently) race on it: serialise
+ *     them.
+ * Other arguments as rib200_online_attention_decode; the cache must be BF16 head-major. */
+Rib200Status rib200_online_attention_decode_static_scratch(const void *query, const void *key, const void *value,
+                                                           const void *gate, void *output, void *kv_cache,
+                                                           size_t kv_cache_bytes, const Rib200AttentionShape *shape,
+                                                           int32_t activation_dtype, const uint32_t *device_position,
+                                                           void *stream);
+
 /* Reads and clears the status word the kernels of this library set on the current device.  It
  * synchronises `stream` first, so it is not for use inside a graph capture. */
 Rib200Status rib200_device_status(void *stream, uint32_t *bits);

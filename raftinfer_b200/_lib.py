@@ -87,6 +87,8 @@ PROTOTYPES = {
     "rib200_batched_decode_workspace_bytes": [sz, sz, C.POINTER(sz)],
     "rib200_batched_decode_attention": [vp, vp, vp, vp, vp, vp, vp, vp, sz, sz, vp, sz, vp],
     "rib200_batched_gdn_decode": [vp, vp, vp, vp, vp, vp, vp, sz, sz, sz, vp],
+    "rib200_online_attention_decode_static_scratch": [vp, vp, vp, vp, vp, vp, sz, C.POINTER(AttentionShape), C.c_int32,
+                                                      vp, vp],
     "rib200_device_status": [vp, C.POINTER(C.c_uint32)],
 }
 

@@ -632,3 +632,95 @@ void launch_batched_decode_attention(const BatchedDecodeArgs &a, cudaStream_t st
 }
 
 } // namespace rib200
+
+// ---- decode with library-owned scratch -------------------------------------------------------
+//
+// Split-k partials of the entry point below live in this array instead of a caller workspace.  It is sized for
+// the largest cache the entry point accepts: 16 heads x (32768 / 256) partitions x (max + sum + 256 values)
+// floats = 2 113 536 bytes.  Every GPU that loads the library keeps that much memory until the process exits.
+constexpr std::uint32_t kStaticScratchMaxContext = 32768;
+constexpr std::uint32_t kStaticScratchPartitions = kStaticScratchMaxContext / 256;
+constexpr std::size_t kStaticScratchFloats = static_cast<std::size_t>(16) * kStaticScratchPartitions * (256 + 2);
+static __device__ __align__(256) float g_decode_scratch[kStaticScratchFloats];
+
+// In host code `g_decode_scratch` is only a handle for the runtime, not a device address, so a kernel must
+// never be given the name itself.  The real address is looked up once per device, with that device current.
+static float *static_scratch_for_current_device() {
+  using namespace rib200;
+  static std::mutex lock;
+  static float *address[64] = {};
+  int device = 0;
+  cuda_ok(cudaGetDevice(&device), "cudaGetDevice");
+  require(device >= 0 && device < 64, "device ordinal out of range", RIB200_STATUS_INTERNAL);
+  std::lock_guard<std::mutex> guard(lock);
+  if (address[device] == nullptr) {
+    float *ptr = nullptr;
+    cuda_ok(cudaGetSymbolAddress(reinterpret_cast<void **>(&ptr), g_decode_scratch),
+            "decode scratch: cudaGetSymbolAddress");
+    require(ptr != nullptr, "decode scratch: the runtime returned a null address", RIB200_STATUS_INTERNAL);
+    address[device] = ptr;
+  }
+  return address[device];
+}
+
+extern "C" Rib200Status rib200_online_attention_decode_static_scratch(
+    const void *query, const void *key, const void *value, const void *gate, void *output, void *kv_cache,
+    size_t kv_cache_bytes, const Rib200AttentionShape *shape, int32_t activation_dtype,
+    const uint32_t *device_position, void *stream) {
+  using namespace rib200;
+  return guarded([&] {
+    require(shape != nullptr, "static-scratch decode: shape pointer is null");
+    require(query != nullptr && key != nullptr && value != nullptr && gate != nullptr && output != nullptr,
+            "static-scratch decode: an activation pointer is null");
+    require(kv_cache != nullptr, "static-scratch decode: KV cache pointer is null");
+    require(stream != nullptr, "static-scratch decode: CUDA stream is null");
+    require(shape->tokens == 1 && shape->query_heads == kQueryHeads && shape->kv_heads == kKvHeads &&
+                shape->head_dim == kHeadDim,
+            "static-scratch decode: needs one token, 16 query heads, 4 kv heads, head_dim 256");
+    require(shape->max_context_tokens != 0 && shape->past_tokens < shape->max_context_tokens,
+            "static-scratch decode: position outside the cache");
+    require(shape->max_context_tokens <= kStaticScratchMaxContext,
+            "static-scratch decode: max_context_tokens exceeds the 32768 tokens the built-in scratch is sized for; "
+            "use rib200_online_attention_decode with a caller workspace");
+    require(activation_dtype == RIB200_DTYPE_F32 || activation_dtype == RIB200_DTYPE_BF16,
+            "static-scratch decode: activations must be F32 or BF16");
+    require(kv_cache_bytes >= 2 * shape->max_context_tokens * kKvHeads * kHeadDim * sizeof(__nv_bfloat16),
+            "static-scratch decode: KV cache is too small");
+    for (const void *ptr : {query, key, value, gate, static_cast<const void *>(output),
+                            static_cast<const void *>(kv_cache)}) {
+      require(reinterpret_cast<std::uintptr_t>(ptr) % 16 == 0,
+              "static-scratch decode: pointers must be 16-byte aligned");
+    }
+    const std::uint32_t max_ctx = static_cast<std::uint32_t>(shape->max_context_tokens);
+    const std::uint32_t partitions = (max_ctx + 255) / 256;
+    float *scratch = static_scratch_for_current_device();
+    DecodeParams params{};
+    params.query = query;
+    params.key = key;
+    params.value = value;
+    params.gate = gate;
+    params.output = output;
+    params.cache = static_cast<__nv_bfloat16 *>(kv_cache);
+    params.pos_array = device_position;
+    params.max_ctx = max_ctx;
+    params.host_pos = static_cast<std::uint32_t>(shape->past_tokens);
+    params.partition_tokens = 256;
+    params.threshold_tokens = 256;
+    params.capacity = partitions;
+    params.max_partitions = partitions;
+    const std::size_t partials = static_cast<std::size_t>(kQueryHeads) * partitions;
+    params.partial_max = scratch;
+    params.partial_sum = scratch + partials;
+    params.partial_value = scratch + 2 * partials;
+    params.partial_stride = 0;
+    params.status = device_status_word();
+    const dim3 partition_grid(partitions, kKvHeads, 1);
+    const dim3 combine_grid(kQueryHeads, 4, 1);
+    auto *cuda_stream = static_cast<cudaStream_t>(stream);
+    if (activation_dtype == RIB200_DTYPE_F32) {
+      launch_pair<true, false>(params, partition_grid, combine_grid, true, cuda_stream);
+    } else {
+      launch_pair<false, false>(params, partition_grid, combine_grid, true, cuda_stream);
+    }
+  });
+}

@@ -219,6 +219,18 @@ def qwen35_online_attention_decode(query, key, value, gate, output, kv_cache, kv
                                               _ptr(device_position), _stream(stream)))
 
 
+def online_attention_decode_static_scratch(query, key, value, gate, output, kv_cache, kv_cache_bytes, shape,
+                                           activation_dtype, device_position, stream):
+    """Split-k decode whose partials live in an array built into the library (no workspace argument, nothing
+    allocated): for hosts that cannot allocate on the decode path.  Caches of at most 32768 tokens; calls that
+    overlap on one GPU race on the shared array.  See include/rib200.h."""
+    s = shape.c()
+    _check(lib.rib200_online_attention_decode_static_scratch(_ptr(query), _ptr(key), _ptr(value), _ptr(gate),
+                                                             _ptr(output), _ptr(kv_cache), kv_cache_bytes,
+                                                             C.byref(s), activation_dtype, _ptr(device_position),
+                                                             _stream(stream)))
+
+
 def batched_decode_workspace_bytes(batch, max_context_tokens):
     out = C.c_size_t()
     _check(lib.rib200_batched_decode_workspace_bytes(batch, max_context_tokens, C.byref(out)))
