@@ -26,6 +26,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdint>
+#include <cstdlib>
 #include <mutex>
 
 namespace rib200 {
@@ -35,13 +36,18 @@ constexpr int kHeadDim = 256;
 constexpr int kQueryHeads = 16;
 constexpr int kKvHeads = 4;
 constexpr int kGroup = kQueryHeads / kKvHeads;
-constexpr int kWarps = 4;
-constexpr int kStages = 3;
 constexpr int kStepTokens = 16;
-constexpr int kStageBytes = 2 * kStepTokens * kHeadDim * 2; // K + V of one step: 16 KiB
-constexpr int kRingBytes = kWarps * kStages * kStageBytes;  // 192 KiB
-constexpr int kMergeFloats = kWarps * (kGroup * kHeadDim + 2 * kGroup);
-constexpr int kSmemBytes = kRingBytes + kMergeFloats * 4;
+constexpr int kSlotBytes = kStepTokens * kHeadDim * 2; // the K rows or the V rows of one step: 8 KiB
+
+// Shape of one CTA: `Warps` warps, each with a private ring of `Slots` 8 KiB slots (K and V slots alternate).
+template <int Warps, int Slots> struct Tile {
+  static constexpr int kWarps = Warps;
+  static constexpr int kRingSlots = Slots;
+  static constexpr int kRingBytes = Warps * Slots * kSlotBytes;
+  static constexpr int kMergeFloats = Warps * (kGroup * kHeadDim + 2 * kGroup);
+  static constexpr int kSmemBytes = kRingBytes + kMergeFloats * 4;
+  static constexpr int kCtasPerSm = (227 * 1024) / (kSmemBytes + 1024) > 0 ? (227 * 1024) / (kSmemBytes + 1024) : 1;
+};
 constexpr float kLog2e = 1.4426950408889634F;
 
 struct DecodeParams {
@@ -74,6 +80,10 @@ __device__ __forceinline__ std::uint32_t smem_address(const void *p) {
 __device__ __forceinline__ void cp_async_16(std::uint32_t dst, const void *src, bool valid) {
   const int bytes = valid ? 16 : 0; // 0 source bytes: the 16 destination bytes are zero-filled
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void cp_async_16_full(std::uint32_t dst, const void *src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
 }
 
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
@@ -156,9 +166,12 @@ template <bool F32> __device__ __forceinline__ uint4 load8_as_bf16(const void *b
   return raw;
 }
 
-// Partition kernel.  grid = (partition capacity, 4 KV heads, sequences), 128 threads.
-template <bool F32, bool Batched>
-__global__ void __launch_bounds__(kWarps * 32, 1) decode_partition_kernel(const DecodeParams p) {
+// Partition kernel.  grid = (partition capacity, 4 KV heads, sequences), Warps * 32 threads.
+template <bool F32, bool Batched, class T>
+__global__ void __launch_bounds__(T::kWarps * 32, T::kCtasPerSm) decode_partition_kernel(const DecodeParams p) {
+  constexpr int kWarps = T::kWarps;
+  constexpr int kRingSlots = T::kRingSlots;
+  constexpr int kRingBytes = T::kRingBytes;
   extern __shared__ __align__(128) unsigned char smem[];
   // The combine kernel is launched with programmatic stream serialisation: let it become resident now;
   // it blocks in griddepcontrol.wait until this whole grid has finished and flushed.
@@ -200,6 +213,94 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_partition_kernel(const 
   const std::size_t act_seq = static_cast<std::size_t>(seq);
   const std::size_t kv_in_base = (act_seq * kKvHeads + kvh) * kHeadDim;
 
+  const std::uint32_t total_steps = (end - begin + kStepTokens - 1) / kStepTokens;
+  const std::uint32_t my_steps =
+      total_steps > static_cast<std::uint32_t>(warp) ? (total_steps - warp + kWarps - 1) / kWarps : 0;
+  const std::uint32_t my_slots = 2 * my_steps; // slot 2i = K rows of step i, slot 2i+1 = V rows of step i
+  const std::uint32_t ring = smem_address(smem) + warp * kRingSlots * kSlotBytes + lane * 16;
+
+  // Copies slot `n` of this warp into ring position n % kRingSlots.  Steps that lie wholly inside the live
+  // range and do not hold the token being appended take the branch-free path (constant offsets from one base
+  // pointer).  The row being appended is not in the cache yet: its owner lane converts it from the key/value
+  // inputs, feeds the ring and writes the cache row.  Rows past the range are zero-filled.
+  auto issue = [&](std::uint32_t n) {
+    const std::uint32_t tok0 = begin + (warp + (n >> 1) * kWarps) * kStepTokens;
+    const std::uint32_t slot = ring + (n % kRingSlots) * kSlotBytes;
+    const bool plain = tok0 + kStepTokens <= end && !(pos >= tok0 && pos < tok0 + kStepTokens);
+    if ((n & 1U) == 0) {
+      if (plain) {
+        const __nv_bfloat16 *src = k_plane + static_cast<std::size_t>(tok0 + g) * kHeadDim + 8 * t;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            cp_async_16_full(slot + (2 * j + r) * 512, src + r * 8 * kHeadDim + 32 * j);
+          }
+        }
+        return;
+      }
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const std::uint32_t tok = tok0 + g + 8 * r;
+        const bool valid = tok < end;
+        const std::size_t row = static_cast<std::size_t>(valid ? tok : end - 1) * kHeadDim;
+        if (tok == pos) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint4 raw = load8_as_bf16<F32>(p.key, kv_in_base + 32 * j + 8 * t);
+            sts128(slot + (2 * j + r) * 512, raw);
+            *reinterpret_cast<uint4 *>(k_plane + row + 32 * j + 8 * t) = raw;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            cp_async_16(slot + (2 * j + r) * 512, k_plane + row + 32 * j + 8 * t, valid);
+          }
+        }
+      }
+      return;
+    }
+    if (plain) {
+      const __nv_bfloat16 *src = v_plane + static_cast<std::size_t>(tok0 + 2 * t) * kHeadDim + 8 * g;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+          cp_async_16_full(slot + (4 * s + q) * 512, src + ((q & 1) + 8 * (q >> 1)) * kHeadDim + 64 * s);
+        }
+      }
+      return;
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const std::uint32_t tok = tok0 + 2 * t + (q & 1) + 8 * (q >> 1);
+      const bool valid = tok < end;
+      const std::size_t row = static_cast<std::size_t>(valid ? tok : end - 1) * kHeadDim;
+      if (tok == pos) {
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+          const uint4 raw = load8_as_bf16<F32>(p.value, kv_in_base + 8 * (8 * s + g));
+          sts128(slot + (4 * s + q) * 512, raw);
+          *reinterpret_cast<uint4 *>(v_plane + row + 8 * (8 * s + g)) = raw;
+        }
+      } else {
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+          cp_async_16(slot + (4 * s + q) * 512, v_plane + row + 8 * (8 * s + g), valid);
+        }
+      }
+    }
+  };
+
+  // get the first slots moving before anything else is fetched
+#pragma unroll
+  for (int n = 0; n < kRingSlots - 1; ++n) {
+    if (static_cast<std::uint32_t>(n) < my_slots) {
+      issue(n);
+    }
+    cp_async_commit();
+  }
+
   // Query fragments (the B operand of the score product): lane (g, t) holds, for every 32-dim block j,
   // dims 32j + 8t .. +8 of N column g = (head g>>1, split part g&1), pre-scaled by 1/sqrt(256).
   std::uint32_t qf[32];
@@ -218,57 +319,6 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_partition_kernel(const 
     }
   }
 
-  const std::uint32_t total_steps = (end - begin + kStepTokens - 1) / kStepTokens;
-  const std::uint32_t my_steps =
-      total_steps > static_cast<std::uint32_t>(warp) ? (total_steps - warp + kWarps - 1) / kWarps : 0;
-  const std::uint32_t ring = smem_address(smem) + warp * kStages * kStageBytes + lane * 16;
-
-  // Copies step `i` of this warp into ring stage i % kStages.  The row of the token being appended is
-  // not in the cache yet: its owner lane converts it from the key/value inputs, feeds the ring and
-  // writes the cache row.
-  auto issue = [&](std::uint32_t i) {
-    const std::uint32_t tok0 = begin + (warp + i * kWarps) * kStepTokens;
-    const std::uint32_t stage = ring + (i % kStages) * kStageBytes;
-#pragma unroll
-    for (int r = 0; r < 2; ++r) {
-      const std::uint32_t tok = tok0 + g + 8 * r;
-      const bool valid = tok < end;
-      const std::size_t row = static_cast<std::size_t>(valid ? tok : end - 1) * kHeadDim;
-      if (tok == pos) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint4 raw = load8_as_bf16<F32>(p.key, kv_in_base + 32 * j + 8 * t);
-          sts128(stage + (2 * j + r) * 512, raw);
-          *reinterpret_cast<uint4 *>(k_plane + row + 32 * j + 8 * t) = raw;
-        }
-      } else {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          cp_async_16(stage + (2 * j + r) * 512, k_plane + row + 32 * j + 8 * t, valid);
-        }
-      }
-    }
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const std::uint32_t tok = tok0 + 2 * t + (q & 1) + 8 * (q >> 1);
-      const bool valid = tok < end;
-      const std::size_t row = static_cast<std::size_t>(valid ? tok : end - 1) * kHeadDim;
-      if (tok == pos) {
-#pragma unroll
-        for (int s = 0; s < 4; ++s) {
-          const uint4 raw = load8_as_bf16<F32>(p.value, kv_in_base + 8 * (8 * s + g));
-          sts128(stage + 8192 + (4 * s + q) * 512, raw);
-          *reinterpret_cast<uint4 *>(v_plane + row + 8 * (8 * s + g)) = raw;
-        }
-      } else {
-#pragma unroll
-        for (int s = 0; s < 4; ++s) {
-          cp_async_16(stage + 8192 + (4 * s + q) * 512, v_plane + row + 8 * (8 * s + g), valid);
-        }
-      }
-    }
-  };
-
   float oacc[16][4];
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
@@ -277,37 +327,36 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_partition_kernel(const 
   float run_max = -INFINITY; // head t, identical in the eight lanes that share t
   float run_sum = 0.0F;      // this lane's share of the row sum of head t
 
-#pragma unroll
-  for (int s = 0; s < kStages - 1; ++s) {
-    if (static_cast<std::uint32_t>(s) < my_steps) {
-      issue(s);
-    }
-    cp_async_commit();
-  }
-
   for (std::uint32_t i = 0; i < my_steps; ++i) {
-    if (i + kStages - 1 < my_steps) {
-      issue(i + kStages - 1);
+    const std::uint32_t tok0 = begin + (warp + i * kWarps) * kStepTokens;
+
+    // ---- K slot: scores and softmax ----
+    if (2 * i + kRingSlots - 1 < my_slots) {
+      issue(2 * i + kRingSlots - 1);
     }
     cp_async_commit();
-    cp_async_wait<kStages - 1>();
+    cp_async_wait<kRingSlots - 1>();
+    const std::uint32_t k_slot = ring + ((2 * i) % kRingSlots) * kSlotBytes;
 
-    const std::uint32_t tok0 = begin + (warp + i * kWarps) * kStepTokens;
-    const std::uint32_t stage = ring + (i % kStages) * kStageBytes;
-
-    // scores: S[token][column] = K[token][:] . Q[column][:]
+    // S[token][column] = K[token][:] . Q[column][:], four independent accumulator chains
     float s0[4] = {0.0F, 0.0F, 0.0F, 0.0F};
     float s1[4] = {0.0F, 0.0F, 0.0F, 0.0F};
+    float s2[4] = {0.0F, 0.0F, 0.0F, 0.0F};
+    float s3[4] = {0.0F, 0.0F, 0.0F, 0.0F};
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const uint4 ka = lds128(stage + (2 * j) * 512);
-      const uint4 kb = lds128(stage + (2 * j + 1) * 512);
+    for (int j = 0; j < 8; j += 2) {
+      const uint4 ka = lds128(k_slot + (2 * j) * 512);
+      const uint4 kb = lds128(k_slot + (2 * j + 1) * 512);
+      const uint4 kc = lds128(k_slot + (2 * j + 2) * 512);
+      const uint4 kd = lds128(k_slot + (2 * j + 3) * 512);
       mma_bf16(s0, ka.x, kb.x, ka.y, kb.y, qf[4 * j + 0], qf[4 * j + 1]);
       mma_bf16(s1, ka.z, kb.z, ka.w, kb.w, qf[4 * j + 2], qf[4 * j + 3]);
+      mma_bf16(s2, kc.x, kd.x, kc.y, kd.y, qf[4 * j + 4], qf[4 * j + 5]);
+      mma_bf16(s3, kc.z, kd.z, kc.w, kd.w, qf[4 * j + 6], qf[4 * j + 7]);
     }
     // lane (g, t): head t, tokens tok0 + g and tok0 + g + 8 (high part + residual columns)
-    float score_a = (s0[0] + s1[0]) + (s0[1] + s1[1]);
-    float score_b = (s0[2] + s1[2]) + (s0[3] + s1[3]);
+    float score_a = ((s0[0] + s1[0]) + (s2[0] + s3[0])) + ((s0[1] + s1[1]) + (s2[1] + s3[1]));
+    float score_b = ((s0[2] + s1[2]) + (s2[2] + s3[2])) + ((s0[3] + s1[3]) + (s2[3] + s3[3]));
     if (tok0 + g >= end) {
       score_a = -INFINITY;
     }
@@ -318,19 +367,23 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_partition_kernel(const 
     step_max = fmaxf(step_max, __shfl_xor_sync(0xFFFFFFFFU, step_max, 4));
     step_max = fmaxf(step_max, __shfl_xor_sync(0xFFFFFFFFU, step_max, 8));
     step_max = fmaxf(step_max, __shfl_xor_sync(0xFFFFFFFFU, step_max, 16));
-    const float new_max = fmaxf(run_max, step_max); // finite: the step holds at least one live token
-    const float rescale = exp2f((run_max - new_max) * kLog2e);
-    const float prob_a = exp2f((score_a - new_max) * kLog2e);
-    const float prob_b = exp2f((score_b - new_max) * kLog2e);
-    run_sum = run_sum * rescale + (prob_a + prob_b);
-    run_max = new_max;
+    if (__any_sync(0xFFFFFFFFU, step_max > run_max)) {
+      // some head's running maximum moved: rescale what has been accumulated (rare after the first steps)
+      const float new_max = fmaxf(run_max, step_max); // finite: the step holds at least one live token
+      const float rescale = exp2f((run_max - new_max) * kLog2e);
+      run_sum *= rescale;
+      run_max = new_max;
 #pragma unroll
-    for (int m = 0; m < 16; ++m) {
-      oacc[m][0] *= rescale;
-      oacc[m][1] *= rescale;
-      oacc[m][2] *= rescale;
-      oacc[m][3] *= rescale;
+      for (int m = 0; m < 16; ++m) {
+        oacc[m][0] *= rescale;
+        oacc[m][1] *= rescale;
+        oacc[m][2] *= rescale;
+        oacc[m][3] *= rescale;
+      }
     }
+    const float prob_a = exp2f((score_a - run_max) * kLog2e);
+    const float prob_b = exp2f((score_b - run_max) * kLog2e);
+    run_sum += prob_a + prob_b;
 
     // probabilities as the B operand of the value product: lane (g, t) needs column g = (head g>>1,
     // part g&1) for tokens 2t, 2t+1, 2t+8, 2t+9; lane (token, head) holds them after the softmax.
@@ -344,13 +397,19 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_partition_kernel(const 
     const std::uint32_t pb0 = pack_bf16(split_part(p0, part), split_part(p1, part));
     const std::uint32_t pb1 = pack_bf16(split_part(p2, part), split_part(p3, part));
 
-    // values: O[dim][column] += V[token][dim] * P[token][column]
+    // ---- V slot: O[dim][column] += V[token][dim] * P[token][column] ----
+    if (2 * i + kRingSlots < my_slots) {
+      issue(2 * i + kRingSlots);
+    }
+    cp_async_commit();
+    cp_async_wait<kRingSlots - 1>();
+    const std::uint32_t v_slot = ring + ((2 * i + 1) % kRingSlots) * kSlotBytes;
 #pragma unroll
     for (int s = 0; s < 4; ++s) {
-      const uint4 l0 = lds128(stage + 8192 + (4 * s + 0) * 512);
-      const uint4 l1 = lds128(stage + 8192 + (4 * s + 1) * 512);
-      const uint4 l2 = lds128(stage + 8192 + (4 * s + 2) * 512);
-      const uint4 l3 = lds128(stage + 8192 + (4 * s + 3) * 512);
+      const uint4 l0 = lds128(v_slot + (4 * s + 0) * 512);
+      const uint4 l1 = lds128(v_slot + (4 * s + 1) * 512);
+      const uint4 l2 = lds128(v_slot + (4 * s + 2) * 512);
+      const uint4 l3 = lds128(v_slot + (4 * s + 3) * 512);
       const std::uint32_t w0[4] = {l0.x, l0.y, l0.z, l0.w};
       const std::uint32_t w1[4] = {l1.x, l1.y, l1.z, l1.w};
       const std::uint32_t w2[4] = {l2.x, l2.y, l2.z, l2.w};
@@ -398,50 +457,53 @@ __global__ void __launch_bounds__(kWarps * 32, 1) decode_partition_kernel(const 
   }
   __syncthreads();
 
-  const int head_in_group = threadIdx.x >> 5;
-  const int dim0 = (threadIdx.x & 31) * 8;
-  float block_max = -INFINITY;
+  // 4 heads x 32 eight-dim pieces = 128 work items over the CTA's threads
+  for (int item = threadIdx.x; item < kGroup * 32; item += kWarps * 32) {
+    const int head_in_group = item >> 5;
+    const int dim0 = (item & 31) * 8;
+    float block_max = -INFINITY;
 #pragma unroll
-  for (int w = 0; w < kWarps; ++w) {
-    block_max = fmaxf(block_max, warp_max[w * kGroup + head_in_group]);
-  }
-  float block_sum = 0.0F;
-  float acc[8] = {0.0F, 0.0F, 0.0F, 0.0F, 0.0F, 0.0F, 0.0F, 0.0F};
-#pragma unroll
-  for (int w = 0; w < kWarps; ++w) {
-    const float weight = exp2f((warp_max[w * kGroup + head_in_group] - block_max) * kLog2e);
-    block_sum += warp_sum[w * kGroup + head_in_group] * weight;
-    const float *src = warp_out + (w * kGroup + head_in_group) * kHeadDim + dim0;
-    const float4 a = *reinterpret_cast<const float4 *>(src);
-    const float4 b = *reinterpret_cast<const float4 *>(src + 4);
-    acc[0] += a.x * weight; acc[1] += a.y * weight; acc[2] += a.z * weight; acc[3] += a.w * weight;
-    acc[4] += b.x * weight; acc[5] += b.y * weight; acc[6] += b.z * weight; acc[7] += b.w * weight;
-  }
-
-  const int head = kvh * kGroup + head_in_group;
-  if (direct) {
-    const std::size_t out_index = (act_seq * kQueryHeads + head) * kHeadDim + dim0;
-    float gate[8];
-    load8<F32>(p.gate, out_index, gate);
-    float result[8];
-#pragma unroll
-    for (int e = 0; e < 8; ++e) {
-      result[e] = (acc[e] / block_sum) / (1.0F + expf(-gate[e]));
+    for (int w = 0; w < kWarps; ++w) {
+      block_max = fmaxf(block_max, warp_max[w * kGroup + head_in_group]);
     }
-    store8<F32>(p.output, out_index, result);
-    return;
+    float block_sum = 0.0F;
+    float acc[8] = {0.0F, 0.0F, 0.0F, 0.0F, 0.0F, 0.0F, 0.0F, 0.0F};
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const float weight = exp2f((warp_max[w * kGroup + head_in_group] - block_max) * kLog2e);
+      block_sum += warp_sum[w * kGroup + head_in_group] * weight;
+      const float *src = warp_out + (w * kGroup + head_in_group) * kHeadDim + dim0;
+      const float4 a = *reinterpret_cast<const float4 *>(src);
+      const float4 b = *reinterpret_cast<const float4 *>(src + 4);
+      acc[0] += a.x * weight; acc[1] += a.y * weight; acc[2] += a.z * weight; acc[3] += a.w * weight;
+      acc[4] += b.x * weight; acc[5] += b.y * weight; acc[6] += b.z * weight; acc[7] += b.w * weight;
+    }
+
+    const int head = kvh * kGroup + head_in_group;
+    if (direct) {
+      const std::size_t out_index = (act_seq * kQueryHeads + head) * kHeadDim + dim0;
+      float gate[8];
+      load8<F32>(p.gate, out_index, gate);
+      float result[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        result[e] = (acc[e] / block_sum) / (1.0F + expf(-gate[e]));
+      }
+      store8<F32>(p.output, out_index, result);
+      continue;
+    }
+    const std::size_t partial = static_cast<std::size_t>(head) * p.max_partitions + blockIdx.x;
+    float *pmax = p.partial_max + act_seq * p.partial_stride;
+    float *psum = p.partial_sum + act_seq * p.partial_stride;
+    float *pval = p.partial_value + act_seq * p.partial_stride * kHeadDim;
+    if ((item & 31) == 0) {
+      pmax[partial] = block_max;
+      psum[partial] = block_sum;
+    }
+    float *dst = pval + partial * kHeadDim + dim0;
+    *reinterpret_cast<float4 *>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    *reinterpret_cast<float4 *>(dst + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
   }
-  const std::size_t partial = static_cast<std::size_t>(head) * p.max_partitions + blockIdx.x;
-  float *pmax = p.partial_max + act_seq * p.partial_stride;
-  float *psum = p.partial_sum + act_seq * p.partial_stride;
-  float *pval = p.partial_value + act_seq * p.partial_stride * kHeadDim;
-  if ((threadIdx.x & 31) == 0) {
-    pmax[partial] = block_max;
-    psum[partial] = block_sum;
-  }
-  float *dst = pval + partial * kHeadDim + dim0;
-  *reinterpret_cast<float4 *>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-  *reinterpret_cast<float4 *>(dst + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
 }
 
 // Combine kernel.  grid = (16 query heads, 4 dim quarters, sequences), 256 threads: sixteen partition
@@ -539,23 +601,28 @@ __global__ void __launch_bounds__(256) decode_combine_kernel(const DecodeParams 
   }
 }
 
-template <bool F32, bool Batched> void configure_once() {
+// CTA shape: two warps with three 8 KiB slots each (56 KiB with the merge area), four CTAs per SM.  Many
+// small CTAs keep enough warps resident to hide the latency of each warp's dependent chain, and one CTA's
+// start-up and epilogue hide behind the others' streaming.
+using DecodeTile = Tile<2, 3>;
+
+template <bool F32, bool Batched, class T> void configure_once() {
   static std::once_flag flags[64];
   int device = 0;
   cuda_ok(cudaGetDevice(&device), "cudaGetDevice");
   require(device >= 0 && device < 64, "device ordinal out of range", RIB200_STATUS_INTERNAL);
   std::call_once(flags[device], [] {
-    cuda_ok(cudaFuncSetAttribute(decode_partition_kernel<F32, Batched>,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes),
+    cuda_ok(cudaFuncSetAttribute(decode_partition_kernel<F32, Batched, T>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes),
             "decode attention shared-memory opt-in");
   });
 }
 
-template <bool F32, bool Batched>
-void launch_pair(const DecodeParams &params, dim3 partition_grid, dim3 combine_grid, bool combine,
-                 cudaStream_t stream) {
-  configure_once<F32, Batched>();
-  decode_partition_kernel<F32, Batched><<<partition_grid, kWarps * 32, kSmemBytes, stream>>>(params);
+template <bool F32, bool Batched, class T>
+void launch_pair_tiled(const DecodeParams &params, dim3 partition_grid, dim3 combine_grid, bool combine,
+                       cudaStream_t stream) {
+  configure_once<F32, Batched, T>();
+  decode_partition_kernel<F32, Batched, T><<<partition_grid, T::kWarps * 32, T::kSmemBytes, stream>>>(params);
   cuda_ok(cudaGetLastError(), "decode attention partition launch");
   if (!combine) {
     return;
@@ -572,6 +639,42 @@ void launch_pair(const DecodeParams &params, dim3 partition_grid, dim3 combine_g
   config.numAttrs = 1;
   cuda_ok(cudaLaunchKernelEx(&config, decode_combine_kernel<F32, Batched>, params),
           "decode attention combine launch");
+}
+
+// RIB200_DECODE_TILE=<warps><slots> (e.g. 43) picks another CTA shape; a tuning aid, not an interface.
+int tuning_tile() {
+  static const int choice = [] {
+    const char *env = std::getenv("RIB200_DECODE_TILE");
+    return env != nullptr ? std::atoi(env) : 0;
+  }();
+  return choice;
+}
+
+template <bool F32, bool Batched>
+void launch_pair(const DecodeParams &params, dim3 partition_grid, dim3 combine_grid, bool combine,
+                 cudaStream_t stream) {
+  switch (tuning_tile()) {
+  case 24:
+    launch_pair_tiled<F32, Batched, Tile<2, 4>>(params, partition_grid, combine_grid, combine, stream);
+    return;
+  case 26:
+    launch_pair_tiled<F32, Batched, Tile<2, 6>>(params, partition_grid, combine_grid, combine, stream);
+    return;
+  case 43:
+    launch_pair_tiled<F32, Batched, Tile<4, 3>>(params, partition_grid, combine_grid, combine, stream);
+    return;
+  case 44:
+    launch_pair_tiled<F32, Batched, Tile<4, 4>>(params, partition_grid, combine_grid, combine, stream);
+    return;
+  case 13:
+    launch_pair_tiled<F32, Batched, Tile<1, 3>>(params, partition_grid, combine_grid, combine, stream);
+    return;
+  case 83:
+    launch_pair_tiled<F32, Batched, Tile<8, 3>>(params, partition_grid, combine_grid, combine, stream);
+    return;
+  default:
+    launch_pair_tiled<F32, Batched, DecodeTile>(params, partition_grid, combine_grid, combine, stream);
+  }
 }
 
 } // namespace
