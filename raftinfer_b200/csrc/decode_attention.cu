@@ -9,16 +9,21 @@
 //
 // Bandwidth plan.  One CTA serves one (partition, KV head) and all four query heads of the group, so
 // every K and V byte is read from HBM once (the reference streams each KV head four times).  Each warp
-// owns 16-token steps of the partition and keeps three of them (16 KiB each) in flight through a private
-// cp.async ring in shared memory: a lane copies exactly the 16-byte pieces it will later consume as
-// tensor-core fragments, so the ring needs no barrier and no swizzle and reads back conflict-free.
-// 4 warps x 3 stages x 16 KiB = 192 KiB in flight per SM.
+// owns 16-token steps of the partition.  Lane 0 of the warp is its producer: it moves the 512-byte K (or V)
+// rows of a step from the cache into a private ring of shared-memory slots with TMA bulk copies
+// (cp.async.bulk, completion counted on an mbarrier), several slots ahead of the consumer.  Rows sit at a
+// 528-byte pitch, which makes every ldmatrix of eight rows hit eight different bank groups.  Because ring,
+// barriers and producer are private to the warp, no block-level barrier is needed while streaming.
 //
 // Arithmetic plan.  Tokens are the M dimension of mma.sync.m16n8k16 (BF16 in, FP32 accumulate) and the
 // eight N columns carry the four query heads twice: column 2h holds the BF16 high part and column 2h+1
 // the BF16 residual of head h, for q in the score product and for the probabilities in the value
 // product.  Both products therefore see ~16 mantissa bits although the tensor cores run in BF16, at no
-// extra cost (N = 8 is the minimum tile).  Softmax runs in FP32 with exp2f.
+// extra cost (N = 8 is the minimum tile).  Softmax runs in FP32 with exp2f; accumulators are rescaled only
+// when a running maximum moves.
+//
+// Every wait on an mbarrier is bounded: when it runs out the warp records RIB200_DEVICE_WAIT_TIMED_OUT in
+// the device status word and leaves the streaming loop.
 
 #include "common.hpp"
 
@@ -37,15 +42,22 @@ constexpr int kQueryHeads = 16;
 constexpr int kKvHeads = 4;
 constexpr int kGroup = kQueryHeads / kKvHeads;
 constexpr int kStepTokens = 16;
-constexpr int kSlotBytes = kStepTokens * kHeadDim * 2; // the K rows or the V rows of one step: 8 KiB
+constexpr int kRowBytes = kHeadDim * 2;                // one cached K or V row
+constexpr int kRowPitch = kRowBytes + 16;              // shared-memory pitch of a row (bank-conflict-free ldmatrix)
+constexpr int kSlotBytes = kStepTokens * kRowPitch;    // the K rows or the V rows of one step
+constexpr int kMergePitch = kHeadDim + 8;              // floats per (warp, head) row of the merge area
+constexpr long long kWaitLimitCycles = 1LL << 28;      // SM cycles an mbarrier wait may take before giving up
 
-// Shape of one CTA: `Warps` warps, each with a private ring of `Slots` 8 KiB slots (K and V slots alternate).
+// Shape of one CTA: `Warps` warps, each with a private ring of `Slots` slots (K and V slots alternate).
 template <int Warps, int Slots> struct Tile {
   static constexpr int kWarps = Warps;
   static constexpr int kRingSlots = Slots;
   static constexpr int kRingBytes = Warps * Slots * kSlotBytes;
-  static constexpr int kMergeFloats = Warps * (kGroup * kHeadDim + 2 * kGroup);
-  static constexpr int kSmemBytes = kRingBytes + kMergeFloats * 4;
+  static constexpr int kBarrierBytes = (Warps * Slots * 8 + 15) / 16 * 16;
+  // the cross-warp merge area reuses the ring once streaming is over
+  static constexpr int kMergeFloats = Warps * (kGroup * kMergePitch + 2 * kGroup);
+  static_assert(kMergeFloats * 4 <= kRingBytes, "merge area must fit in the ring");
+  static constexpr int kSmemBytes = kRingBytes + kBarrierBytes;
   static constexpr int kCtasPerSm = (227 * 1024) / (kSmemBytes + 1024) > 0 ? (227 * 1024) / (kSmemBytes + 1024) : 1;
 };
 constexpr float kLog2e = 1.4426950408889634F;
@@ -77,25 +89,49 @@ __device__ __forceinline__ std::uint32_t smem_address(const void *p) {
   return static_cast<std::uint32_t>(__cvta_generic_to_shared(p));
 }
 
-__device__ __forceinline__ void cp_async_16(std::uint32_t dst, const void *src, bool valid) {
-  const int bytes = valid ? 16 : 0; // 0 source bytes: the 16 destination bytes are zero-filled
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+__device__ __forceinline__ void mbarrier_init(std::uint32_t bar, std::uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
 }
 
-__device__ __forceinline__ void cp_async_16_full(std::uint32_t dst, const void *src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+__device__ __forceinline__ void mbarrier_expect_tx(std::uint32_t bar, std::uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
 }
 
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-
-template <int N> __device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+__device__ __forceinline__ bool mbarrier_try_wait(std::uint32_t bar, std::uint32_t parity) {
+  std::uint32_t done;
+  asm volatile("{\n"
+               ".reg .pred p;\n"
+               "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+               "selp.u32 %0, 1, 0, p;\n"
+               "}\n"
+               : "=r"(done)
+               : "r"(bar), "r"(parity)
+               : "memory");
+  return done != 0;
 }
 
-__device__ __forceinline__ uint4 lds128(std::uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-  return v;
+// TMA bulk copy global -> shared, completion bytes counted on `bar`
+__device__ __forceinline__ void bulk_copy_g2s(std::uint32_t dst, const void *src, std::uint32_t bytes,
+                                              std::uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(std::uint32_t addr, std::uint32_t &r0, std::uint32_t &r1,
+                                            std::uint32_t &r2, std::uint32_t &r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(std::uint32_t addr, std::uint32_t &r0, std::uint32_t &r1,
+                                                  std::uint32_t &r2, std::uint32_t &r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
 }
 
 __device__ __forceinline__ void sts128(std::uint32_t addr, uint4 v) {
@@ -217,78 +253,78 @@ __global__ void __launch_bounds__(T::kWarps * 32, T::kCtasPerSm) decode_partitio
   const std::uint32_t my_steps =
       total_steps > static_cast<std::uint32_t>(warp) ? (total_steps - warp + kWarps - 1) / kWarps : 0;
   const std::uint32_t my_slots = 2 * my_steps; // slot 2i = K rows of step i, slot 2i+1 = V rows of step i
-  const std::uint32_t ring = smem_address(smem) + warp * kRingSlots * kSlotBytes + lane * 16;
+  const std::uint32_t ring = smem_address(smem) + warp * kRingSlots * kSlotBytes;
+  const std::uint32_t bars = smem_address(smem) + kRingBytes + warp * kRingSlots * 8;
 
-  // Copies slot `n` of this warp into ring position n % kRingSlots.  Steps that lie wholly inside the live
-  // range and do not hold the token being appended take the branch-free path (constant offsets from one base
-  // pointer).  The row being appended is not in the cache yet: its owner lane converts it from the key/value
-  // inputs, feeds the ring and writes the cache row.  Rows past the range are zero-filled.
+  if (lane == 0) {
+#pragma unroll
+    for (int r = 0; r < kRingSlots; ++r) {
+      mbarrier_init(bars + r * 8, 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  __syncwarp();
+
+  // Producer (lane 0): slot n goes to ring position n % kRingSlots.  Only the live rows of the step are
+  // copied; the consumer zero-fills the rest and patches in the row that is being appended.
   auto issue = [&](std::uint32_t n) {
+    if (lane != 0) {
+      return;
+    }
     const std::uint32_t tok0 = begin + (warp + (n >> 1) * kWarps) * kStepTokens;
+    const std::uint32_t rows = min(static_cast<std::uint32_t>(kStepTokens), end - tok0);
     const std::uint32_t slot = ring + (n % kRingSlots) * kSlotBytes;
-    const bool plain = tok0 + kStepTokens <= end && !(pos >= tok0 && pos < tok0 + kStepTokens);
-    if ((n & 1U) == 0) {
-      if (plain) {
-        const __nv_bfloat16 *src = k_plane + static_cast<std::size_t>(tok0 + g) * kHeadDim + 8 * t;
+    const std::uint32_t bar = bars + (n % kRingSlots) * 8;
+    const __nv_bfloat16 *src = ((n & 1U) == 0 ? k_plane : v_plane) + static_cast<std::size_t>(tok0) * kHeadDim;
+    fence_proxy_async(); // earlier reads of this ring position are ordered before the TMA write
+    mbarrier_expect_tx(bar, rows * kRowBytes);
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            cp_async_16_full(slot + (2 * j + r) * 512, src + r * 8 * kHeadDim + 32 * j);
-          }
-        }
-        return;
+    for (int r = 0; r < kStepTokens; ++r) {
+      if (static_cast<std::uint32_t>(r) < rows) {
+        bulk_copy_g2s(slot + r * kRowPitch, src + r * kHeadDim, kRowBytes, bar);
       }
-#pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        const std::uint32_t tok = tok0 + g + 8 * r;
-        const bool valid = tok < end;
-        const std::size_t row = static_cast<std::size_t>(valid ? tok : end - 1) * kHeadDim;
-        if (tok == pos) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const uint4 raw = load8_as_bf16<F32>(p.key, kv_in_base + 32 * j + 8 * t);
-            sts128(slot + (2 * j + r) * 512, raw);
-            *reinterpret_cast<uint4 *>(k_plane + row + 32 * j + 8 * t) = raw;
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            cp_async_16(slot + (2 * j + r) * 512, k_plane + row + 32 * j + 8 * t, valid);
-          }
-        }
-      }
-      return;
     }
-    if (plain) {
-      const __nv_bfloat16 *src = v_plane + static_cast<std::size_t>(tok0 + 2 * t) * kHeadDim + 8 * g;
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-#pragma unroll
-        for (int s = 0; s < 4; ++s) {
-          cp_async_16_full(slot + (4 * s + q) * 512, src + ((q & 1) + 8 * (q >> 1)) * kHeadDim + 64 * s);
+  };
+
+  // Consumer side of slot n.  Returns false when the wait ran out.
+  bool healthy = true;
+  auto wait_slot = [&](std::uint32_t n) {
+    const std::uint32_t bar = bars + (n % kRingSlots) * 8;
+    const std::uint32_t parity = (n / kRingSlots) & 1U;
+    if (!mbarrier_try_wait(bar, parity)) {
+      const long long started = clock64();
+      while (!mbarrier_try_wait(bar, parity)) {
+        if (clock64() - started > kWaitLimitCycles) {
+          healthy = false;
+          break;
         }
       }
-      return;
     }
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const std::uint32_t tok = tok0 + 2 * t + (q & 1) + 8 * (q >> 1);
-      const bool valid = tok < end;
-      const std::size_t row = static_cast<std::size_t>(valid ? tok : end - 1) * kHeadDim;
-      if (tok == pos) {
-#pragma unroll
-        for (int s = 0; s < 4; ++s) {
-          const uint4 raw = load8_as_bf16<F32>(p.value, kv_in_base + 8 * (8 * s + g));
-          sts128(slot + (4 * s + q) * 512, raw);
-          *reinterpret_cast<uint4 *>(v_plane + row + 8 * (8 * s + g)) = raw;
-        }
-      } else {
-#pragma unroll
-        for (int s = 0; s < 4; ++s) {
-          cp_async_16(slot + (4 * s + q) * 512, v_plane + row + 8 * (8 * s + g), valid);
-        }
+    healthy = __all_sync(0xFFFFFFFFU, healthy);
+    return healthy;
+  };
+
+  // After the copy has landed: patch in the row being appended (it is not in the cache yet; its bytes come
+  // from the key/value input and also go to the cache) and zero the rows past the live range.
+  auto fix_rows = [&](std::uint32_t n, std::uint32_t tok0) {
+    const std::uint32_t slot = ring + (n % kRingSlots) * kSlotBytes;
+    const bool is_value = (n & 1U) != 0;
+    bool touched = false;
+    if (pos >= tok0 && pos < tok0 + kStepTokens && pos < end) {
+      const uint4 raw = load8_as_bf16<F32>(is_value ? p.value : p.key, kv_in_base + 8 * lane);
+      sts128(slot + (pos - tok0) * kRowPitch + lane * 16, raw);
+      __nv_bfloat16 *plane = is_value ? v_plane : k_plane;
+      *reinterpret_cast<uint4 *>(plane + static_cast<std::size_t>(pos) * kHeadDim + 8 * lane) = raw;
+      touched = true;
+    }
+    if (tok0 + kStepTokens > end) {
+      for (std::uint32_t r = end - tok0; r < kStepTokens; ++r) {
+        sts128(slot + r * kRowPitch + lane * 16, make_uint4(0U, 0U, 0U, 0U));
       }
+      touched = true;
+    }
+    if (touched) {
+      __syncwarp();
     }
   };
 
@@ -298,26 +334,44 @@ __global__ void __launch_bounds__(T::kWarps * 32, T::kCtasPerSm) decode_partitio
     if (static_cast<std::uint32_t>(n) < my_slots) {
       issue(n);
     }
-    cp_async_commit();
   }
 
-  // Query fragments (the B operand of the score product): lane (g, t) holds, for every 32-dim block j,
-  // dims 32j + 8t .. +8 of N column g = (head g>>1, split part g&1), pre-scaled by 1/sqrt(256).
+  // Query fragments (the B operand of the score product): lane (g, t) holds, for k-step ks, dims
+  // 16ks + 2t, +1 and 16ks + 8 + 2t, +1 of N column g = (head g>>1, split part g&1), pre-scaled by
+  // 1/sqrt(256).
   std::uint32_t qf[32];
   {
     const int head = kvh * kGroup + (g >> 1);
     const int part = g & 1;
     const std::size_t q_base = (act_seq * kQueryHeads + head) * kHeadDim;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      float v[8];
-      load8<F32>(p.query, q_base + 32 * j + 8 * t, v);
+    for (int ks = 0; ks < 16; ++ks) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        qf[4 * j + e] = pack_bf16(split_part(v[2 * e] * 0.0625F, part), split_part(v[2 * e + 1] * 0.0625F, part));
+      for (int half = 0; half < 2; ++half) {
+        const std::size_t index = q_base + 16 * ks + 8 * half + 2 * t;
+        float x0;
+        float x1;
+        if constexpr (F32) {
+          const float2 v = *reinterpret_cast<const float2 *>(static_cast<const float *>(p.query) + index);
+          x0 = v.x;
+          x1 = v.y;
+        } else {
+          const std::uint32_t raw =
+              *reinterpret_cast<const std::uint32_t *>(static_cast<const __nv_bfloat16 *>(p.query) + index);
+          x0 = __uint_as_float(raw << 16);
+          x1 = __uint_as_float(raw & 0xFFFF0000U);
+        }
+        qf[2 * ks + half] = pack_bf16(split_part(x0 * 0.0625F, part), split_part(x1 * 0.0625F, part));
       }
     }
   }
+
+  // ldmatrix lane addressing.  K (A operand, tokens x dims): matrix mi = lane>>3 covers token rows
+  // (mi&1)*8.., 16-byte chunk (mi>>1) of the k-step.  V (A operand transposed, dims x tokens): matrix mi
+  // covers token rows (mi>>1)*8.., chunk (mi&1) of the 16-dim tile.
+  const int mi = lane >> 3;
+  const std::uint32_t k_lane = ((lane & 7) + 8 * (mi & 1)) * kRowPitch + (mi >> 1) * 16;
+  const std::uint32_t v_lane = ((lane & 7) + 8 * (mi >> 1)) * kRowPitch + (mi & 1) * 16;
 
   float oacc[16][4];
 #pragma unroll
@@ -331,12 +385,16 @@ __global__ void __launch_bounds__(T::kWarps * 32, T::kCtasPerSm) decode_partitio
     const std::uint32_t tok0 = begin + (warp + i * kWarps) * kStepTokens;
 
     // ---- K slot: scores and softmax ----
+    fence_proxy_async();
+    __syncwarp(); // all lanes are done with the ring position that is refilled next
     if (2 * i + kRingSlots - 1 < my_slots) {
       issue(2 * i + kRingSlots - 1);
     }
-    cp_async_commit();
-    cp_async_wait<kRingSlots - 1>();
-    const std::uint32_t k_slot = ring + ((2 * i) % kRingSlots) * kSlotBytes;
+    if (!wait_slot(2 * i)) {
+      break;
+    }
+    fix_rows(2 * i, tok0);
+    const std::uint32_t k_slot = ring + ((2 * i) % kRingSlots) * kSlotBytes + k_lane;
 
     // S[token][column] = K[token][:] . Q[column][:], four independent accumulator chains
     float s0[4] = {0.0F, 0.0F, 0.0F, 0.0F};
@@ -344,15 +402,16 @@ __global__ void __launch_bounds__(T::kWarps * 32, T::kCtasPerSm) decode_partitio
     float s2[4] = {0.0F, 0.0F, 0.0F, 0.0F};
     float s3[4] = {0.0F, 0.0F, 0.0F, 0.0F};
 #pragma unroll
-    for (int j = 0; j < 8; j += 2) {
-      const uint4 ka = lds128(k_slot + (2 * j) * 512);
-      const uint4 kb = lds128(k_slot + (2 * j + 1) * 512);
-      const uint4 kc = lds128(k_slot + (2 * j + 2) * 512);
-      const uint4 kd = lds128(k_slot + (2 * j + 3) * 512);
-      mma_bf16(s0, ka.x, kb.x, ka.y, kb.y, qf[4 * j + 0], qf[4 * j + 1]);
-      mma_bf16(s1, ka.z, kb.z, ka.w, kb.w, qf[4 * j + 2], qf[4 * j + 3]);
-      mma_bf16(s2, kc.x, kd.x, kc.y, kd.y, qf[4 * j + 4], qf[4 * j + 5]);
-      mma_bf16(s3, kc.z, kd.z, kc.w, kd.w, qf[4 * j + 6], qf[4 * j + 7]);
+    for (int ks = 0; ks < 16; ks += 4) {
+      std::uint32_t a[4][4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        ldmatrix_x4(k_slot + (ks + u) * 32, a[u][0], a[u][1], a[u][2], a[u][3]);
+      }
+      mma_bf16(s0, a[0][0], a[0][1], a[0][2], a[0][3], qf[2 * ks + 0], qf[2 * ks + 1]);
+      mma_bf16(s1, a[1][0], a[1][1], a[1][2], a[1][3], qf[2 * ks + 2], qf[2 * ks + 3]);
+      mma_bf16(s2, a[2][0], a[2][1], a[2][2], a[2][3], qf[2 * ks + 4], qf[2 * ks + 5]);
+      mma_bf16(s3, a[3][0], a[3][1], a[3][2], a[3][3], qf[2 * ks + 6], qf[2 * ks + 7]);
     }
     // lane (g, t): head t, tokens tok0 + g and tok0 + g + 8 (high part + residual columns)
     float score_a = ((s0[0] + s1[0]) + (s2[0] + s3[0])) + ((s0[1] + s1[1]) + (s2[1] + s3[1]));
@@ -398,62 +457,53 @@ __global__ void __launch_bounds__(T::kWarps * 32, T::kCtasPerSm) decode_partitio
     const std::uint32_t pb1 = pack_bf16(split_part(p2, part), split_part(p3, part));
 
     // ---- V slot: O[dim][column] += V[token][dim] * P[token][column] ----
+    fence_proxy_async();
+    __syncwarp();
     if (2 * i + kRingSlots < my_slots) {
       issue(2 * i + kRingSlots);
     }
-    cp_async_commit();
-    cp_async_wait<kRingSlots - 1>();
-    const std::uint32_t v_slot = ring + ((2 * i + 1) % kRingSlots) * kSlotBytes;
+    if (!wait_slot(2 * i + 1)) {
+      break;
+    }
+    fix_rows(2 * i + 1, tok0);
+    const std::uint32_t v_slot = ring + ((2 * i + 1) % kRingSlots) * kSlotBytes + v_lane;
 #pragma unroll
-    for (int s = 0; s < 4; ++s) {
-      const uint4 l0 = lds128(v_slot + (4 * s + 0) * 512);
-      const uint4 l1 = lds128(v_slot + (4 * s + 1) * 512);
-      const uint4 l2 = lds128(v_slot + (4 * s + 2) * 512);
-      const uint4 l3 = lds128(v_slot + (4 * s + 3) * 512);
-      const std::uint32_t w0[4] = {l0.x, l0.y, l0.z, l0.w};
-      const std::uint32_t w1[4] = {l1.x, l1.y, l1.z, l1.w};
-      const std::uint32_t w2[4] = {l2.x, l2.y, l2.z, l2.w};
-      const std::uint32_t w3[4] = {l3.x, l3.y, l3.z, l3.w};
+    for (int mt = 0; mt < 16; mt += 4) {
+      std::uint32_t a[4][4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const std::uint32_t a0 = __byte_perm(w0[e], w1[e], 0x5410);
-        const std::uint32_t a1 = __byte_perm(w0[e], w1[e], 0x7632);
-        const std::uint32_t a2 = __byte_perm(w2[e], w3[e], 0x5410);
-        const std::uint32_t a3 = __byte_perm(w2[e], w3[e], 0x7632);
-        mma_bf16(oacc[4 * s + e], a0, a1, a2, a3, pb0, pb1);
+      for (int u = 0; u < 4; ++u) {
+        ldmatrix_x4_trans(v_slot + (mt + u) * 32, a[u][0], a[u][1], a[u][2], a[u][3]);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        mma_bf16(oacc[mt + u], a[u][0], a[u][1], a[u][2], a[u][3], pb0, pb1);
       }
     }
   }
-  cp_async_wait<0>();
+  if (!healthy && lane == 0) {
+    atomicOr(p.status, static_cast<unsigned int>(RIB200_DEVICE_WAIT_TIMED_OUT));
+  }
 
   run_sum += __shfl_xor_sync(0xFFFFFFFFU, run_sum, 4);
   run_sum += __shfl_xor_sync(0xFFFFFFFFU, run_sum, 8);
   run_sum += __shfl_xor_sync(0xFFFFFFFFU, run_sum, 16);
 
-  // cross-warp combine through shared memory
-  float *merge = reinterpret_cast<float *>(smem + kRingBytes);
+  // cross-warp combine through shared memory.  Lane (g, t) holds, for head t and every 16-dim tile mt,
+  // dims 16mt + g and 16mt + g + 8 (high-part column + residual column).
+  __syncthreads(); // every warp has left its ring: the merge area may now overwrite it
+  float *merge = reinterpret_cast<float *>(smem);
   float *warp_max = merge;                       // [kWarps][4]
   float *warp_sum = merge + kWarps * kGroup;     // [kWarps][4]
-  float *warp_out = merge + 2 * kWarps * kGroup; // [kWarps][4][256]
+  float *warp_out = merge + 2 * kWarps * kGroup; // [kWarps][4][kMergePitch]
   if (g == 0) {
     warp_max[warp * kGroup + t] = run_max;
     warp_sum[warp * kGroup + t] = run_sum;
   }
 #pragma unroll
-  for (int s = 0; s < 4; ++s) {
-    float *dst = warp_out + (warp * kGroup + t) * kHeadDim + 8 * (8 * s + g);
-    float4 lo;
-    float4 hi;
-    lo.x = oacc[4 * s + 0][0] + oacc[4 * s + 0][1];
-    lo.y = oacc[4 * s + 0][2] + oacc[4 * s + 0][3];
-    lo.z = oacc[4 * s + 1][0] + oacc[4 * s + 1][1];
-    lo.w = oacc[4 * s + 1][2] + oacc[4 * s + 1][3];
-    hi.x = oacc[4 * s + 2][0] + oacc[4 * s + 2][1];
-    hi.y = oacc[4 * s + 2][2] + oacc[4 * s + 2][3];
-    hi.z = oacc[4 * s + 3][0] + oacc[4 * s + 3][1];
-    hi.w = oacc[4 * s + 3][2] + oacc[4 * s + 3][3];
-    *reinterpret_cast<float4 *>(dst) = lo;
-    *reinterpret_cast<float4 *>(dst + 4) = hi;
+  for (int mt = 0; mt < 16; ++mt) {
+    float *dst = warp_out + (warp * kGroup + t) * kMergePitch + 16 * mt + g;
+    dst[0] = oacc[mt][0] + oacc[mt][1];
+    dst[8] = oacc[mt][2] + oacc[mt][3];
   }
   __syncthreads();
 
@@ -472,7 +522,7 @@ __global__ void __launch_bounds__(T::kWarps * 32, T::kCtasPerSm) decode_partitio
     for (int w = 0; w < kWarps; ++w) {
       const float weight = exp2f((warp_max[w * kGroup + head_in_group] - block_max) * kLog2e);
       block_sum += warp_sum[w * kGroup + head_in_group] * weight;
-      const float *src = warp_out + (w * kGroup + head_in_group) * kHeadDim + dim0;
+      const float *src = warp_out + (w * kGroup + head_in_group) * kMergePitch + dim0;
       const float4 a = *reinterpret_cast<const float4 *>(src);
       const float4 b = *reinterpret_cast<const float4 *>(src + 4);
       acc[0] += a.x * weight; acc[1] += a.y * weight; acc[2] += a.z * weight; acc[3] += a.w * weight;
@@ -601,11 +651,10 @@ __global__ void __launch_bounds__(256) decode_combine_kernel(const DecodeParams 
   }
 }
 
-// CTA shape: two warps with three 8 KiB slots each (56 KiB with the merge area), four CTAs per SM.  Many
-// small CTAs keep enough warps resident to hide the latency of each warp's dependent chain, and one CTA's
-// start-up and epilogue hide behind the others' streaming.
-using DecodeTile = Tile<2, 3>;
-
+// CTA shapes.  Shared memory bounds the bytes in flight per SM (the rings fill it either way), so the shape
+// only decides how the partitions spread over the machine: with many partitions a CTA is a single warp (no
+// cross-warp merge, most CTAs resident); with few, more warps share a partition so that every SM has work and
+// each warp's chain of dependent steps is short.  All shapes are the same kernel template.
 template <bool F32, bool Batched, class T> void configure_once() {
   static std::once_flag flags[64];
   int device = 0;
@@ -654,26 +703,45 @@ template <bool F32, bool Batched>
 void launch_pair(const DecodeParams &params, dim3 partition_grid, dim3 combine_grid, bool combine,
                  cudaStream_t stream) {
   switch (tuning_tile()) {
+  case 13:
+    launch_pair_tiled<F32, Batched, Tile<1, 3>>(params, partition_grid, combine_grid, combine, stream);
+    return;
+  case 14:
+    launch_pair_tiled<F32, Batched, Tile<1, 4>>(params, partition_grid, combine_grid, combine, stream);
+    return;
+  case 16:
+    launch_pair_tiled<F32, Batched, Tile<1, 6>>(params, partition_grid, combine_grid, combine, stream);
+    return;
+  case 23:
+    launch_pair_tiled<F32, Batched, Tile<2, 3>>(params, partition_grid, combine_grid, combine, stream);
+    return;
   case 24:
     launch_pair_tiled<F32, Batched, Tile<2, 4>>(params, partition_grid, combine_grid, combine, stream);
     return;
-  case 26:
-    launch_pair_tiled<F32, Batched, Tile<2, 6>>(params, partition_grid, combine_grid, combine, stream);
+  case 42:
+    launch_pair_tiled<F32, Batched, Tile<4, 2>>(params, partition_grid, combine_grid, combine, stream);
     return;
   case 43:
     launch_pair_tiled<F32, Batched, Tile<4, 3>>(params, partition_grid, combine_grid, combine, stream);
     return;
-  case 44:
-    launch_pair_tiled<F32, Batched, Tile<4, 4>>(params, partition_grid, combine_grid, combine, stream);
-    return;
-  case 13:
-    launch_pair_tiled<F32, Batched, Tile<1, 3>>(params, partition_grid, combine_grid, combine, stream);
+  case 82:
+    launch_pair_tiled<F32, Batched, Tile<8, 2>>(params, partition_grid, combine_grid, combine, stream);
     return;
   case 83:
     launch_pair_tiled<F32, Batched, Tile<8, 3>>(params, partition_grid, combine_grid, combine, stream);
     return;
   default:
-    launch_pair_tiled<F32, Batched, DecodeTile>(params, partition_grid, combine_grid, combine, stream);
+    break;
+  }
+  const std::size_t ctas = static_cast<std::size_t>(partition_grid.x) * partition_grid.y * partition_grid.z;
+  if (ctas <= 148) {
+    launch_pair_tiled<F32, Batched, Tile<8, 3>>(params, partition_grid, combine_grid, combine, stream);
+  } else if (ctas <= 296) {
+    launch_pair_tiled<F32, Batched, Tile<4, 3>>(params, partition_grid, combine_grid, combine, stream);
+  } else if (ctas <= 592) {
+    launch_pair_tiled<F32, Batched, Tile<2, 3>>(params, partition_grid, combine_grid, combine, stream);
+  } else {
+    launch_pair_tiled<F32, Batched, Tile<1, 3>>(params, partition_grid, combine_grid, combine, stream);
   }
 }
 

@@ -1,6 +1,705 @@
+// Causal GQA prefill attention with online softmax and a sigmoid output gate, for 16 query heads / 4 KV heads /
+// head_dim 256, BF16 head-major KV cache (replaces cpp/kernels/qwen35_online_attention.cu:296-322 append and
+// :499-600 prefill; CPU form cpp/reference/qwen35.cpp:316-370).
+//
+// Two launches: a small append kernel writes this chunk's K and V rows into the cache (BF16, nearest even, as
+// the reference's append does), then the attention kernel reads every key and value - past and new - from the
+// cache, which is exactly what the reference's prefill kernel sees.  The second launch uses programmatic
+// dependent launch so that its set-up overlaps the append.
+//
+// Attention kernel (one CTA per 128 query rows of one head, 192 threads):
+//   warp 4   producer.  TMA tiled loads with the 128-byte swizzle: the Q tile once (64 KiB), then K and V in
+//            half blocks of 64 keys (32 KiB each) through a ring of four slots.  The tensor maps end at the
+//            live context, so rows the cache has never held arrive as zeros.
+//   warp 5   issues tcgen05.mma (BF16 in, FP32 accumulate in tensor memory).  Tensor memory holds the output
+//            tile O (128 lanes x 256 columns) and two score tiles S (128 x 128 each): 512 columns in all.
+//            S = Q K^T takes both operands from shared memory (K-major); O += P V takes P from tensor memory
+//            (written over the S tile it came from, as BF16) and V from shared memory (dim-major).
+//            The issue order QK(j+1), PV(j) keeps the tensor pipe busy while the softmax of block j runs.
+//   warps 0-3 softmax: one thread per query row (tensor-memory lane), FP32, exp2f.  The running maximum used
+//            for the exponentials only moves when it falls more than 8 (base-2) behind, at which point the
+//            thread rescales its row of O in tensor memory; this is rare after the first blocks.  The same
+//            threads normalise, gate and store the tile at the end.
+//
+// Work per launch: 4 * 16 * 256 * (T * P + T (T + 1) / 2) flops for T new tokens after P past tokens.
+// Every wait on an mbarrier is bounded; when one runs out the CTA records RIB200_DEVICE_WAIT_TIMED_OUT, all
+// roles leave their loops, tensor memory is released and the kernel returns.
+
 #include "common.hpp"
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <mutex>
+
 namespace rib200 {
-void launch_prefill_attention(const PrefillArgs &, cudaStream_t) {
-  unsupported(false, "prefill attention kernel is not built yet");
+namespace {
+
+constexpr int kHeadDim = 256;
+constexpr int kQueryHeads = 16;
+constexpr int kKvHeads = 4;
+constexpr int kGroup = kQueryHeads / kKvHeads;
+constexpr int kTileRows = 128;  // query rows per CTA
+constexpr int kBlockKeys = 128; // keys per score tile
+constexpr int kHalfKeys = 64;   // keys per ring slot
+constexpr int kSlots = 4;
+constexpr int kBoxCols = 64;                              // 64 BF16 = one 128-byte swizzle row
+constexpr int kQBoxBytes = kTileRows * 128;               // 16 KiB
+constexpr int kQBytes = 4 * kQBoxBytes;                   // 64 KiB
+constexpr int kSlotBoxBytes = kHalfKeys * 128;            // 8 KiB
+constexpr int kSlotBytes = 4 * kSlotBoxBytes;             // 32 KiB
+constexpr int kRingOffset = kQBytes;
+constexpr int kBarrierOffset = kRingOffset + kSlots * kSlotBytes;
+constexpr int kSmemBytes = kBarrierOffset + 256 + 1024;   // + barriers + slack to align the base to 1 KiB
+constexpr int kThreads = 192;
+constexpr long long kWaitLimitCycles = 1LL << 30;
+constexpr float kScaleLog2e = 0.0625F * 1.4426950408889634F; // (1 / sqrt(256)) * log2(e)
+constexpr float kRescaleThreshold = 8.0F;
+
+// barrier indices (8 bytes each) inside the barrier block
+enum : int {
+  kBarQFull = 0,
+  kBarFull = 1,             // kSlots
+  kBarEmpty = 1 + kSlots,   // kSlots
+  kBarSFull = 1 + 2 * kSlots,  // 2
+  kBarPFull = 3 + 2 * kSlots,  // 2
+  kBarPvDone = 5 + 2 * kSlots, // 2
+  kBarCount = 7 + 2 * kSlots
+};
+
+struct PrefillParams {
+  const void *gate;
+  void *output;
+  std::uint32_t tokens;
+  std::uint32_t past;
+  std::uint32_t tiles;
+  unsigned int *status;
+};
+
+__device__ __forceinline__ std::uint32_t smem_u32(const void *p) {
+  return static_cast<std::uint32_t>(__cvta_generic_to_shared(p));
 }
+
+__device__ __forceinline__ void mbar_init(std::uint32_t bar, std::uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(std::uint32_t bar, std::uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(std::uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(std::uint32_t bar, std::uint32_t parity) {
+  std::uint32_t done;
+  asm volatile("{\n"
+               ".reg .pred p;\n"
+               "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+               "selp.u32 %0, 1, 0, p;\n"
+               "}\n"
+               : "=r"(done)
+               : "r"(bar), "r"(parity)
+               : "memory");
+  return done != 0;
+}
+
+// Bounded wait.  Returns false when the wait ran out or another role has already given up.
+__device__ __forceinline__ bool mbar_wait(std::uint32_t bar, std::uint32_t parity, volatile std::uint32_t *abort_flag) {
+  if (mbar_try_wait(bar, parity)) {
+    return true;
+  }
+  const long long started = clock64();
+  std::uint32_t polls = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++polls & 255U) == 0) {
+      if (*abort_flag != 0) {
+        return false;
+      }
+      if (clock64() - started > kWaitLimitCycles) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(std::uint32_t dst, const CUtensorMap *map, int c0, int c1,
+                                            std::uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::
+                   "r"(dst),
+               "l"(reinterpret_cast<std::uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar)
+               : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d(std::uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2,
+                                            std::uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];\n" ::
+          "r"(dst),
+      "l"(reinterpret_cast<std::uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1.
+// lbo / sbo in bytes (the field drops the low four bits).
+__device__ __forceinline__ std::uint64_t smem_desc(std::uint32_t addr, std::uint32_t lbo, std::uint32_t sbo) {
+  std::uint64_t d = 0;
+  d |= static_cast<std::uint64_t>((addr & 0x3FFFFU) >> 4);
+  d |= static_cast<std::uint64_t>((lbo >> 4) & 0x3FFFU) << 16;
+  d |= static_cast<std::uint64_t>((sbo >> 4) & 0x3FFFU) << 32;
+  d |= static_cast<std::uint64_t>(1) << 46; // version
+  d |= static_cast<std::uint64_t>(2) << 61; // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor: BF16 x BF16 -> FP32, M = 128.
+__host__ __device__ constexpr std::uint32_t instr_desc(int n, bool b_mn_major) {
+  return (1U << 4) | (1U << 7) | (1U << 10) | (b_mn_major ? (1U << 16) : 0U) |
+         (static_cast<std::uint32_t>(n >> 3) << 17) | (static_cast<std::uint32_t>(kTileRows >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_ss(std::uint32_t d_tmem, std::uint64_t a_desc, std::uint64_t b_desc,
+                                        std::uint32_t idesc, std::uint32_t accumulate) {
+  asm volatile("{\n"
+               ".reg .pred p;\n"
+               "setp.ne.b32 p, %4, 0;\n"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+               "}\n" ::"r"(d_tmem),
+               "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+
+__device__ __forceinline__ void umma_ts(std::uint32_t d_tmem, std::uint32_t a_tmem, std::uint64_t b_desc,
+                                        std::uint32_t idesc, std::uint32_t accumulate) {
+  asm volatile("{\n"
+               ".reg .pred p;\n"
+               "setp.ne.b32 p, %4, 0;\n"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+               "}\n" ::"r"(d_tmem),
+               "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(std::uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(std::uint32_t taddr, std::uint32_t (&v)[32]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+               "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+               "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                 "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]),
+                 "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]),
+                 "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]),
+                 "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+               : "r"(taddr)
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_st32(std::uint32_t taddr, const std::uint32_t (&v)[32]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+               "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+               "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n" ::"r"(taddr),
+               "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+               "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]),
+               "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]),
+               "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+
+__device__ __forceinline__ std::uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const std::uint32_t *>(&v);
+}
+
+// ---- append: K and V of this chunk into the cache -----------------------------------------------------
+template <bool F32>
+__global__ void __launch_bounds__(256) prefill_append_kernel(const void *key, const void *value,
+                                                             __nv_bfloat16 *cache, std::uint32_t tokens,
+                                                             std::uint32_t past, std::uint32_t max_ctx) {
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+  // one thread per 8 elements: [plane][token][kv head][32 pieces of 8]
+  const std::size_t pieces = static_cast<std::size_t>(tokens) * kKvHeads * 32;
+  const std::size_t id = static_cast<std::size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (id >= 2 * pieces) {
+    return;
+  }
+  const bool is_value = id >= pieces;
+  const std::size_t local = is_value ? id - pieces : id;
+  const std::uint32_t piece = static_cast<std::uint32_t>(local % 32);
+  const std::uint32_t head = static_cast<std::uint32_t>((local / 32) % kKvHeads);
+  const std::uint32_t token = static_cast<std::uint32_t>(local / (32 * kKvHeads));
+  const std::size_t src = (static_cast<std::size_t>(token) * kKvHeads + head) * kHeadDim + piece * 8;
+  const void *base = is_value ? value : key;
+  uint4 raw;
+  if constexpr (F32) {
+    const float4 a = *reinterpret_cast<const float4 *>(static_cast<const float *>(base) + src);
+    const float4 b = *reinterpret_cast<const float4 *>(static_cast<const float *>(base) + src + 4);
+    raw.x = pack_bf16(a.x, a.y);
+    raw.y = pack_bf16(a.z, a.w);
+    raw.z = pack_bf16(b.x, b.y);
+    raw.w = pack_bf16(b.z, b.w);
+  } else {
+    raw = *reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(base) + src);
+  }
+  const std::size_t plane = static_cast<std::size_t>(kKvHeads) * max_ctx * kHeadDim;
+  const std::size_t dst = (is_value ? plane : 0) + (static_cast<std::size_t>(head) * max_ctx + past + token) * kHeadDim +
+                          piece * 8;
+  *reinterpret_cast<uint4 *>(cache + dst) = raw;
+}
+
+// ---- attention ----------------------------------------------------------------------------------------
+template <bool F32>
+__global__ void __launch_bounds__(kThreads, 1)
+    prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
+                             const __grid_constant__ CUtensorMap v_map, const void *query_f32,
+                             const PrefillParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  const std::uint32_t base = (smem_u32(smem_raw) + 1023U) & ~1023U;
+  unsigned char *smem = smem_raw + (base - smem_u32(smem_raw));
+  const std::uint32_t q_smem = base;
+  const std::uint32_t ring = base + kRingOffset;
+  const std::uint32_t bars = base + kBarrierOffset;
+  volatile std::uint32_t *tmem_slot = reinterpret_cast<volatile std::uint32_t *>(smem + kBarrierOffset + kBarCount * 8);
+  volatile std::uint32_t *abort_flag = tmem_slot + 1;
+  auto bar = [&](int index) { return bars + static_cast<std::uint32_t>(index) * 8U; };
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const std::uint32_t head = blockIdx.x;
+  const std::uint32_t tile = p.tiles - 1 - blockIdx.y; // long tiles first
+  const std::uint32_t kv_head = head / kGroup;
+  const std::uint32_t row0 = tile * kTileRows;                               // first query row of the tile
+  const std::uint32_t rows = min(static_cast<std::uint32_t>(kTileRows), p.tokens - row0);
+  const std::uint32_t last_pos = p.past + row0 + rows - 1;                   // newest key any row of the tile sees
+  const std::uint32_t blocks = last_pos / kBlockKeys + 1;
+
+  if (threadIdx.x == 0) {
+    mbar_init(bar(kBarQFull), F32 ? 128 : 1);
+    for (int s = 0; s < kSlots; ++s) {
+      mbar_init(bar(kBarFull + s), 1);
+      mbar_init(bar(kBarEmpty + s), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar(kBarSFull + b), 1);
+      mbar_init(bar(kBarPFull + b), 128);
+      mbar_init(bar(kBarPvDone + b), 1);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 5) {
+    // the whole tensor memory of the SM: O (256 columns) + two score tiles (128 each)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;\n" ::"r"(
+                     smem_u32(const_cast<std::uint32_t *>(tmem_slot)))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const std::uint32_t tmem = *tmem_slot;
+  const std::uint32_t tmem_o = tmem;         // columns [0, 256)
+  const std::uint32_t tmem_s = tmem + 256;   // two tiles of 128 columns
+
+  if (warp == 4) {
+    // ================= producer =================
+    if (lane == 0) {
+      if constexpr (!F32) {
+        mbar_expect_tx(bar(kBarQFull), kQBytes);
+        for (int b = 0; b < 4; ++b) {
+          tma_load_2d(q_smem + b * kQBoxBytes, &q_map, static_cast<int>(head * kHeadDim + b * kBoxCols),
+                      static_cast<int>(row0), bar(kBarQFull));
+        }
+      }
+      // the cache rows of this chunk are written by the append kernel that precedes this launch
+      asm volatile("griddepcontrol.wait;\n" ::: "memory");
+      std::uint32_t n = 0; // running slot number; the MMA warp walks the same sequence
+      auto load_half = [&](const CUtensorMap *map, std::uint32_t block, std::uint32_t half) {
+        const std::uint32_t slot = n % kSlots;
+        if (n >= kSlots) {
+          if (!mbar_wait(bar(kBarEmpty + slot), ((n / kSlots) - 1) & 1U, abort_flag)) {
+            return false;
+          }
+        }
+        mbar_expect_tx(bar(kBarFull + slot), kSlotBytes);
+        const int key0 = static_cast<int>(block * kBlockKeys + half * kHalfKeys);
+        for (int b = 0; b < 4; ++b) {
+          tma_load_3d(ring + slot * kSlotBytes + b * kSlotBoxBytes, map, b * kBoxCols, key0,
+                      static_cast<int>(kv_head), bar(kBarFull + slot));
+        }
+        ++n;
+        return true;
+      };
+      bool ok = load_half(&k_map, 0, 0) && load_half(&k_map, 0, 1);
+      for (std::uint32_t j = 0; ok && j < blocks; ++j) {
+        if (j + 1 < blocks) {
+          ok = load_half(&k_map, j + 1, 0) && load_half(&k_map, j + 1, 1);
+        }
+        ok = ok && load_half(&v_map, j, 0) && load_half(&v_map, j, 1);
+      }
+    }
+  } else if (warp == 5) {
+    // ================= MMA issue =================
+    if (lane == 0) {
+      constexpr std::uint32_t kIdescQk = instr_desc(kHalfKeys, false);
+      constexpr std::uint32_t kIdescPv = instr_desc(kHeadDim, true);
+      std::uint32_t n = 0;
+      bool ok = mbar_wait(bar(kBarQFull), 0, abort_flag);
+      tcgen05_fence_after();
+      // S[block % 2] = Q K_block^T, one half (64 keys = 64 columns) per ring slot
+      auto issue_qk = [&](std::uint32_t block) {
+        for (std::uint32_t half = 0; half < 2 && ok; ++half) {
+          const std::uint32_t slot = n % kSlots;
+          ok = mbar_wait(bar(kBarFull + slot), (n / kSlots) & 1U, abort_flag);
+          if (!ok) {
+            break;
+          }
+          tcgen05_fence_after();
+          const std::uint32_t d = tmem_s + (block & 1U) * kBlockKeys + half * kHalfKeys;
+#pragma unroll
+          for (int ks = 0; ks < 16; ++ks) {
+            const std::uint64_t a = smem_desc(q_smem + (ks >> 2) * kQBoxBytes + (ks & 3) * 32, 16, 1024);
+            const std::uint64_t b =
+                smem_desc(ring + slot * kSlotBytes + (ks >> 2) * kSlotBoxBytes + (ks & 3) * 32, 16, 1024);
+            umma_ss(d, a, b, kIdescQk, ks > 0 ? 1U : 0U);
+          }
+          umma_commit(bar(kBarEmpty + slot));
+          ++n;
+        }
+        if (ok) {
+          umma_commit(bar(kBarSFull + (block & 1U)));
+        }
+      };
+      if (ok) {
+        issue_qk(0);
+      }
+      for (std::uint32_t j = 0; ok && j < blocks; ++j) {
+        if (j + 1 < blocks) {
+          issue_qk(j + 1);
+        }
+        if (!ok) {
+          break;
+        }
+        ok = mbar_wait(bar(kBarPFull + (j & 1U)), (j >> 1) & 1U, abort_flag);
+        if (!ok) {
+          break;
+        }
+        tcgen05_fence_after();
+        // O += P_j V_j, P from tensor memory (BF16 pairs: 16 keys = 8 columns), V dim-major from the ring
+        for (std::uint32_t half = 0; half < 2 && ok; ++half) {
+          const std::uint32_t slot = n % kSlots;
+          ok = mbar_wait(bar(kBarFull + slot), (n / kSlots) & 1U, abort_flag);
+          if (!ok) {
+            break;
+          }
+          tcgen05_fence_after();
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            const std::uint32_t a = tmem_s + (j & 1U) * kBlockKeys + half * 32 + ks * 8;
+            const std::uint64_t b = smem_desc(ring + slot * kSlotBytes + ks * 2048, kSlotBoxBytes, 1024);
+            umma_ts(tmem_o, a, b, kIdescPv, (j > 0 || half > 0 || ks > 0) ? 1U : 0U);
+          }
+          umma_commit(bar(kBarEmpty + slot));
+          ++n;
+        }
+        if (ok) {
+          umma_commit(bar(kBarPvDone + (j & 1U)));
+        }
+      }
+    }
+  } else {
+    // ================= softmax, correction, epilogue: thread = query row =================
+    const std::uint32_t row = warp * 32 + lane;
+    const std::uint32_t lane_base = static_cast<std::uint32_t>(warp * 32) << 16;
+    const std::uint32_t q_pos = p.past + row0 + row; // position of this row's query (rows past the tile are idle)
+    bool ok = true;
+
+    if constexpr (F32) {
+      // FP32 queries: round to BF16 and lay the tile out by hand in the swizzled form TMA would have produced
+      const float *src = static_cast<const float *>(query_f32) +
+                         (static_cast<std::size_t>(row0 + row) * kQueryHeads + head) * kHeadDim;
+      const bool live = row < rows;
+#pragma unroll 4
+      for (int c = 0; c < 32; ++c) { // 32 chunks of 8 dims
+        float4 a = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+        float4 b = a;
+        if (live) {
+          a = *reinterpret_cast<const float4 *>(src + 8 * c);
+          b = *reinterpret_cast<const float4 *>(src + 8 * c + 4);
+        }
+        uint4 raw;
+        raw.x = pack_bf16(a.x, a.y);
+        raw.y = pack_bf16(a.z, a.w);
+        raw.z = pack_bf16(b.x, b.y);
+        raw.w = pack_bf16(b.z, b.w);
+        const std::uint32_t box = c >> 3;
+        const std::uint32_t chunk = (c & 7) ^ (row & 7);
+        *reinterpret_cast<uint4 *>(smem + box * kQBoxBytes + row * 128 + chunk * 16) = raw;
+      }
+      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+      mbar_arrive(bar(kBarQFull));
+    }
+
+    float m_used = -INFINITY; // maximum the exponentials are taken against (scaled, base 2)
+    float l_sum = 0.0F;
+    for (std::uint32_t j = 0; j < blocks && ok; ++j) {
+      const std::uint32_t buf = j & 1U;
+      ok = mbar_wait(bar(kBarSFull + buf), (j >> 1) & 1U, abort_flag);
+      if (!ok) {
+        break;
+      }
+      tcgen05_fence_after();
+      const std::uint32_t s_addr = tmem_s + lane_base + buf * kBlockKeys;
+      float x[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        std::uint32_t v[32];
+        tmem_ld32(s_addr + c * 32, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          x[c * 32 + e] = __uint_as_float(v[e]) * kScaleLog2e;
+        }
+      }
+      // causal mask: key position j*128 + c is visible iff <= q_pos (also hides rows the context never held)
+      const std::uint32_t key0 = j * kBlockKeys;
+      if (key0 + kBlockKeys - 1 > p.past + row0) {
+        const int visible = static_cast<int>(q_pos) - static_cast<int>(key0) + 1;
+#pragma unroll
+        for (int e = 0; e < 128; ++e) {
+          if (e >= visible) {
+            x[e] = -INFINITY;
+          }
+        }
+      }
+      float mx = x[0];
+#pragma unroll
+      for (int e = 1; e < 128; ++e) {
+        mx = fmaxf(mx, x[e]);
+      }
+      // move the reference maximum only when it fell far behind; block 0 always sets it
+      const bool move = mx > m_used + kRescaleThreshold;
+      if (__any_sync(0xFFFFFFFFU, move && j > 0)) {
+        // rescale this warp's 32 rows of O; PV(j-1) must have landed
+        ok = mbar_wait(bar(kBarPvDone + ((j - 1) & 1U)), ((j - 1) >> 1) & 1U, abort_flag);
+        ok = __all_sync(0xFFFFFFFFU, ok);
+        if (!ok) {
+          break;
+        }
+        tcgen05_fence_after();
+        const float factor = move ? exp2f(m_used - mx) : 1.0F;
+#pragma unroll 1
+        for (int c = 0; c < 8; ++c) {
+          std::uint32_t v[32];
+          tmem_ld32(tmem_o + lane_base + c * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            v[e] = __float_as_uint(__uint_as_float(v[e]) * factor);
+          }
+          tmem_st32(tmem_o + lane_base + c * 32, v);
+        }
+        tmem_wait_st();
+        l_sum *= factor;
+      }
+      if (move) {
+        m_used = mx;
+      }
+      float part = 0.0F;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        std::uint32_t packed[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const float p0 = exp2f(x[c * 64 + 2 * e] - m_used);
+          const float p1 = exp2f(x[c * 64 + 2 * e + 1] - m_used);
+          part += p0 + p1;
+          packed[e] = pack_bf16(p0, p1);
+        }
+        tmem_st32(s_addr + c * 32, packed);
+      }
+      l_sum += part;
+      tmem_wait_st();
+      tcgen05_fence_before();
+      mbar_arrive(bar(kBarPFull + buf));
+    }
+
+    // epilogue: out = O / l * sigmoid(gate)
+    if (ok) {
+      ok = mbar_wait(bar(kBarPvDone + ((blocks - 1) & 1U)), ((blocks - 1) >> 1) & 1U, abort_flag);
+    }
+    ok = __all_sync(0xFFFFFFFFU, ok);
+    if (ok) {
+      tcgen05_fence_after();
+      const float inv = 1.0F / l_sum;
+      const std::size_t out_base = (static_cast<std::size_t>(row0 + row) * kQueryHeads + head) * kHeadDim;
+#pragma unroll 1
+      for (int c = 0; c < 8; ++c) {
+        std::uint32_t v[32];
+        tmem_ld32(tmem_o + lane_base + c * 32, v);
+        tmem_wait_ld();
+        if (row < rows) {
+          if constexpr (F32) {
+            const float *g = static_cast<const float *>(p.gate) + out_base + c * 32;
+            float *o = static_cast<float *>(p.output) + out_base + c * 32;
+#pragma unroll
+            for (int e = 0; e < 32; e += 4) {
+              const float4 gv = *reinterpret_cast<const float4 *>(g + e);
+              float4 r;
+              r.x = __uint_as_float(v[e + 0]) * inv / (1.0F + expf(-gv.x));
+              r.y = __uint_as_float(v[e + 1]) * inv / (1.0F + expf(-gv.y));
+              r.z = __uint_as_float(v[e + 2]) * inv / (1.0F + expf(-gv.z));
+              r.w = __uint_as_float(v[e + 3]) * inv / (1.0F + expf(-gv.w));
+              *reinterpret_cast<float4 *>(o + e) = r;
+            }
+          } else {
+            const __nv_bfloat16 *g = static_cast<const __nv_bfloat16 *>(p.gate) + out_base + c * 32;
+            __nv_bfloat16 *o = static_cast<__nv_bfloat16 *>(p.output) + out_base + c * 32;
+#pragma unroll
+            for (int e = 0; e < 32; e += 8) {
+              const uint4 gv = *reinterpret_cast<const uint4 *>(g + e);
+              const std::uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+              std::uint32_t ow[4];
+#pragma unroll
+              for (int h = 0; h < 4; ++h) {
+                const float g0 = __uint_as_float(gw[h] << 16);
+                const float g1 = __uint_as_float(gw[h] & 0xFFFF0000U);
+                const float r0 = __uint_as_float(v[e + 2 * h]) * inv / (1.0F + expf(-g0));
+                const float r1 = __uint_as_float(v[e + 2 * h + 1]) * inv / (1.0F + expf(-g1));
+                ow[h] = pack_bf16(r0, r1);
+              }
+              *reinterpret_cast<uint4 *>(o + e) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag != 0) {
+    atomicOr(p.status, static_cast<unsigned int>(RIB200_DEVICE_WAIT_TIMED_OUT));
+  }
+  if (warp == 5) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;\n" ::"r"(tmem) : "memory");
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------------------------
+using EncodeTiled = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                 const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_tiled_entry() {
+  static EncodeTiled fn = [] {
+    void *entry = nullptr;
+    cudaDriverEntryPointQueryResult result{};
+    cuda_ok(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &result),
+            "cuTensorMapEncodeTiled lookup");
+    require(entry != nullptr && result == cudaDriverEntryPointSuccess, "cuTensorMapEncodeTiled is unavailable",
+            RIB200_STATUS_UNAVAILABLE);
+    return reinterpret_cast<EncodeTiled>(entry);
+  }();
+  return fn;
+}
+
+CUtensorMap make_map(void *base, int rank, const cuuint64_t *dims, const cuuint64_t *strides_bytes,
+                     const cuuint32_t *box) {
+  CUtensorMap map;
+  const cuuint32_t elem_strides[3] = {1, 1, 1};
+  const CUresult rc =
+      encode_tiled_entry()(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank), base, dims,
+                           strides_bytes, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  require(rc == CUDA_SUCCESS, "tensor map encoding failed", RIB200_STATUS_CUDA_ERROR);
+  return map;
+}
+
+template <bool F32> void configure_once() {
+  static std::once_flag flags[64];
+  int device = 0;
+  cuda_ok(cudaGetDevice(&device), "cudaGetDevice");
+  require(device >= 0 && device < 64, "device ordinal out of range", RIB200_STATUS_INTERNAL);
+  std::call_once(flags[device], [] {
+    cuda_ok(cudaFuncSetAttribute(prefill_attention_kernel<F32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 kSmemBytes),
+            "prefill attention shared-memory opt-in");
+  });
+}
+
+template <bool F32> void launch(const PrefillArgs &a, cudaStream_t stream) {
+  configure_once<F32>();
+  auto *cache = static_cast<__nv_bfloat16 *>(a.kv_cache);
+  const std::size_t pieces = static_cast<std::size_t>(a.tokens) * kKvHeads * 32 * 2;
+  prefill_append_kernel<F32><<<static_cast<unsigned int>((pieces + 255) / 256), 256, 0, stream>>>(
+      a.key, a.value, cache, a.tokens, a.past_tokens, a.max_context_tokens);
+  cuda_ok(cudaGetLastError(), "prefill append launch");
+
+  const std::uint64_t context = static_cast<std::uint64_t>(a.past_tokens) + a.tokens;
+  // K / V: [kv head][row < context][256], rows 512 bytes apart, heads max_ctx rows apart
+  const cuuint64_t kv_dims[3] = {kHeadDim, context, kKvHeads};
+  const cuuint64_t kv_strides[2] = {kHeadDim * 2, static_cast<cuuint64_t>(a.max_context_tokens) * kHeadDim * 2};
+  const cuuint32_t kv_box[3] = {kBoxCols, kHalfKeys, 1};
+  const CUtensorMap k_map = make_map(cache, 3, kv_dims, kv_strides, kv_box);
+  const CUtensorMap v_map =
+      make_map(cache + static_cast<std::size_t>(kKvHeads) * a.max_context_tokens * kHeadDim, 3, kv_dims, kv_strides,
+               kv_box);
+  // Q: [token][16 * 256] (BF16 activations only; FP32 queries are converted inside the kernel)
+  CUtensorMap q_map = k_map;
+  if (!F32) {
+    const cuuint64_t q_dims[2] = {kQueryHeads * kHeadDim, a.tokens};
+    const cuuint64_t q_strides[1] = {kQueryHeads * kHeadDim * 2};
+    const cuuint32_t q_box[2] = {kBoxCols, kTileRows};
+    q_map = make_map(const_cast<void *>(a.query), 2, q_dims, q_strides, q_box);
+  }
+
+  PrefillParams params{};
+  params.gate = a.gate;
+  params.output = a.output;
+  params.tokens = a.tokens;
+  params.past = a.past_tokens;
+  params.tiles = (a.tokens + kTileRows - 1) / kTileRows;
+  params.status = device_status_word();
+
+  cudaLaunchConfig_t config{};
+  config.gridDim = dim3(kQueryHeads, params.tiles, 1);
+  config.blockDim = dim3(kThreads, 1, 1);
+  config.dynamicSmemBytes = kSmemBytes;
+  config.stream = stream;
+  cudaLaunchAttribute attribute{};
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  cuda_ok(cudaLaunchKernelEx(&config, prefill_attention_kernel<F32>, q_map, k_map, v_map, a.query, params),
+          "prefill attention launch");
+}
+
+} // namespace
+
+void launch_prefill_attention(const PrefillArgs &args, cudaStream_t stream) {
+  require(args.tokens <= 65535U * kTileRows, "prefill attention: too many tokens for one launch");
+  if (args.activations_f32) {
+    launch<true>(args, stream);
+  } else {
+    launch<false>(args, stream);
+  }
+}
+
 } // namespace rib200
