@@ -58,6 +58,39 @@ def test_recurrent_core(tokens, dtype):
     assert m_state["nonfinite"] == 0 and m_state["rel_l2"] <= 1.0e-5, m_state
 
 
+@pytest.mark.parametrize("tokens", [64, 65, 100, 128, 257, 1024])
+@pytest.mark.parametrize("dtype", [K.DTYPE_BF16, K.DTYPE_F32])
+def test_chunked_core_matches_the_sequential_recurrence(tokens, dtype):
+    """Runs of 64 tokens or more take the chunk-64 WY-form kernels; the ground truth stays the token-sequential
+    recurrence.  Outputs: max abs <= 3e-2, relative L2 <= 1e-2 (held to 2e-3); FP32 state relative L2 <= 1e-3."""
+    m_out, m_state = run_core(tokens, dtype, seed=0xB2001300 + tokens)
+    assert m_out["nonfinite"] == 0 and m_out["max_abs"] <= 3.0e-2 and m_out["rel_l2"] <= 2.0e-3, m_out
+    assert m_state["nonfinite"] == 0 and m_state["rel_l2"] <= 1.0e-3, m_state
+
+
+def test_chunked_prefill_4096_then_128_decode_steps():
+    """The benchmark's gated-delta configuration: zero state, 4096-token chunked prefill, then 128 recurrent steps."""
+    tokens, steps, seed = 4096, 128, 0xB2001400
+    q, k, v, beta, g = core_operands(seed, tokens + steps)
+    state0 = np.zeros((HV, DK, DK), dtype=np.float32)
+    state = torch.zeros(HV, DK, DK, device=dev())
+    out = torch.zeros(tokens + steps, HV, DK, device=dev())
+    dq, dk, dv = bf16_tensor(q), bf16_tensor(k), bf16_tensor(v)
+    dbeta, dg = torch.from_numpy(beta).to(dev()), torch.from_numpy(g).to(dev())
+    ws_bytes = K.gdn_core_workspace_bytes(tokens, HK, HV, DK, DK)
+    ws = torch.zeros(ws_bytes // 4, device=dev())
+    stream = torch.cuda.current_stream()
+    K.gdn_core(dq, dk, dv, dbeta, dg, state, out, ws, ws_bytes, tokens, HK, HV, DK, DK, K.DTYPE_BF16, stream)
+    for t in range(tokens, tokens + steps):
+        K.gdn_core(dq[t], dk[t], dv[t], dbeta[t], dg[t], state, out[t], None, 0, 1, HK, HV, DK, DK, K.DTYPE_BF16, stream)
+    torch.cuda.synchronize()
+    want_out, want_state = ob.gdn_core(q, k, v, beta, np.exp(g), state0)
+    m_out = compare(to_numpy_f32(out), want_out)
+    m_state = compare(to_numpy_f32(state), want_state)
+    assert m_out["nonfinite"] == 0 and m_out["max_abs"] <= 3.0e-2 and m_out["rel_l2"] <= 1.0e-2, m_out
+    assert m_state["nonfinite"] == 0 and m_state["rel_l2"] <= 1.0e-3, m_state
+
+
 def test_recurrent_core_small_head_counts():
     m_out, m_state = run_core(3, K.DTYPE_F32, seed=0xB2001100, hk=2, hv=4)
     assert m_out["rel_l2"] <= 1.0e-4 and m_state["rel_l2"] <= 1.0e-5
@@ -156,6 +189,15 @@ def test_layer_small_heads(tokens, dtype, wdtype):
 def test_layer_model_shape_prefill_then_decode_then_continued_prefill():
     run = LayerRun(0xB2002100, HK, HV, 4, K.DTYPE_BF16, K.DTYPE_F32, 3 + 1 + 1 + 5)
     for tokens in (3, 1, 1, 5):
+        out, want, _ = run.step(tokens)
+        run.check(out, want)
+
+
+@pytest.mark.parametrize("dtype", [K.DTYPE_BF16, K.DTYPE_F32])
+def test_layer_chunked_prefill_then_decode(dtype):
+    """A 150-token call takes the chunked kernels inside the layer; a one-token call follows on the same states."""
+    run = LayerRun(0xB2002500, 4, 8, 4, dtype, K.DTYPE_F32, 151)
+    for tokens in (150, 1):
         out, want, _ = run.step(tokens)
         run.check(out, want)
 
