@@ -166,11 +166,13 @@ class LayerRun:
                                                                 1.0e-6))
         return out, want, (d_in, ws)
 
-    def check(self, out, want):
+    def check(self, out, want, chunked=False):
         m = compare(to_numpy_f32(out), want)
         assert m["nonfinite"] == 0 and m["max_abs"] <= 3.0e-2 and m["rel_l2"] <= 1.0e-2, m
-        if self.dtype == K.DTYPE_F32:
-            assert m["max_abs"] <= 2.0e-3 and m["rel_l2"] <= 2.0e-4, m
+        if self.dtype == K.DTYPE_F32 and not chunked:
+            assert m["max_abs"] <= 2.0e-3 and m["rel_l2"] <= 2.0e-4, m  # FP32 recurrent path
+        if self.dtype == K.DTYPE_F32 and chunked:
+            assert m["max_abs"] <= 1.5e-2 and m["rel_l2"] <= 2.0e-3, m  # TF32 tensor-core products
         cs = compare(to_numpy_f32(self.d_cs).reshape(-1), self.cs.reshape(-1))
         assert cs["max_abs"] == 0.0, cs
         rs = compare(to_numpy_f32(self.d_rs).reshape(-1), self.rs.reshape(-1))
@@ -199,7 +201,7 @@ def test_layer_chunked_prefill_then_decode(dtype):
     run = LayerRun(0xB2002500, 4, 8, 4, dtype, K.DTYPE_F32, 151)
     for tokens in (150, 1):
         out, want, _ = run.step(tokens)
-        run.check(out, want)
+        run.check(out, want, chunked=True)
 
 
 def test_layer_three_launches_share_device_state_without_a_sync():
