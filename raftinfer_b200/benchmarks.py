@@ -179,3 +179,44 @@ def run(dev, stream, hbm_peak, tensor_peak):
             extra[name] = {"unavailable": str(err)}
         torch.cuda.empty_cache()
     return extra
+
+
+def main(argv=None):
+    """python -m raftinfer_b200.benchmarks [decode] [serving] [gdn] [prefill] [--tokens N] [--reps R]
+
+    Prints one JSON object with the requested sections (all when none is named)."""
+    import argparse
+    import json
+    import os
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("sections", nargs="*", default=[])
+    ap.add_argument("--tokens", type=int, nargs="*", default=None, help="prefill token counts")
+    ap.add_argument("--contexts", type=int, nargs="*", default=None, help="decode contexts")
+    args = ap.parse_args(argv)
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    torch.cuda.set_stream(torch.cuda.Stream(device=dev))
+    stream = torch.cuda.current_stream()
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    peaks_path = os.path.join(root, "MEASURED_PEAKS.json")
+    hbm, tensor = 6650.0, 1590.0
+    if os.path.exists(peaks_path):
+        peaks = json.load(open(peaks_path))
+        hbm, tensor = float(peaks["hbm_gbs"]), float(peaks["bf16_tflops"])
+    want = set(args.sections) or {"decode", "serving", "gdn", "prefill"}
+    out = {}
+    if "decode" in want:
+        out["decode_attention"] = decode_contexts(dev, stream, hbm, tuple(args.contexts or (4096, 32768, 131072)))
+    if "serving" in want:
+        out["batched_serving_decode"] = batched_serving_decode(dev, stream, hbm)
+    if "gdn" in want:
+        out["gated_delta"] = gdn_layer(dev, stream, hbm, tensor)
+    if "prefill" in want:
+        out["prefill_attention"] = prefill_attention(dev, stream, tensor, tuple(args.tokens or (128, 512, 4096)))
+    print(json.dumps(out))
+    return out
+
+
+if __name__ == "__main__":
+    main()

@@ -50,7 +50,7 @@ template <bool F32> __device__ __forceinline__ void load4(const void *base, std:
 }
 
 template <bool F32>
-__global__ void __launch_bounds__(256) gdn_recurrent_kernel(const RecurrentParams p) {
+__global__ void __launch_bounds__(256, 4) gdn_recurrent_kernel(const RecurrentParams p) {
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const std::uint32_t head = blockIdx.y;

@@ -7,19 +7,22 @@
 // cache, which is exactly what the reference's prefill kernel sees.  The second launch uses programmatic
 // dependent launch so that its set-up overlaps the append.
 //
-// Attention kernel (one CTA per 128 query rows of one head, 192 threads):
-//   warp 4   producer.  TMA tiled loads with the 128-byte swizzle: the Q tile once (64 KiB), then K and V in
-//            half blocks of 64 keys (32 KiB each) through a ring of four slots.  The tensor maps end at the
+// Attention kernel (one CTA per 128 query rows of one head, 320 threads):
+//   warp 8   producer.  TMA tiled loads with the 128-byte swizzle: the Q tile once (64 KiB), then K and V in
+//            half blocks of 64 keys (32 KiB each) through a ring of five slots, which is what lets a load be
+//            issued four half-blocks (one and a half microseconds of tensor work) ahead of its use.  The tensor maps end at the
 //            live context, so rows the cache has never held arrive as zeros.
-//   warp 5   issues tcgen05.mma (BF16 in, FP32 accumulate in tensor memory).  Tensor memory holds the output
+//   warp 9   issues tcgen05.mma (BF16 in, FP32 accumulate in tensor memory).  Tensor memory holds the output
 //            tile O (128 lanes x 256 columns) and two score tiles S (128 x 128 each): 512 columns in all.
 //            S = Q K^T takes both operands from shared memory (K-major); O += P V takes P from tensor memory
 //            (written over the S tile it came from, as BF16) and V from shared memory (dim-major).
 //            The issue order QK(j+1), PV(j) keeps the tensor pipe busy while the softmax of block j runs.
-//   warps 0-3 softmax: one thread per query row (tensor-memory lane), FP32, exp2f.  The running maximum used
-//            for the exponentials only moves when it falls more than 8 (base-2) behind, at which point the
-//            thread rescales its row of O in tensor memory; this is rare after the first blocks.  The same
-//            threads normalise, gate and store the tile at the end.
+//   warps 0-7 softmax, two groups of four warps: a thread owns one query row (its tensor-memory lane) and 64 of
+//            the 128 score columns, FP32, ex2.  Two warps per scheduler hide each other's latencies; with one
+//            the softmax, not the tensor pipe, set the pace.  The running maximum used for the exponentials only
+//            moves when it falls more than 8 (base-2) behind, at which point the threads rescale their rows of
+//            O in tensor memory; this is rare after the first blocks.  The same threads normalise, gate and
+//            store the tile at the end.
 //
 // Work per launch: 4 * 16 * 256 * (T * P + T (T + 1) / 2) flops for T new tokens after P past tokens.
 // Every wait on an mbarrier is bounded; when one runs out the CTA records RIB200_DEVICE_WAIT_TIMED_OUT, all
@@ -44,16 +47,21 @@ constexpr int kGroup = kQueryHeads / kKvHeads;
 constexpr int kTileRows = 128;  // query rows per CTA
 constexpr int kBlockKeys = 128; // keys per score tile
 constexpr int kHalfKeys = 64;   // keys per ring slot
-constexpr int kSlots = 4;
+constexpr int kSlots = 5;
 constexpr int kBoxCols = 64;                              // 64 BF16 = one 128-byte swizzle row
 constexpr int kQBoxBytes = kTileRows * 128;               // 16 KiB
 constexpr int kQBytes = 4 * kQBoxBytes;                   // 64 KiB
 constexpr int kSlotBoxBytes = kHalfKeys * 128;            // 8 KiB
 constexpr int kSlotBytes = 4 * kSlotBoxBytes;             // 32 KiB
+constexpr int kKeyBoxBytes = kBlockKeys * 128;            // K slot: two boxes of 128 keys x 64 dims, 16 KiB each
 constexpr int kRingOffset = kQBytes;
 constexpr int kBarrierOffset = kRingOffset + kSlots * kSlotBytes;
-constexpr int kSmemBytes = kBarrierOffset + 256 + 1024;   // + barriers + slack to align the base to 1 KiB
-constexpr int kThreads = 192;
+constexpr int kExchangeOffset = kBarrierOffset + 256;     // row maxima / row sums passed between the two softmax groups
+constexpr int kSmemBytes = kExchangeOffset + 2 * 2 * kTileRows * 4;
+constexpr int kSoftmaxThreads = 256;                      // two groups of four warps, 64 score columns per thread
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr int kThreads = 320;
 constexpr long long kWaitLimitCycles = 1LL << 30;
 constexpr float kScaleLog2e = 0.0625F * 1.4426950408889634F; // (1 / sqrt(256)) * log2(e)
 constexpr float kRescaleThreshold = 8.0F;
@@ -219,6 +227,12 @@ __device__ __forceinline__ void tmem_st32(std::uint32_t taddr, const std::uint32
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ std::uint32_t pack_bf16(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const std::uint32_t *>(&v);
@@ -266,9 +280,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                              const __grid_constant__ CUtensorMap v_map, const void *query_f32,
                              const PrefillParams p) {
-  extern __shared__ unsigned char smem_raw[];
-  const std::uint32_t base = (smem_u32(smem_raw) + 1023U) & ~1023U;
-  unsigned char *smem = smem_raw + (base - smem_u32(smem_raw));
+  extern __shared__ __align__(1024) unsigned char smem[];
+  const std::uint32_t base = smem_u32(smem); // the 128-byte swizzle needs 1 KiB alignment; checked below
   const std::uint32_t q_smem = base;
   const std::uint32_t ring = base + kRingOffset;
   const std::uint32_t bars = base + kBarrierOffset;
@@ -287,20 +300,20 @@ __global__ void __launch_bounds__(kThreads, 1)
   const std::uint32_t blocks = last_pos / kBlockKeys + 1;
 
   if (threadIdx.x == 0) {
-    mbar_init(bar(kBarQFull), F32 ? 128 : 1);
+    mbar_init(bar(kBarQFull), F32 ? kSoftmaxThreads : 1);
     for (int s = 0; s < kSlots; ++s) {
       mbar_init(bar(kBarFull + s), 1);
       mbar_init(bar(kBarEmpty + s), 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar(kBarSFull + b), 1);
-      mbar_init(bar(kBarPFull + b), 128);
+      mbar_init(bar(kBarPFull + b), kSoftmaxThreads);
       mbar_init(bar(kBarPvDone + b), 1);
     }
-    *abort_flag = 0;
+    *abort_flag = (base & 1023U) != 0 ? 1U : 0U; // a misaligned window would scramble every tile: give up cleanly
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     // the whole tensor memory of the SM: O (256 columns) + two score tiles (128 each)
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;\n" ::"r"(
                      smem_u32(const_cast<std::uint32_t *>(tmem_slot)))
@@ -314,7 +327,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const std::uint32_t tmem_o = tmem;         // columns [0, 256)
   const std::uint32_t tmem_s = tmem + 256;   // two tiles of 128 columns
 
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     // ================= producer =================
     if (lane == 0) {
       if constexpr (!F32) {
@@ -327,7 +340,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       // the cache rows of this chunk are written by the append kernel that precedes this launch
       asm volatile("griddepcontrol.wait;\n" ::: "memory");
       std::uint32_t n = 0; // running slot number; the MMA warp walks the same sequence
-      auto load_half = [&](const CUtensorMap *map, std::uint32_t block, std::uint32_t half) {
+      // K travels as two slots per block split by head dims (128 keys x 128 dims each, so that one MMA spans all
+      // 128 keys); V as two slots split by keys (64 keys x 256 dims each).
+      auto load_half = [&](bool is_value, std::uint32_t block, std::uint32_t half) {
         const std::uint32_t slot = n % kSlots;
         if (n >= kSlots) {
           if (!mbar_wait(bar(kBarEmpty + slot), ((n / kSlots) - 1) & 1U, abort_flag)) {
@@ -335,32 +350,47 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
         mbar_expect_tx(bar(kBarFull + slot), kSlotBytes);
-        const int key0 = static_cast<int>(block * kBlockKeys + half * kHalfKeys);
-        for (int b = 0; b < 4; ++b) {
-          tma_load_3d(ring + slot * kSlotBytes + b * kSlotBoxBytes, map, b * kBoxCols, key0,
-                      static_cast<int>(kv_head), bar(kBarFull + slot));
+        const std::uint32_t dst = ring + slot * kSlotBytes;
+        if (is_value) {
+          const int key0 = static_cast<int>(block * kBlockKeys + half * kHalfKeys);
+          for (int b = 0; b < 4; ++b) {
+            tma_load_3d(dst + b * kSlotBoxBytes, &v_map, b * kBoxCols, key0, static_cast<int>(kv_head),
+                        bar(kBarFull + slot));
+          }
+        } else {
+          const int key0 = static_cast<int>(block * kBlockKeys);
+          for (int b = 0; b < 2; ++b) {
+            tma_load_3d(dst + b * kKeyBoxBytes, &k_map, static_cast<int>((half * 2 + b) * kBoxCols), key0,
+                        static_cast<int>(kv_head), bar(kBarFull + slot));
+          }
         }
         ++n;
         return true;
       };
-      bool ok = load_half(&k_map, 0, 0) && load_half(&k_map, 0, 1);
+      bool ok = *abort_flag == 0;
+      ok = ok && load_half(false, 0, 0) && load_half(false, 0, 1);
       for (std::uint32_t j = 0; ok && j < blocks; ++j) {
         if (j + 1 < blocks) {
-          ok = load_half(&k_map, j + 1, 0) && load_half(&k_map, j + 1, 1);
+          ok = load_half(false, j + 1, 0) && load_half(false, j + 1, 1);
         }
-        ok = ok && load_half(&v_map, j, 0) && load_half(&v_map, j, 1);
+        ok = ok && load_half(true, j, 0) && load_half(true, j, 1);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     // ================= MMA issue =================
     if (lane == 0) {
-      constexpr std::uint32_t kIdescQk = instr_desc(kHalfKeys, false);
+      constexpr std::uint32_t kIdescQk = instr_desc(kBlockKeys, false);
       constexpr std::uint32_t kIdescPv = instr_desc(kHeadDim, true);
+      // Descriptors are built once; inside the loops only a constant is added to the address field.
+      const std::uint64_t q_desc = smem_desc(q_smem, 16, 1024);
+      const std::uint64_t k_desc = smem_desc(ring, 16, 1024);            // K-major, 8-row groups 1 KiB apart
+      const std::uint64_t v_desc = smem_desc(ring, kSlotBoxBytes, 1024); // dim-major, 64-dim boxes 8 KiB apart
       std::uint32_t n = 0;
-      bool ok = mbar_wait(bar(kBarQFull), 0, abort_flag);
+      bool ok = *abort_flag == 0 && mbar_wait(bar(kBarQFull), 0, abort_flag);
       tcgen05_fence_after();
-      // S[block % 2] = Q K_block^T, one half (64 keys = 64 columns) per ring slot
+      // S[block % 2] = Q K_block^T: two slots, each holding all 128 keys for half of the head dims
       auto issue_qk = [&](std::uint32_t block) {
+        const std::uint32_t d = tmem_s + (block & 1U) * kBlockKeys;
         for (std::uint32_t half = 0; half < 2 && ok; ++half) {
           const std::uint32_t slot = n % kSlots;
           ok = mbar_wait(bar(kBarFull + slot), (n / kSlots) & 1U, abort_flag);
@@ -368,13 +398,13 @@ __global__ void __launch_bounds__(kThreads, 1)
             break;
           }
           tcgen05_fence_after();
-          const std::uint32_t d = tmem_s + (block & 1U) * kBlockKeys + half * kHalfKeys;
+          const std::uint64_t a0 = q_desc + ((half * 2 * kQBoxBytes) >> 4);
+          const std::uint64_t b0 = k_desc + ((slot * kSlotBytes) >> 4);
 #pragma unroll
-          for (int ks = 0; ks < 16; ++ks) {
-            const std::uint64_t a = smem_desc(q_smem + (ks >> 2) * kQBoxBytes + (ks & 3) * 32, 16, 1024);
-            const std::uint64_t b =
-                smem_desc(ring + slot * kSlotBytes + (ks >> 2) * kSlotBoxBytes + (ks & 3) * 32, 16, 1024);
-            umma_ss(d, a, b, kIdescQk, ks > 0 ? 1U : 0U);
+          for (int ks = 0; ks < 8; ++ks) {
+            const std::uint32_t a_off = ((ks >> 2) * kQBoxBytes + (ks & 3) * 32) >> 4;
+            const std::uint32_t b_off = ((ks >> 2) * kKeyBoxBytes + (ks & 3) * 32) >> 4;
+            umma_ss(d, a0 + a_off, b0 + b_off, kIdescQk, (half > 0 || ks > 0) ? 1U : 0U);
           }
           umma_commit(bar(kBarEmpty + slot));
           ++n;
@@ -406,11 +436,11 @@ __global__ void __launch_bounds__(kThreads, 1)
             break;
           }
           tcgen05_fence_after();
+          const std::uint64_t b0 = v_desc + ((slot * kSlotBytes) >> 4);
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {
             const std::uint32_t a = tmem_s + (j & 1U) * kBlockKeys + half * 32 + ks * 8;
-            const std::uint64_t b = smem_desc(ring + slot * kSlotBytes + ks * 2048, kSlotBoxBytes, 1024);
-            umma_ts(tmem_o, a, b, kIdescPv, (j > 0 || half > 0 || ks > 0) ? 1U : 0U);
+            umma_ts(tmem_o, a, b0 + ((ks * 2048) >> 4), kIdescPv, (j > 0 || half > 0 || ks > 0) ? 1U : 0U);
           }
           umma_commit(bar(kBarEmpty + slot));
           ++n;
@@ -421,19 +451,26 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
   } else {
-    // ================= softmax, correction, epilogue: thread = query row =================
-    const std::uint32_t row = warp * 32 + lane;
-    const std::uint32_t lane_base = static_cast<std::uint32_t>(warp * 32) << 16;
+    // ================= softmax, correction, epilogue =================
+    // Two groups of four warps.  A thread owns one query row (tensor-memory lane 32 * (warp % 4) + lane) and the
+    // 64 score columns of its group, so two threads share a row; they agree on the row maximum through shared
+    // memory once per block and keep separate partial row sums until the end.
+    const int group = warp >> 2;
+    const std::uint32_t row = (warp & 3) * 32 + lane;
+    const std::uint32_t lane_base = static_cast<std::uint32_t>((warp & 3) * 32) << 16;
     const std::uint32_t q_pos = p.past + row0 + row; // position of this row's query (rows past the tile are idle)
-    bool ok = true;
+    float *exchange = reinterpret_cast<float *>(smem + kExchangeOffset); // [parity][group][row]
+    bool ok = *abort_flag == 0;
 
     if constexpr (F32) {
-      // FP32 queries: round to BF16 and lay the tile out by hand in the swizzled form TMA would have produced
+      // FP32 queries: round to BF16 and lay the tile out by hand in the swizzled form TMA would have produced.
+      // Each group converts its 128 of the 256 dims.
       const float *src = static_cast<const float *>(query_f32) +
                          (static_cast<std::size_t>(row0 + row) * kQueryHeads + head) * kHeadDim;
       const bool live = row < rows;
 #pragma unroll 4
-      for (int c = 0; c < 32; ++c) { // 32 chunks of 8 dims
+      for (int cc = 0; cc < 16; ++cc) { // 16 chunks of 8 dims
+        const int c = group * 16 + cc;
         float4 a = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
         float4 b = a;
         if (live) {
@@ -453,47 +490,54 @@ __global__ void __launch_bounds__(kThreads, 1)
       mbar_arrive(bar(kBarQFull));
     }
 
-    float m_used = -INFINITY; // maximum the exponentials are taken against (scaled, base 2)
-    float l_sum = 0.0F;
+    float m_used = -INFINITY; // maximum the exponentials are taken against (scaled, base 2); same in both groups
+    float l_sum = 0.0F;       // this thread's share of the row sum
     for (std::uint32_t j = 0; j < blocks && ok; ++j) {
       const std::uint32_t buf = j & 1U;
       ok = mbar_wait(bar(kBarSFull + buf), (j >> 1) & 1U, abort_flag);
+      ok = __all_sync(0xFFFFFFFFU, ok);
       if (!ok) {
         break;
       }
       tcgen05_fence_after();
       const std::uint32_t s_addr = tmem_s + lane_base + buf * kBlockKeys;
-      float x[128];
+      // raw scores (unscaled) of this group's 64 columns: both loads are in flight before the single wait
+      std::uint32_t xr[2][32];
+      tmem_ld32(s_addr + group * 64, xr[0]);
+      tmem_ld32(s_addr + group * 64 + 32, xr[1]);
+      tmem_wait_ld();
+      float x[64];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        std::uint32_t v[32];
-        tmem_ld32(s_addr + c * 32, v);
-        tmem_wait_ld();
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          x[c * 32 + e] = __uint_as_float(v[e]) * kScaleLog2e;
-        }
+      for (int e = 0; e < 64; ++e) {
+        x[e] = __uint_as_float(xr[e >> 5][e & 31]);
       }
       // causal mask: key position j*128 + c is visible iff <= q_pos (also hides rows the context never held)
       const std::uint32_t key0 = j * kBlockKeys;
       if (key0 + kBlockKeys - 1 > p.past + row0) {
-        const int visible = static_cast<int>(q_pos) - static_cast<int>(key0) + 1;
+        const int visible = static_cast<int>(q_pos) - static_cast<int>(key0 + group * 64) + 1;
 #pragma unroll
-        for (int e = 0; e < 128; ++e) {
+        for (int e = 0; e < 64; ++e) {
           if (e >= visible) {
             x[e] = -INFINITY;
           }
         }
       }
-      float mx = x[0];
+      float mx0 = fmaxf(x[0], x[1]);
+      float mx1 = fmaxf(x[2], x[3]);
 #pragma unroll
-      for (int e = 1; e < 128; ++e) {
-        mx = fmaxf(mx, x[e]);
+      for (int e = 4; e < 64; e += 4) {
+        mx0 = fmaxf(mx0, fmaxf(x[e], x[e + 1]));
+        mx1 = fmaxf(mx1, fmaxf(x[e + 2], x[e + 3]));
       }
+      const float mine = fmaxf(mx0, mx1);
+      exchange[(buf * 2 + group) * kTileRows + row] = mine;
+      asm volatile("bar.sync 1, 256;\n" ::: "memory");
+      const float theirs = exchange[(buf * 2 + (group ^ 1)) * kTileRows + row];
+      const float mx = fmaxf(mine, theirs) * kScaleLog2e; // the scale is positive, so it commutes with the maximum
       // move the reference maximum only when it fell far behind; block 0 always sets it
       const bool move = mx > m_used + kRescaleThreshold;
       if (__any_sync(0xFFFFFFFFU, move && j > 0)) {
-        // rescale this warp's 32 rows of O; PV(j-1) must have landed
+        // rescale this warp's 32 rows of O (this group's 128 columns); PV(j-1) must have landed
         ok = mbar_wait(bar(kBarPvDone + ((j - 1) & 1U)), ((j - 1) >> 1) & 1U, abort_flag);
         ok = __all_sync(0xFFFFFFFFU, ok);
         if (!ok) {
@@ -502,15 +546,16 @@ __global__ void __launch_bounds__(kThreads, 1)
         tcgen05_fence_after();
         const float factor = move ? exp2f(m_used - mx) : 1.0F;
 #pragma unroll 1
-        for (int c = 0; c < 8; ++c) {
+        for (int c = 0; c < 4; ++c) {
           std::uint32_t v[32];
-          tmem_ld32(tmem_o + lane_base + c * 32, v);
+          const std::uint32_t o_addr = tmem_o + lane_base + group * 128 + c * 32;
+          tmem_ld32(o_addr, v);
           tmem_wait_ld();
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
             v[e] = __float_as_uint(__uint_as_float(v[e]) * factor);
           }
-          tmem_st32(tmem_o + lane_base + c * 32, v);
+          tmem_st32(o_addr, v);
         }
         tmem_wait_st();
         l_sum *= factor;
@@ -518,38 +563,52 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (move) {
         m_used = mx;
       }
-      float part = 0.0F;
+      // p = 2^(x * scale - m): one FMA and one ex2 per score; four partial sums
+      const float neg_m = -m_used;
+      float part0 = 0.0F;
+      float part1 = 0.0F;
+      float part2 = 0.0F;
+      float part3 = 0.0F;
+      std::uint32_t packed[32];
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        std::uint32_t packed[32];
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const float p0 = exp2f(x[c * 64 + 2 * e] - m_used);
-          const float p1 = exp2f(x[c * 64 + 2 * e + 1] - m_used);
-          part += p0 + p1;
-          packed[e] = pack_bf16(p0, p1);
-        }
-        tmem_st32(s_addr + c * 32, packed);
+      for (int e = 0; e < 32; e += 2) {
+        const float p0 = fast_exp2(fmaf(x[2 * e], kScaleLog2e, neg_m));
+        const float p1 = fast_exp2(fmaf(x[2 * e + 1], kScaleLog2e, neg_m));
+        const float p2 = fast_exp2(fmaf(x[2 * e + 2], kScaleLog2e, neg_m));
+        const float p3 = fast_exp2(fmaf(x[2 * e + 3], kScaleLog2e, neg_m));
+        part0 += p0;
+        part1 += p1;
+        part2 += p2;
+        part3 += p3;
+        packed[e] = pack_bf16(p0, p1);
+        packed[e + 1] = pack_bf16(p2, p3);
       }
-      l_sum += part;
+      tmem_st32(s_addr + group * 32, packed); // keys 64*group .. +63 are BF16 pairs in columns 32*group .. +31
+      l_sum += (part0 + part1) + (part2 + part3);
       tmem_wait_st();
       tcgen05_fence_before();
       mbar_arrive(bar(kBarPFull + buf));
     }
 
-    // epilogue: out = O / l * sigmoid(gate)
+    // epilogue: out = O / l * sigmoid(gate); each group writes its 128 of the 256 columns
     if (ok) {
       ok = mbar_wait(bar(kBarPvDone + ((blocks - 1) & 1U)), ((blocks - 1) >> 1) & 1U, abort_flag);
     }
     ok = __all_sync(0xFFFFFFFFU, ok);
+    // the row sum is the two groups' shares, passed through the Q tile's memory: every MMA that read Q has
+    // completed by now (the last PV commit covers all earlier tensor work)
+    float *sums = reinterpret_cast<float *>(smem); // [group][row]
+    sums[group * kTileRows + row] = l_sum;
+    asm volatile("bar.sync 1, 256;\n" ::: "memory");
     if (ok) {
       tcgen05_fence_after();
-      const float inv = 1.0F / l_sum;
-      const std::size_t out_base = (static_cast<std::size_t>(row0 + row) * kQueryHeads + head) * kHeadDim;
+      const float inv = 1.0F / (l_sum + sums[(group ^ 1) * kTileRows + row]);
+      const std::size_t out_base =
+          (static_cast<std::size_t>(row0 + row) * kQueryHeads + head) * kHeadDim + group * 128;
 #pragma unroll 1
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < 4; ++c) {
         std::uint32_t v[32];
-        tmem_ld32(tmem_o + lane_base + c * 32, v);
+        tmem_ld32(tmem_o + lane_base + group * 128 + c * 32, v);
         tmem_wait_ld();
         if (row < rows) {
           if constexpr (F32) {
@@ -594,7 +653,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (threadIdx.x == 0 && *abort_flag != 0) {
     atomicOr(p.status, static_cast<unsigned int>(RIB200_DEVICE_WAIT_TIMED_OUT));
   }
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tcgen05_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;\n" ::"r"(tmem) : "memory");
   }
@@ -655,8 +714,9 @@ template <bool F32> void launch(const PrefillArgs &a, cudaStream_t stream) {
   // K / V: [kv head][row < context][256], rows 512 bytes apart, heads max_ctx rows apart
   const cuuint64_t kv_dims[3] = {kHeadDim, context, kKvHeads};
   const cuuint64_t kv_strides[2] = {kHeadDim * 2, static_cast<cuuint64_t>(a.max_context_tokens) * kHeadDim * 2};
+  const cuuint32_t k_box[3] = {kBoxCols, kBlockKeys, 1};
   const cuuint32_t kv_box[3] = {kBoxCols, kHalfKeys, 1};
-  const CUtensorMap k_map = make_map(cache, 3, kv_dims, kv_strides, kv_box);
+  const CUtensorMap k_map = make_map(cache, 3, kv_dims, kv_strides, k_box);
   const CUtensorMap v_map =
       make_map(cache + static_cast<std::size_t>(kKvHeads) * a.max_context_tokens * kHeadDim, 3, kv_dims, kv_strides,
                kv_box);
