@@ -34,6 +34,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <cstdint>
 #include <mutex>
 
@@ -74,8 +75,32 @@ enum : int {
   kBarSFull = 1 + 2 * kSlots,  // 2
   kBarPFull = 3 + 2 * kSlots,  // 2
   kBarPvDone = 5 + 2 * kSlots, // 2
-  kBarCount = 7 + 2 * kSlots
+  kBarQFree = 7 + 2 * kSlots,  // the tile's last score product has read Q
+  kBarOFree = 8 + 2 * kSlots,  // the tile's epilogue has read O
+  kBarCount = 9 + 2 * kSlots
 };
+
+// Optional timeline probe (compile with -DRIB200_TRACE): the first CTA of the grid stamps clock64() at the
+// points named below, 16 stamps per key block, into a device array that rib200_debug_read_trace copies out.
+#ifdef RIB200_TRACE
+__device__ long long g_trace[128 * 16];
+__device__ long long g_cta_trace[1024 * 4]; // per CTA: start ns, end ns, key blocks, SM id
+__device__ __forceinline__ long long global_ns() {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define RIB200_STAMP(block, slot)                                                   \
+  do {                                                                              \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && (block) < 128) {                      \
+      g_trace[(block) * 16 + (slot)] = clock64();                                   \
+    }                                                                               \
+  } while (0)
+#else
+#define RIB200_STAMP(block, slot)                                                   \
+  do {                                                                              \
+  } while (0)
+#endif
 
 struct PrefillParams {
   const void *gate;
@@ -233,6 +258,11 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// 1 / (1 + e^-x) through ex2 and an approximate reciprocal (relative error ~1e-6, far below BF16 resolution)
+__device__ __forceinline__ float fast_sigmoid(float x) {
+  return __fdividef(1.0F, 1.0F + fast_exp2(x * -1.4426950408889634F));
+}
+
 __device__ __forceinline__ std::uint32_t pack_bf16(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const std::uint32_t *>(&v);
@@ -275,6 +305,23 @@ __global__ void __launch_bounds__(256) prefill_append_kernel(const void *key, co
 }
 
 // ---- attention ----------------------------------------------------------------------------------------
+// One persistent CTA per SM walks its share of the (query tile, head) list; the list is sorted by length and
+// dealt out in a snake so that every CTA gets about the same number of key blocks.
+struct TileWalk {
+  std::uint32_t tiles, total, stride, cta, iteration;
+  __device__ TileWalk(std::uint32_t tiles_, std::uint32_t stride_, std::uint32_t cta_)
+      : tiles(tiles_), total(tiles_ * kQueryHeads), stride(stride_), cta(cta_), iteration(0) {}
+  // position in the length-sorted list, or total when the walk is over
+  __device__ std::uint32_t position() const {
+    const std::uint32_t p = iteration * stride + ((iteration & 1U) ? stride - 1 - cta : cta);
+    return p < total ? p : total;
+  }
+  __device__ bool done() const { return position() >= total; }
+  __device__ std::uint32_t head() const { return position() % kQueryHeads; }
+  __device__ std::uint32_t tile() const { return tiles - 1 - position() / kQueryHeads; } // long tiles first
+  __device__ void next() { ++iteration; }
+};
+
 template <bool F32>
 __global__ void __launch_bounds__(kThreads, 1)
     prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
@@ -289,18 +336,17 @@ __global__ void __launch_bounds__(kThreads, 1)
   volatile std::uint32_t *abort_flag = tmem_slot + 1;
   auto bar = [&](int index) { return bars + static_cast<std::uint32_t>(index) * 8U; };
 
+#ifdef RIB200_TRACE
+  const long long cta_started = global_ns();
+  std::uint32_t traced_blocks = 0;
+#endif
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const std::uint32_t head = blockIdx.x;
-  const std::uint32_t tile = p.tiles - 1 - blockIdx.y; // long tiles first
-  const std::uint32_t kv_head = head / kGroup;
-  const std::uint32_t row0 = tile * kTileRows;                               // first query row of the tile
-  const std::uint32_t rows = min(static_cast<std::uint32_t>(kTileRows), p.tokens - row0);
-  const std::uint32_t last_pos = p.past + row0 + rows - 1;                   // newest key any row of the tile sees
-  const std::uint32_t blocks = last_pos / kBlockKeys + 1;
 
   if (threadIdx.x == 0) {
     mbar_init(bar(kBarQFull), F32 ? kSoftmaxThreads : 1);
+    mbar_init(bar(kBarQFree), 1);
+    mbar_init(bar(kBarOFree), kSoftmaxThreads);
     for (int s = 0; s < kSlots; ++s) {
       mbar_init(bar(kBarFull + s), 1);
       mbar_init(bar(kBarEmpty + s), 1);
@@ -327,53 +373,74 @@ __global__ void __launch_bounds__(kThreads, 1)
   const std::uint32_t tmem_o = tmem;         // columns [0, 256)
   const std::uint32_t tmem_s = tmem + 256;   // two tiles of 128 columns
 
+  // geometry of one tile
+  auto tile_rows = [&](std::uint32_t tile) {
+    return min(static_cast<std::uint32_t>(kTileRows), p.tokens - tile * kTileRows);
+  };
+  auto tile_blocks = [&](std::uint32_t tile) {
+    return (p.past + tile * kTileRows + tile_rows(tile) - 1) / kBlockKeys + 1; // newest visible key / 128 + 1
+  };
+
   if (warp == kProducerWarp) {
     // ================= producer =================
     if (lane == 0) {
-      if constexpr (!F32) {
-        mbar_expect_tx(bar(kBarQFull), kQBytes);
-        for (int b = 0; b < 4; ++b) {
-          tma_load_2d(q_smem + b * kQBoxBytes, &q_map, static_cast<int>(head * kHeadDim + b * kBoxCols),
-                      static_cast<int>(row0), bar(kBarQFull));
-        }
-      }
       // the cache rows of this chunk are written by the append kernel that precedes this launch
       asm volatile("griddepcontrol.wait;\n" ::: "memory");
       std::uint32_t n = 0; // running slot number; the MMA warp walks the same sequence
-      // K travels as two slots per block split by head dims (128 keys x 128 dims each, so that one MMA spans all
-      // 128 keys); V as two slots split by keys (64 keys x 256 dims each).
-      auto load_half = [&](bool is_value, std::uint32_t block, std::uint32_t half) {
-        const std::uint32_t slot = n % kSlots;
-        if (n >= kSlots) {
-          if (!mbar_wait(bar(kBarEmpty + slot), ((n / kSlots) - 1) & 1U, abort_flag)) {
-            return false;
-          }
-        }
-        mbar_expect_tx(bar(kBarFull + slot), kSlotBytes);
-        const std::uint32_t dst = ring + slot * kSlotBytes;
-        if (is_value) {
-          const int key0 = static_cast<int>(block * kBlockKeys + half * kHalfKeys);
-          for (int b = 0; b < 4; ++b) {
-            tma_load_3d(dst + b * kSlotBoxBytes, &v_map, b * kBoxCols, key0, static_cast<int>(kv_head),
-                        bar(kBarFull + slot));
-          }
-        } else {
-          const int key0 = static_cast<int>(block * kBlockKeys);
-          for (int b = 0; b < 2; ++b) {
-            tma_load_3d(dst + b * kKeyBoxBytes, &k_map, static_cast<int>((half * 2 + b) * kBoxCols), key0,
-                        static_cast<int>(kv_head), bar(kBarFull + slot));
-          }
-        }
-        ++n;
-        return true;
-      };
       bool ok = *abort_flag == 0;
-      ok = ok && load_half(false, 0, 0) && load_half(false, 0, 1);
-      for (std::uint32_t j = 0; ok && j < blocks; ++j) {
-        if (j + 1 < blocks) {
-          ok = load_half(false, j + 1, 0) && load_half(false, j + 1, 1);
+      for (TileWalk walk(p.tiles, gridDim.x, blockIdx.x); ok && !walk.done(); walk.next()) {
+        const std::uint32_t head = walk.head();
+        const std::uint32_t kv_head = head / kGroup;
+        const std::uint32_t row0 = walk.tile() * kTileRows;
+        const std::uint32_t blocks = tile_blocks(walk.tile());
+        if (walk.iteration > 0) {
+          // the previous tile's last score product has finished reading Q
+          ok = mbar_wait(bar(kBarQFree), (walk.iteration - 1) & 1U, abort_flag);
+          if (!ok) {
+            break;
+          }
         }
-        ok = ok && load_half(true, j, 0) && load_half(true, j, 1);
+        if constexpr (!F32) {
+          mbar_expect_tx(bar(kBarQFull), kQBytes);
+          for (int b = 0; b < 4; ++b) {
+            tma_load_2d(q_smem + b * kQBoxBytes, &q_map, static_cast<int>(head * kHeadDim + b * kBoxCols),
+                        static_cast<int>(row0), bar(kBarQFull));
+          }
+        }
+        // K travels as two slots per block split by head dims (128 keys x 128 dims each, so that one MMA spans
+        // all 128 keys); V as two slots split by keys (64 keys x 256 dims each).
+        auto load_half = [&](bool is_value, std::uint32_t block, std::uint32_t half) {
+          const std::uint32_t slot = n % kSlots;
+          if (n >= kSlots) {
+            if (!mbar_wait(bar(kBarEmpty + slot), ((n / kSlots) - 1) & 1U, abort_flag)) {
+              return false;
+            }
+          }
+          mbar_expect_tx(bar(kBarFull + slot), kSlotBytes);
+          const std::uint32_t dst = ring + slot * kSlotBytes;
+          if (is_value) {
+            const int key0 = static_cast<int>(block * kBlockKeys + half * kHalfKeys);
+            for (int b = 0; b < 4; ++b) {
+              tma_load_3d(dst + b * kSlotBoxBytes, &v_map, b * kBoxCols, key0, static_cast<int>(kv_head),
+                          bar(kBarFull + slot));
+            }
+          } else {
+            const int key0 = static_cast<int>(block * kBlockKeys);
+            for (int b = 0; b < 2; ++b) {
+              tma_load_3d(dst + b * kKeyBoxBytes, &k_map, static_cast<int>((half * 2 + b) * kBoxCols), key0,
+                          static_cast<int>(kv_head), bar(kBarFull + slot));
+            }
+          }
+          ++n;
+          return true;
+        };
+        ok = load_half(false, 0, 0) && load_half(false, 0, 1);
+        for (std::uint32_t j = 0; ok && j < blocks; ++j) {
+          if (j + 1 < blocks) {
+            ok = load_half(false, j + 1, 0) && load_half(false, j + 1, 1);
+          }
+          ok = ok && load_half(true, j, 0) && load_half(true, j, 1);
+        }
       }
     }
   } else if (warp == kMmaWarp) {
@@ -385,259 +452,345 @@ __global__ void __launch_bounds__(kThreads, 1)
       const std::uint64_t q_desc = smem_desc(q_smem, 16, 1024);
       const std::uint64_t k_desc = smem_desc(ring, 16, 1024);            // K-major, 8-row groups 1 KiB apart
       const std::uint64_t v_desc = smem_desc(ring, kSlotBoxBytes, 1024); // dim-major, 64-dim boxes 8 KiB apart
-      std::uint32_t n = 0;
-      bool ok = *abort_flag == 0 && mbar_wait(bar(kBarQFull), 0, abort_flag);
-      tcgen05_fence_after();
-      // S[block % 2] = Q K_block^T: two slots, each holding all 128 keys for half of the head dims
-      auto issue_qk = [&](std::uint32_t block) {
-        const std::uint32_t d = tmem_s + (block & 1U) * kBlockKeys;
-        for (std::uint32_t half = 0; half < 2 && ok; ++half) {
-          const std::uint32_t slot = n % kSlots;
-          ok = mbar_wait(bar(kBarFull + slot), (n / kSlots) & 1U, abort_flag);
-          if (!ok) {
-            break;
-          }
-          tcgen05_fence_after();
-          const std::uint64_t a0 = q_desc + ((half * 2 * kQBoxBytes) >> 4);
-          const std::uint64_t b0 = k_desc + ((slot * kSlotBytes) >> 4);
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {
-            const std::uint32_t a_off = ((ks >> 2) * kQBoxBytes + (ks & 3) * 32) >> 4;
-            const std::uint32_t b_off = ((ks >> 2) * kKeyBoxBytes + (ks & 3) * 32) >> 4;
-            umma_ss(d, a0 + a_off, b0 + b_off, kIdescQk, (half > 0 || ks > 0) ? 1U : 0U);
-          }
-          umma_commit(bar(kBarEmpty + slot));
-          ++n;
-        }
-        if (ok) {
-          umma_commit(bar(kBarSFull + (block & 1U)));
-        }
-      };
-      if (ok) {
-        issue_qk(0);
-      }
-      for (std::uint32_t j = 0; ok && j < blocks; ++j) {
-        if (j + 1 < blocks) {
-          issue_qk(j + 1);
-        }
-        if (!ok) {
-          break;
-        }
-        ok = mbar_wait(bar(kBarPFull + (j & 1U)), (j >> 1) & 1U, abort_flag);
+      std::uint32_t n = 0;  // running slot number
+      std::uint32_t g0 = 0; // running key-block number of the tile's first block (S buffer = block & 1)
+      bool ok = *abort_flag == 0;
+      for (TileWalk walk(p.tiles, gridDim.x, blockIdx.x); ok && !walk.done(); walk.next()) {
+        const std::uint32_t blocks = tile_blocks(walk.tile());
+        ok = mbar_wait(bar(kBarQFull), walk.iteration & 1U, abort_flag);
         if (!ok) {
           break;
         }
         tcgen05_fence_after();
-        // O += P_j V_j, P from tensor memory (BF16 pairs: 16 keys = 8 columns), V dim-major from the ring
-        for (std::uint32_t half = 0; half < 2 && ok; ++half) {
-          const std::uint32_t slot = n % kSlots;
-          ok = mbar_wait(bar(kBarFull + slot), (n / kSlots) & 1U, abort_flag);
+        // S[g & 1] = Q K_block^T: two slots, each holding all 128 keys for half of the head dims
+        auto issue_qk = [&](std::uint32_t j) {
+          const std::uint32_t g = g0 + j;
+          if (walk.iteration == 0) {
+            RIB200_STAMP(j, 0); // QK issue begins
+          }
+          const std::uint32_t d = tmem_s + (g & 1U) * kBlockKeys;
+          for (std::uint32_t half = 0; half < 2 && ok; ++half) {
+            const std::uint32_t slot = n % kSlots;
+            ok = mbar_wait(bar(kBarFull + slot), (n / kSlots) & 1U, abort_flag);
+            if (!ok) {
+              break;
+            }
+            tcgen05_fence_after();
+            const std::uint64_t a0 = q_desc + ((half * 2 * kQBoxBytes) >> 4);
+            const std::uint64_t b0 = k_desc + ((slot * kSlotBytes) >> 4);
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+              const std::uint32_t a_off = ((ks >> 2) * kQBoxBytes + (ks & 3) * 32) >> 4;
+              const std::uint32_t b_off = ((ks >> 2) * kKeyBoxBytes + (ks & 3) * 32) >> 4;
+              umma_ss(d, a0 + a_off, b0 + b_off, kIdescQk, (half > 0 || ks > 0) ? 1U : 0U);
+            }
+            umma_commit(bar(kBarEmpty + slot));
+            ++n;
+          }
+          if (ok) {
+            umma_commit(bar(kBarSFull + (g & 1U)));
+            if (j + 1 == blocks) {
+              umma_commit(bar(kBarQFree)); // the tile's last read of Q
+            }
+          }
+          if (walk.iteration == 0) {
+            RIB200_STAMP(j, 1); // QK issued
+          }
+        };
+        issue_qk(0);
+        for (std::uint32_t j = 0; ok && j < blocks; ++j) {
+          const std::uint32_t g = g0 + j;
+          if (j + 1 < blocks) {
+            issue_qk(j + 1);
+          }
           if (!ok) {
             break;
           }
-          tcgen05_fence_after();
-          const std::uint64_t b0 = v_desc + ((slot * kSlotBytes) >> 4);
-#pragma unroll
-          for (int ks = 0; ks < 4; ++ks) {
-            const std::uint32_t a = tmem_s + (j & 1U) * kBlockKeys + half * 32 + ks * 8;
-            umma_ts(tmem_o, a, b0 + ((ks * 2048) >> 4), kIdescPv, (j > 0 || half > 0 || ks > 0) ? 1U : 0U);
+          if (walk.iteration == 0) {
+            RIB200_STAMP(j, 2); // waiting for P
           }
-          umma_commit(bar(kBarEmpty + slot));
-          ++n;
+          ok = mbar_wait(bar(kBarPFull + (g & 1U)), (g >> 1) & 1U, abort_flag);
+          if (ok && j == 0 && walk.iteration > 0) {
+            // the first PV of a tile overwrites O: the previous tile's epilogue must have read it
+            ok = mbar_wait(bar(kBarOFree), (walk.iteration - 1) & 1U, abort_flag);
+          }
+          if (!ok) {
+            break;
+          }
+          if (walk.iteration == 0) {
+            RIB200_STAMP(j, 3); // P arrived
+          }
+          tcgen05_fence_after();
+          // O += P_j V_j, P from tensor memory (BF16 pairs: 16 keys = 8 columns), V dim-major from the ring
+          for (std::uint32_t half = 0; half < 2 && ok; ++half) {
+            const std::uint32_t slot = n % kSlots;
+            ok = mbar_wait(bar(kBarFull + slot), (n / kSlots) & 1U, abort_flag);
+            if (!ok) {
+              break;
+            }
+            tcgen05_fence_after();
+            const std::uint64_t b0 = v_desc + ((slot * kSlotBytes) >> 4);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+              const std::uint32_t a = tmem_s + (g & 1U) * kBlockKeys + half * 32 + ks * 8;
+              umma_ts(tmem_o, a, b0 + ((ks * 2048) >> 4), kIdescPv, (j > 0 || half > 0 || ks > 0) ? 1U : 0U);
+            }
+            umma_commit(bar(kBarEmpty + slot));
+            ++n;
+          }
+          if (ok) {
+            umma_commit(bar(kBarPvDone + (g & 1U)));
+          }
+          if (walk.iteration == 0) {
+            RIB200_STAMP(j, 4); // PV issued
+          }
         }
-        if (ok) {
-          umma_commit(bar(kBarPvDone + (j & 1U)));
-        }
+        g0 += blocks;
       }
     }
   } else {
     // ================= softmax, correction, epilogue =================
     // Two groups of four warps.  A thread owns one query row (tensor-memory lane 32 * (warp % 4) + lane) and the
     // 64 score columns of its group, so two threads share a row; they agree on the row maximum through shared
-    // memory once per block and keep separate partial row sums until the end.
+    // memory once per block and keep separate partial row sums until the end of the tile.
     const int group = warp >> 2;
     const std::uint32_t row = (warp & 3) * 32 + lane;
     const std::uint32_t lane_base = static_cast<std::uint32_t>((warp & 3) * 32) << 16;
-    const std::uint32_t q_pos = p.past + row0 + row; // position of this row's query (rows past the tile are idle)
     float *exchange = reinterpret_cast<float *>(smem + kExchangeOffset); // [parity][group][row]
     bool ok = *abort_flag == 0;
+    std::uint32_t g0 = 0;
 
-    if constexpr (F32) {
-      // FP32 queries: round to BF16 and lay the tile out by hand in the swizzled form TMA would have produced.
-      // Each group converts its 128 of the 256 dims.
-      const float *src = static_cast<const float *>(query_f32) +
-                         (static_cast<std::size_t>(row0 + row) * kQueryHeads + head) * kHeadDim;
-      const bool live = row < rows;
-#pragma unroll 4
-      for (int cc = 0; cc < 16; ++cc) { // 16 chunks of 8 dims
-        const int c = group * 16 + cc;
-        float4 a = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
-        float4 b = a;
-        if (live) {
-          a = *reinterpret_cast<const float4 *>(src + 8 * c);
-          b = *reinterpret_cast<const float4 *>(src + 8 * c + 4);
+    for (TileWalk walk(p.tiles, gridDim.x, blockIdx.x); ok && !walk.done(); walk.next()) {
+      const std::uint32_t head = walk.head();
+      const std::uint32_t row0 = walk.tile() * kTileRows;
+      const std::uint32_t rows = tile_rows(walk.tile());
+      const std::uint32_t blocks = tile_blocks(walk.tile());
+      const std::uint32_t q_pos = p.past + row0 + row; // position of this row's query (rows past the tile are idle)
+
+      if constexpr (F32) {
+        // FP32 queries: round to BF16 and lay the tile out by hand in the swizzled form TMA would have produced.
+        // Each group converts its 128 of the 256 dims.
+        if (walk.iteration > 0) {
+          ok = mbar_wait(bar(kBarQFree), (walk.iteration - 1) & 1U, abort_flag);
+          ok = __all_sync(0xFFFFFFFFU, ok);
+          if (!ok) {
+            break;
+          }
         }
-        uint4 raw;
-        raw.x = pack_bf16(a.x, a.y);
-        raw.y = pack_bf16(a.z, a.w);
-        raw.z = pack_bf16(b.x, b.y);
-        raw.w = pack_bf16(b.z, b.w);
-        const std::uint32_t box = c >> 3;
-        const std::uint32_t chunk = (c & 7) ^ (row & 7);
-        *reinterpret_cast<uint4 *>(smem + box * kQBoxBytes + row * 128 + chunk * 16) = raw;
+        const float *src = static_cast<const float *>(query_f32) +
+                           (static_cast<std::size_t>(row0 + row) * kQueryHeads + head) * kHeadDim;
+        const bool live = row < rows;
+#pragma unroll 4
+        for (int cc = 0; cc < 16; ++cc) { // 16 chunks of 8 dims
+          const int c = group * 16 + cc;
+          float4 a = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+          float4 b = a;
+          if (live) {
+            a = *reinterpret_cast<const float4 *>(src + 8 * c);
+            b = *reinterpret_cast<const float4 *>(src + 8 * c + 4);
+          }
+          uint4 raw;
+          raw.x = pack_bf16(a.x, a.y);
+          raw.y = pack_bf16(a.z, a.w);
+          raw.z = pack_bf16(b.x, b.y);
+          raw.w = pack_bf16(b.z, b.w);
+          const std::uint32_t box = c >> 3;
+          const std::uint32_t chunk = (c & 7) ^ (row & 7);
+          *reinterpret_cast<uint4 *>(smem + box * kQBoxBytes + row * 128 + chunk * 16) = raw;
+        }
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        mbar_arrive(bar(kBarQFull));
       }
-      asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-      mbar_arrive(bar(kBarQFull));
-    }
 
-    float m_used = -INFINITY; // maximum the exponentials are taken against (scaled, base 2); same in both groups
-    float l_sum = 0.0F;       // this thread's share of the row sum
-    for (std::uint32_t j = 0; j < blocks && ok; ++j) {
-      const std::uint32_t buf = j & 1U;
-      ok = mbar_wait(bar(kBarSFull + buf), (j >> 1) & 1U, abort_flag);
+      float m_used = -INFINITY; // maximum the exponentials are taken against (scaled, base 2); same in both groups
+      float l_sum = 0.0F;       // this thread's share of the row sum
+      for (std::uint32_t j = 0; j < blocks && ok; ++j) {
+        const std::uint32_t g = g0 + j;
+        const std::uint32_t buf = g & 1U;
+        if (threadIdx.x == 0 && walk.iteration == 0) {
+          RIB200_STAMP(j, 8); // softmax waits for S
+        }
+        ok = mbar_wait(bar(kBarSFull + buf), (g >> 1) & 1U, abort_flag);
+        ok = __all_sync(0xFFFFFFFFU, ok);
+        if (!ok) {
+          break;
+        }
+        if (threadIdx.x == 0 && walk.iteration == 0) {
+          RIB200_STAMP(j, 9); // S arrived
+        }
+        tcgen05_fence_after();
+        const std::uint32_t s_addr = tmem_s + lane_base + buf * kBlockKeys;
+        // raw scores (unscaled) of this group's 64 columns: both loads are in flight before the single wait
+        std::uint32_t xr[2][32];
+        tmem_ld32(s_addr + group * 64, xr[0]);
+        tmem_ld32(s_addr + group * 64 + 32, xr[1]);
+        tmem_wait_ld();
+        if (threadIdx.x == 0 && walk.iteration == 0) {
+          RIB200_STAMP(j, 10); // S in registers
+        }
+        float x[64];
+#pragma unroll
+        for (int e = 0; e < 64; ++e) {
+          x[e] = __uint_as_float(xr[e >> 5][e & 31]);
+        }
+        // causal mask: key position j*128 + c is visible iff <= q_pos (also hides rows the context never held)
+        const std::uint32_t key0 = j * kBlockKeys;
+        if (key0 + kBlockKeys - 1 > p.past + row0) {
+          const int visible = static_cast<int>(q_pos) - static_cast<int>(key0 + group * 64) + 1;
+#pragma unroll
+          for (int e = 0; e < 64; ++e) {
+            if (e >= visible) {
+              x[e] = -INFINITY;
+            }
+          }
+        }
+        float mx0 = fmaxf(x[0], x[1]);
+        float mx1 = fmaxf(x[2], x[3]);
+#pragma unroll
+        for (int e = 4; e < 64; e += 4) {
+          mx0 = fmaxf(mx0, fmaxf(x[e], x[e + 1]));
+          mx1 = fmaxf(mx1, fmaxf(x[e + 2], x[e + 3]));
+        }
+        const float mine = fmaxf(mx0, mx1);
+        exchange[(buf * 2 + group) * kTileRows + row] = mine;
+        asm volatile("bar.sync 1, 256;\n" ::: "memory");
+        const float theirs = exchange[(buf * 2 + (group ^ 1)) * kTileRows + row];
+        if (threadIdx.x == 0 && walk.iteration == 0) {
+          RIB200_STAMP(j, 11); // maxima exchanged
+        }
+        const float mx = fmaxf(mine, theirs) * kScaleLog2e; // the scale is positive: it commutes with the maximum
+        // move the reference maximum only when it fell far behind; block 0 always sets it
+        const bool move = mx > m_used + kRescaleThreshold;
+        if (__any_sync(0xFFFFFFFFU, move && j > 0)) {
+          // rescale this warp's 32 rows of O (this group's 128 columns); PV(j-1) must have landed
+          ok = mbar_wait(bar(kBarPvDone + ((g - 1) & 1U)), ((g - 1) >> 1) & 1U, abort_flag);
+          ok = __all_sync(0xFFFFFFFFU, ok);
+          if (!ok) {
+            break;
+          }
+          tcgen05_fence_after();
+          const float factor = move ? exp2f(m_used - mx) : 1.0F;
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            std::uint32_t v[32];
+            const std::uint32_t o_addr = tmem_o + lane_base + group * 128 + c * 32;
+            tmem_ld32(o_addr, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              v[e] = __float_as_uint(__uint_as_float(v[e]) * factor);
+            }
+            tmem_st32(o_addr, v);
+          }
+          tmem_wait_st();
+          l_sum *= factor;
+        }
+        if (move) {
+          m_used = mx;
+        }
+        // p = 2^(x * scale - m): one FMA and one ex2 per score; four partial sums
+        const float neg_m = -m_used;
+        float part0 = 0.0F;
+        float part1 = 0.0F;
+        float part2 = 0.0F;
+        float part3 = 0.0F;
+        std::uint32_t packed[32];
+#pragma unroll
+        for (int e = 0; e < 32; e += 2) {
+          const float p0 = fast_exp2(fmaf(x[2 * e], kScaleLog2e, neg_m));
+          const float p1 = fast_exp2(fmaf(x[2 * e + 1], kScaleLog2e, neg_m));
+          const float p2 = fast_exp2(fmaf(x[2 * e + 2], kScaleLog2e, neg_m));
+          const float p3 = fast_exp2(fmaf(x[2 * e + 3], kScaleLog2e, neg_m));
+          part0 += p0;
+          part1 += p1;
+          part2 += p2;
+          part3 += p3;
+          packed[e] = pack_bf16(p0, p1);
+          packed[e + 1] = pack_bf16(p2, p3);
+        }
+        if (threadIdx.x == 0 && walk.iteration == 0) {
+          RIB200_STAMP(j, 12); // exponentials done
+        }
+        tmem_st32(s_addr + group * 32, packed); // keys 64*group .. +63 are BF16 pairs in columns 32*group .. +31
+        l_sum += (part0 + part1) + (part2 + part3);
+        tmem_wait_st();
+        tcgen05_fence_before();
+        mbar_arrive(bar(kBarPFull + buf));
+        if (threadIdx.x == 0 && walk.iteration == 0) {
+          RIB200_STAMP(j, 13); // P published
+        }
+      }
+      if (!ok) {
+        break;
+      }
+
+      // ---- epilogue: out = O / l * sigmoid(gate); each group writes its 128 of the 256 columns ----
+      const std::uint32_t g_last = g0 + blocks - 1;
+      g0 += blocks;
+      const std::size_t out_base =
+          (static_cast<std::size_t>(row0 + row) * kQueryHeads + head) * kHeadDim + group * 128;
+      const bool live = row < rows;
+      uint4 gate_raw[16]; // BF16 gates of this thread's 128 columns, fetched while the last PV is still running
+      if constexpr (!F32) {
+        if (live) {
+          const uint4 *gp = reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.gate) + out_base);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            gate_raw[i] = gp[i];
+          }
+        }
+      }
+      ok = mbar_wait(bar(kBarPvDone + (g_last & 1U)), (g_last >> 1) & 1U, abort_flag);
       ok = __all_sync(0xFFFFFFFFU, ok);
       if (!ok) {
         break;
       }
       tcgen05_fence_after();
-      const std::uint32_t s_addr = tmem_s + lane_base + buf * kBlockKeys;
-      // raw scores (unscaled) of this group's 64 columns: both loads are in flight before the single wait
-      std::uint32_t xr[2][32];
-      tmem_ld32(s_addr + group * 64, xr[0]);
-      tmem_ld32(s_addr + group * 64 + 32, xr[1]);
-      tmem_wait_ld();
-      float x[64];
-#pragma unroll
-      for (int e = 0; e < 64; ++e) {
-        x[e] = __uint_as_float(xr[e >> 5][e & 31]);
-      }
-      // causal mask: key position j*128 + c is visible iff <= q_pos (also hides rows the context never held)
-      const std::uint32_t key0 = j * kBlockKeys;
-      if (key0 + kBlockKeys - 1 > p.past + row0) {
-        const int visible = static_cast<int>(q_pos) - static_cast<int>(key0 + group * 64) + 1;
-#pragma unroll
-        for (int e = 0; e < 64; ++e) {
-          if (e >= visible) {
-            x[e] = -INFINITY;
-          }
-        }
-      }
-      float mx0 = fmaxf(x[0], x[1]);
-      float mx1 = fmaxf(x[2], x[3]);
-#pragma unroll
-      for (int e = 4; e < 64; e += 4) {
-        mx0 = fmaxf(mx0, fmaxf(x[e], x[e + 1]));
-        mx1 = fmaxf(mx1, fmaxf(x[e + 2], x[e + 3]));
-      }
-      const float mine = fmaxf(mx0, mx1);
-      exchange[(buf * 2 + group) * kTileRows + row] = mine;
+      // The row sum is the two groups' shares.  They pass through the half of the exchange area that the next
+      // block to run (the first of the next tile) does not use; the first barrier makes sure the partner has
+      // finished reading this tile's last maximum from it.
+      const std::uint32_t sums = ((g0 & 1U) ^ 1U) * 2;
       asm volatile("bar.sync 1, 256;\n" ::: "memory");
-      const float theirs = exchange[(buf * 2 + (group ^ 1)) * kTileRows + row];
-      const float mx = fmaxf(mine, theirs) * kScaleLog2e; // the scale is positive, so it commutes with the maximum
-      // move the reference maximum only when it fell far behind; block 0 always sets it
-      const bool move = mx > m_used + kRescaleThreshold;
-      if (__any_sync(0xFFFFFFFFU, move && j > 0)) {
-        // rescale this warp's 32 rows of O (this group's 128 columns); PV(j-1) must have landed
-        ok = mbar_wait(bar(kBarPvDone + ((j - 1) & 1U)), ((j - 1) >> 1) & 1U, abort_flag);
-        ok = __all_sync(0xFFFFFFFFU, ok);
-        if (!ok) {
-          break;
-        }
-        tcgen05_fence_after();
-        const float factor = move ? exp2f(m_used - mx) : 1.0F;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          std::uint32_t v[32];
-          const std::uint32_t o_addr = tmem_o + lane_base + group * 128 + c * 32;
-          tmem_ld32(o_addr, v);
-          tmem_wait_ld();
+      exchange[(sums + group) * kTileRows + row] = l_sum;
+      asm volatile("bar.sync 1, 256;\n" ::: "memory");
+      const float inv = 1.0F / (l_sum + exchange[(sums + (group ^ 1)) * kTileRows + row]);
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            v[e] = __float_as_uint(__uint_as_float(v[e]) * factor);
-          }
-          tmem_st32(o_addr, v);
-        }
-        tmem_wait_st();
-        l_sum *= factor;
-      }
-      if (move) {
-        m_used = mx;
-      }
-      // p = 2^(x * scale - m): one FMA and one ex2 per score; four partial sums
-      const float neg_m = -m_used;
-      float part0 = 0.0F;
-      float part1 = 0.0F;
-      float part2 = 0.0F;
-      float part3 = 0.0F;
-      std::uint32_t packed[32];
-#pragma unroll
-      for (int e = 0; e < 32; e += 2) {
-        const float p0 = fast_exp2(fmaf(x[2 * e], kScaleLog2e, neg_m));
-        const float p1 = fast_exp2(fmaf(x[2 * e + 1], kScaleLog2e, neg_m));
-        const float p2 = fast_exp2(fmaf(x[2 * e + 2], kScaleLog2e, neg_m));
-        const float p3 = fast_exp2(fmaf(x[2 * e + 3], kScaleLog2e, neg_m));
-        part0 += p0;
-        part1 += p1;
-        part2 += p2;
-        part3 += p3;
-        packed[e] = pack_bf16(p0, p1);
-        packed[e + 1] = pack_bf16(p2, p3);
-      }
-      tmem_st32(s_addr + group * 32, packed); // keys 64*group .. +63 are BF16 pairs in columns 32*group .. +31
-      l_sum += (part0 + part1) + (part2 + part3);
-      tmem_wait_st();
-      tcgen05_fence_before();
-      mbar_arrive(bar(kBarPFull + buf));
-    }
-
-    // epilogue: out = O / l * sigmoid(gate); each group writes its 128 of the 256 columns
-    if (ok) {
-      ok = mbar_wait(bar(kBarPvDone + ((blocks - 1) & 1U)), ((blocks - 1) >> 1) & 1U, abort_flag);
-    }
-    ok = __all_sync(0xFFFFFFFFU, ok);
-    // the row sum is the two groups' shares, passed through the Q tile's memory: every MMA that read Q has
-    // completed by now (the last PV commit covers all earlier tensor work)
-    float *sums = reinterpret_cast<float *>(smem); // [group][row]
-    sums[group * kTileRows + row] = l_sum;
-    asm volatile("bar.sync 1, 256;\n" ::: "memory");
-    if (ok) {
-      tcgen05_fence_after();
-      const float inv = 1.0F / (l_sum + sums[(group ^ 1) * kTileRows + row]);
-      const std::size_t out_base =
-          (static_cast<std::size_t>(row0 + row) * kQueryHeads + head) * kHeadDim + group * 128;
-#pragma unroll 1
       for (int c = 0; c < 4; ++c) {
         std::uint32_t v[32];
         tmem_ld32(tmem_o + lane_base + group * 128 + c * 32, v);
         tmem_wait_ld();
-        if (row < rows) {
+        if (c == 3) {
+          // O has been read: the next tile's first PV may overwrite it
+          tcgen05_fence_before();
+          mbar_arrive(bar(kBarOFree));
+        }
+        if (live) {
           if constexpr (F32) {
-            const float *g = static_cast<const float *>(p.gate) + out_base + c * 32;
+            const float *gsrc = static_cast<const float *>(p.gate) + out_base + c * 32;
             float *o = static_cast<float *>(p.output) + out_base + c * 32;
 #pragma unroll
             for (int e = 0; e < 32; e += 4) {
-              const float4 gv = *reinterpret_cast<const float4 *>(g + e);
+              const float4 gv = *reinterpret_cast<const float4 *>(gsrc + e);
               float4 r;
-              r.x = __uint_as_float(v[e + 0]) * inv / (1.0F + expf(-gv.x));
-              r.y = __uint_as_float(v[e + 1]) * inv / (1.0F + expf(-gv.y));
-              r.z = __uint_as_float(v[e + 2]) * inv / (1.0F + expf(-gv.z));
-              r.w = __uint_as_float(v[e + 3]) * inv / (1.0F + expf(-gv.w));
+              r.x = __uint_as_float(v[e + 0]) * inv * fast_sigmoid(gv.x);
+              r.y = __uint_as_float(v[e + 1]) * inv * fast_sigmoid(gv.y);
+              r.z = __uint_as_float(v[e + 2]) * inv * fast_sigmoid(gv.z);
+              r.w = __uint_as_float(v[e + 3]) * inv * fast_sigmoid(gv.w);
               *reinterpret_cast<float4 *>(o + e) = r;
             }
           } else {
-            const __nv_bfloat16 *g = static_cast<const __nv_bfloat16 *>(p.gate) + out_base + c * 32;
             __nv_bfloat16 *o = static_cast<__nv_bfloat16 *>(p.output) + out_base + c * 32;
 #pragma unroll
             for (int e = 0; e < 32; e += 8) {
-              const uint4 gv = *reinterpret_cast<const uint4 *>(g + e);
+              const uint4 gv = gate_raw[c * 4 + e / 8];
               const std::uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
               std::uint32_t ow[4];
 #pragma unroll
               for (int h = 0; h < 4; ++h) {
-                const float g0 = __uint_as_float(gw[h] << 16);
-                const float g1 = __uint_as_float(gw[h] & 0xFFFF0000U);
-                const float r0 = __uint_as_float(v[e + 2 * h]) * inv / (1.0F + expf(-g0));
-                const float r1 = __uint_as_float(v[e + 2 * h + 1]) * inv / (1.0F + expf(-g1));
+                const float g0f = __uint_as_float(gw[h] << 16);
+                const float g1f = __uint_as_float(gw[h] & 0xFFFF0000U);
+                const float r0 = __uint_as_float(v[e + 2 * h]) * inv * fast_sigmoid(g0f);
+                const float r1 = __uint_as_float(v[e + 2 * h + 1]) * inv * fast_sigmoid(g1f);
                 ow[h] = pack_bf16(r0, r1);
               }
               *reinterpret_cast<uint4 *>(o + e) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
@@ -645,6 +798,9 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
       }
+#ifdef RIB200_TRACE
+      traced_blocks += blocks;
+#endif
     }
   }
 
@@ -653,11 +809,25 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (threadIdx.x == 0 && *abort_flag != 0) {
     atomicOr(p.status, static_cast<unsigned int>(RIB200_DEVICE_WAIT_TIMED_OUT));
   }
+#ifdef RIB200_TRACE
+  if (threadIdx.x == 0) {
+    const std::uint32_t id = blockIdx.x;
+    if (id < 1024) {
+      std::uint32_t smid;
+      asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+      g_cta_trace[id * 4 + 0] = cta_started;
+      g_cta_trace[id * 4 + 1] = global_ns();
+      g_cta_trace[id * 4 + 2] = traced_blocks;
+      g_cta_trace[id * 4 + 3] = smid;
+    }
+  }
+#endif
   if (warp == kMmaWarp) {
     tcgen05_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;\n" ::"r"(tmem) : "memory");
   }
 }
+
 
 // ---- host side ------------------------------------------------------------------------------------------
 using EncodeTiled = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -738,7 +908,12 @@ template <bool F32> void launch(const PrefillArgs &a, cudaStream_t stream) {
   params.status = device_status_word();
 
   cudaLaunchConfig_t config{};
-  config.gridDim = dim3(kQueryHeads, params.tiles, 1);
+  int device = 0;
+  int sm_count = 0;
+  cuda_ok(cudaGetDevice(&device), "cudaGetDevice");
+  cuda_ok(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device), "SM count query");
+  const std::uint32_t total_tiles = params.tiles * kQueryHeads;
+  config.gridDim = dim3(std::min<std::uint32_t>(total_tiles, static_cast<std::uint32_t>(sm_count)), 1, 1);
   config.blockDim = dim3(kThreads, 1, 1);
   config.dynamicSmemBytes = kSmemBytes;
   config.stream = stream;
@@ -752,6 +927,15 @@ template <bool F32> void launch(const PrefillArgs &a, cudaStream_t stream) {
 }
 
 } // namespace
+
+#ifdef RIB200_TRACE
+extern "C" int rib200_debug_read_trace(long long *host, std::size_t count) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host, g_trace, count * sizeof(long long)));
+}
+extern "C" int rib200_debug_read_cta_trace(long long *host, std::size_t count) {
+  return static_cast<int>(cudaMemcpyFromSymbol(host, g_cta_trace, count * sizeof(long long)));
+}
+#endif
 
 void launch_prefill_attention(const PrefillArgs &args, cudaStream_t stream) {
   require(args.tokens <= 65535U * kTileRows, "prefill attention: too many tokens for one launch");
