@@ -303,6 +303,11 @@ def main():
             from raftinfer_b200 import benchmarks
 
             line["extra"] = benchmarks.run(dev, stream, hbm_peak, tensor_peak)
+    if world > 1 and args.extras:
+        from raftinfer_b200 import benchmarks
+
+        extra = benchmarks.run_distributed(dev, stream, hbm_peak, tensor_peak, rank, world, dist)
+        line["extra"] = extra
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -11,6 +11,7 @@ import statistics
 import torch
 
 from . import kernels as K
+from .sharding import assign_sequences
 
 HQ, HKV, D = 16, 4, 256
 HK, HV, DK = 16, 32, 128
@@ -173,6 +174,113 @@ def run(dev, stream, hbm_peak, tensor_peak):
                      ("batched_serving_decode", lambda: batched_serving_decode(dev, stream, hbm_peak)),
                      ("gated_delta", lambda: gdn_layer(dev, stream, hbm_peak, tensor_peak)),
                      ("prefill_attention", lambda: prefill_attention(dev, stream, tensor_peak))):
+        try:
+            extra[name] = fn()
+        except (K.Qwen35PrimitiveError, K.Qwen35DeltaError) as err:
+            extra[name] = {"unavailable": str(err)}
+        torch.cuda.empty_cache()
+    return extra
+
+
+def _timed_max_over_ranks(fn, stream, dist, dev, warmup=3, reps=10):
+    """Median over `reps` of the slowest rank's CUDA-event time for fn(i); a barrier precedes every repetition."""
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    times = []
+    for i in range(reps):
+        dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        fn(i)
+        b.record(stream)
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b)], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        times.append(float(t.item()))
+    return statistics.median(times)
+
+
+def sharded_serving_decode(dev, stream, hbm_peak, rank, world, dist, batch=64, lo=1024, hi=32768, seed=0xB2000004):
+    """The 64-sequence ragged decode step with the sequences sharded over the ranks: no collective on the data
+    path, each rank steps its own sequences (attention + gated-delta decode)."""
+    cpu_gen = torch.Generator().manual_seed(seed)
+    lengths = torch.randint(lo, hi + 1, (batch,), generator=cpu_gen).tolist()
+    owner, load = assign_sequences(lengths, world)
+    mine = [n for n, r in zip(lengths, owner) if r == rank]
+    gen = torch.Generator(device=dev).manual_seed(seed + rank)
+    b = len(mine)
+    caps = [-(-n // 256) * 256 for n in mine]
+    largest = max(caps)
+    caches = [_bf16(gen, dev, 2, HKV, c, D) for c in caps]
+    ptrs = torch.tensor([c.data_ptr() for c in caches], device=dev, dtype=torch.int64)
+    dcaps = torch.tensor(caps, device=dev, dtype=torch.int32)
+    dpos = torch.tensor([n - 1 for n in mine], device=dev, dtype=torch.int32)
+    q, gate = _bf16(gen, dev, b, HQ, D), _bf16(gen, dev, b, HQ, D)
+    k, v = _bf16(gen, dev, b, HKV, D), _bf16(gen, dev, b, HKV, D)
+    o = torch.zeros(b, HQ, D, device=dev, dtype=torch.bfloat16)
+    ws_bytes = K.batched_decode_workspace_bytes(b, largest)
+    ws = torch.zeros(ws_bytes // 4, device=dev)
+    states = [torch.zeros(HV, DK, DK, device=dev) for _ in range(b)]
+    sptrs = torch.tensor([s.data_ptr() for s in states], device=dev, dtype=torch.int64)
+    gq = (torch.nn.functional.normalize(torch.randn(b, HK, DK, device=dev, generator=gen), dim=-1) / DK ** 0.5)
+    gk = torch.nn.functional.normalize(torch.randn(b, HK, DK, device=dev, generator=gen), dim=-1)
+    gq, gk, gv = gq.to(torch.bfloat16), gk.to(torch.bfloat16), _bf16(gen, dev, b, HV, DK)
+    beta = torch.sigmoid(torch.randn(b, HV, device=dev, generator=gen))
+    logd = -torch.nn.functional.softplus(torch.randn(b, HV, device=dev, generator=gen))
+    go = torch.zeros(b, HV, DK, device=dev)
+
+    def step(i):
+        K.batched_decode_attention(q, k, v, gate, o, ptrs, dcaps, dpos, b, largest, ws, ws_bytes, stream)
+        K.batched_gdn_decode(gq, gk, gv, beta, logd, sptrs, go, b, HK, HV, stream)
+
+    ms = _timed_max_over_ranks(step, stream, dist, dev)
+    nbytes = sum(4096 * n + 24576 for n in lengths) + batch * 2 * HV * DK * DK * 4
+    return {"sequences": batch, "ranks": world, "context_tokens_per_rank": load, "ms": ms, "bytes": nbytes,
+            "GB/s": nbytes / ms / 1e6, "frac_of_measured_hbm_all_ranks": nbytes / ms / 1e6 / (hbm_peak * world),
+            "collective": "none"}
+
+
+def head_split_prefill(dev, stream, tensor_peak, rank, world, dist, tokens=4096):
+    """Prefill split by KV-head group: a rank computes 16/world query heads (with 8 ranks two ranks share a KV
+    head, each holding a copy), then one NCCL all-gather assembles [tokens][16][256] on every rank."""
+    hq = HQ // world
+    hkv = max(1, HKV // world)
+    gen = torch.Generator(device=dev).manual_seed(23 + rank)
+    q, gate = _bf16(gen, dev, tokens, hq, D), _bf16(gen, dev, tokens, hq, D)
+    k, v = _bf16(gen, dev, tokens, hkv, D), _bf16(gen, dev, tokens, hkv, D)
+    cache = _bf16(gen, dev, 2, hkv, tokens, D)
+    local = torch.zeros(tokens, hq, D, device=dev, dtype=torch.bfloat16)
+    gathered = torch.zeros(world, tokens, hq, D, device=dev, dtype=torch.bfloat16)
+    full = torch.zeros(tokens, HQ, D, device=dev, dtype=torch.bfloat16)
+    shape = K.Qwen35AttentionShape(tokens, hq, hkv, D, tokens, 0)
+
+    def kernel_only(i):
+        K.qwen35_online_attention_prefill(q, k, v, gate, local, cache, cache.numel() * 2, shape, K.DTYPE_BF16, K.KV_BF16,
+                                          K.HEAD_MAJOR, stream)
+
+    def with_gather(i):
+        kernel_only(i)
+        dist.all_gather_into_tensor(gathered, local)
+        full.view(tokens, world, hq, D).copy_(gathered.permute(1, 0, 2, 3))
+
+    flops = 4 * HQ * D * (tokens * (tokens + 1) // 2)
+    ms_kernel = _timed_max_over_ranks(kernel_only, stream, dist, dev)
+    ms_total = _timed_max_over_ranks(with_gather, stream, dist, dev)
+    return {"tokens": tokens, "ranks": world, "query_heads_per_rank": hq, "kv_heads_per_rank": hkv,
+            "ms_kernel": ms_kernel, "ms_with_all_gather": ms_total, "flops": flops,
+            "TFLOP/s": flops / ms_total / 1e9, "TFLOP/s_kernel_only": flops / ms_kernel / 1e9,
+            "frac_of_measured_bf16_peak_all_ranks": flops / ms_total / 1e9 / (tensor_peak * world),
+            "collective": "ncclAllGather of outputs + layout permute",
+            "all_gather_bytes_per_rank": tokens * hq * D * 2}
+
+
+def run_distributed(dev, stream, hbm_peak, tensor_peak, rank, world, dist):
+    """Sections that need every rank (called by bench.py under torchrun)."""
+    extra = {}
+    for name, fn in (("sharded_serving_decode", lambda: sharded_serving_decode(dev, stream, hbm_peak, rank, world, dist)),
+                     ("head_split_prefill", lambda: head_split_prefill(dev, stream, tensor_peak, rank, world, dist))):
         try:
             extra[name] = fn()
         except (K.Qwen35PrimitiveError, K.Qwen35DeltaError) as err:

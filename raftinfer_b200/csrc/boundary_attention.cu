@@ -220,8 +220,8 @@ void online_prefill(const void *query, const void *key, const void *value, const
           "online attention: KV cache is too small");
   unsupported(cache_dtype == RIB200_KV_CACHE_BF16 && cache_layout == RIB200_KV_LAYOUT_HEAD_MAJOR,
               "online attention: this library serves the BF16 head-major KV cache only");
-  unsupported(s.query_heads == kModelQueryHeads && s.kv_heads == kModelKvHeads && s.head_dim == kModelHeadDim,
-              "online attention: prefill is built for 16 query heads, 4 kv heads, head_dim 256");
+  unsupported(s.head_dim == kModelHeadDim && s.query_heads <= 1024,
+              "online attention: prefill is built for head_dim 256");
   require_aligned16(query, "online attention: query is not 16-byte aligned");
   require_aligned16(key, "online attention: key is not 16-byte aligned");
   require_aligned16(value, "online attention: value is not 16-byte aligned");
@@ -238,6 +238,8 @@ void online_prefill(const void *query, const void *key, const void *value, const
   args.tokens = static_cast<std::uint32_t>(s.tokens);
   args.past_tokens = static_cast<std::uint32_t>(s.past_tokens);
   args.max_context_tokens = static_cast<std::uint32_t>(s.max_context_tokens);
+  args.query_heads = static_cast<std::uint32_t>(s.query_heads);
+  args.kv_heads = static_cast<std::uint32_t>(s.kv_heads);
   args.activations_f32 = activation_dtype == RIB200_DTYPE_F32;
   launch_prefill_attention(args, stream);
 }
@@ -376,9 +378,8 @@ Rib200Status rib200_online_attention_prefill_supported(const Rib200AttentionShap
     *supported = policy.implementation == RIB200_ATTENTION_ONLINE_TILED &&
                          prefill_signature_ok(s, activation_dtype, policy.kv_cache_dtype, policy.kv_cache_layout) &&
                          policy.kv_cache_dtype == RIB200_KV_CACHE_BF16 &&
-                         policy.kv_cache_layout == RIB200_KV_LAYOUT_HEAD_MAJOR &&
-                         s.query_heads == kModelQueryHeads && s.kv_heads == kModelKvHeads &&
-                         s.head_dim == kModelHeadDim
+                         policy.kv_cache_layout == RIB200_KV_LAYOUT_HEAD_MAJOR && s.head_dim == kModelHeadDim &&
+                         s.query_heads <= 1024
                      ? 1
                      : 0;
   });

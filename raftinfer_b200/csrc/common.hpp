@@ -104,15 +104,17 @@ void launch_batched_decode_attention(const BatchedDecodeArgs &args, cudaStream_t
 
 // ---- prefill attention (prefill_attention.cu) -----------------------------------------------
 struct PrefillArgs {
-  const void *query;  // [tokens][16][256] activation dtype
-  const void *key;    // [tokens][4][256]
-  const void *value;  // [tokens][4][256]
-  const void *gate;   // [tokens][16][256]
-  void *output;       // [tokens][16][256]
-  void *kv_cache;     // bf16 [2][4][max_ctx][256]
+  const void *query;  // [tokens][query_heads][256] activation dtype
+  const void *key;    // [tokens][kv_heads][256]
+  const void *value;  // [tokens][kv_heads][256]
+  const void *gate;   // [tokens][query_heads][256]
+  void *output;       // [tokens][query_heads][256]
+  void *kv_cache;     // bf16 [2][kv_heads][max_ctx][256]
   std::uint32_t tokens;
   std::uint32_t past_tokens;
   std::uint32_t max_context_tokens;
+  std::uint32_t query_heads;
+  std::uint32_t kv_heads;
   bool activations_f32;
 };
 void launch_prefill_attention(const PrefillArgs &args, cudaStream_t stream);

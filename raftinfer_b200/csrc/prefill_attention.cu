@@ -42,9 +42,8 @@ namespace rib200 {
 namespace {
 
 constexpr int kHeadDim = 256;
-constexpr int kQueryHeads = 16;
-constexpr int kKvHeads = 4;
-constexpr int kGroup = kQueryHeads / kKvHeads;
+// Head counts are run-time values (the reference's prefill takes any query_heads that is a multiple of kv_heads,
+// cpp/kernels/qwen35_online_attention.cu:33-44), which is also what a head-sharded rank passes: its own slice.
 constexpr int kTileRows = 128;  // query rows per CTA
 constexpr int kBlockKeys = 128; // keys per score tile
 constexpr int kHalfKeys = 64;   // keys per ring slot
@@ -108,6 +107,8 @@ struct PrefillParams {
   std::uint32_t tokens;
   std::uint32_t past;
   std::uint32_t tiles;
+  std::uint32_t query_heads;
+  std::uint32_t group; // query heads per KV head
   unsigned int *status;
 };
 
@@ -272,10 +273,11 @@ __device__ __forceinline__ std::uint32_t pack_bf16(float lo, float hi) {
 template <bool F32>
 __global__ void __launch_bounds__(256) prefill_append_kernel(const void *key, const void *value,
                                                              __nv_bfloat16 *cache, std::uint32_t tokens,
-                                                             std::uint32_t past, std::uint32_t max_ctx) {
+                                                             std::uint32_t past, std::uint32_t max_ctx,
+                                                             std::uint32_t kv_heads) {
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   // one thread per 8 elements: [plane][token][kv head][32 pieces of 8]
-  const std::size_t pieces = static_cast<std::size_t>(tokens) * kKvHeads * 32;
+  const std::size_t pieces = static_cast<std::size_t>(tokens) * kv_heads * 32;
   const std::size_t id = static_cast<std::size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (id >= 2 * pieces) {
     return;
@@ -283,9 +285,9 @@ __global__ void __launch_bounds__(256) prefill_append_kernel(const void *key, co
   const bool is_value = id >= pieces;
   const std::size_t local = is_value ? id - pieces : id;
   const std::uint32_t piece = static_cast<std::uint32_t>(local % 32);
-  const std::uint32_t head = static_cast<std::uint32_t>((local / 32) % kKvHeads);
-  const std::uint32_t token = static_cast<std::uint32_t>(local / (32 * kKvHeads));
-  const std::size_t src = (static_cast<std::size_t>(token) * kKvHeads + head) * kHeadDim + piece * 8;
+  const std::uint32_t head = static_cast<std::uint32_t>((local / 32) % kv_heads);
+  const std::uint32_t token = static_cast<std::uint32_t>(local / (32 * kv_heads));
+  const std::size_t src = (static_cast<std::size_t>(token) * kv_heads + head) * kHeadDim + piece * 8;
   const void *base = is_value ? value : key;
   uint4 raw;
   if constexpr (F32) {
@@ -298,7 +300,7 @@ __global__ void __launch_bounds__(256) prefill_append_kernel(const void *key, co
   } else {
     raw = *reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(base) + src);
   }
-  const std::size_t plane = static_cast<std::size_t>(kKvHeads) * max_ctx * kHeadDim;
+  const std::size_t plane = static_cast<std::size_t>(kv_heads) * max_ctx * kHeadDim;
   const std::size_t dst = (is_value ? plane : 0) + (static_cast<std::size_t>(head) * max_ctx + past + token) * kHeadDim +
                           piece * 8;
   *reinterpret_cast<uint4 *>(cache + dst) = raw;
@@ -308,17 +310,17 @@ __global__ void __launch_bounds__(256) prefill_append_kernel(const void *key, co
 // One persistent CTA per SM walks its share of the (query tile, head) list; the list is sorted by length and
 // dealt out in a snake so that every CTA gets about the same number of key blocks.
 struct TileWalk {
-  std::uint32_t tiles, total, stride, cta, iteration;
-  __device__ TileWalk(std::uint32_t tiles_, std::uint32_t stride_, std::uint32_t cta_)
-      : tiles(tiles_), total(tiles_ * kQueryHeads), stride(stride_), cta(cta_), iteration(0) {}
+  std::uint32_t tiles, heads, total, stride, cta, iteration;
+  __device__ TileWalk(std::uint32_t tiles_, std::uint32_t heads_, std::uint32_t stride_, std::uint32_t cta_)
+      : tiles(tiles_), heads(heads_), total(tiles_ * heads_), stride(stride_), cta(cta_), iteration(0) {}
   // position in the length-sorted list, or total when the walk is over
   __device__ std::uint32_t position() const {
     const std::uint32_t p = iteration * stride + ((iteration & 1U) ? stride - 1 - cta : cta);
     return p < total ? p : total;
   }
   __device__ bool done() const { return position() >= total; }
-  __device__ std::uint32_t head() const { return position() % kQueryHeads; }
-  __device__ std::uint32_t tile() const { return tiles - 1 - position() / kQueryHeads; } // long tiles first
+  __device__ std::uint32_t head() const { return position() % heads; }
+  __device__ std::uint32_t tile() const { return tiles - 1 - position() / heads; } // long tiles first
   __device__ void next() { ++iteration; }
 };
 
@@ -388,9 +390,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       asm volatile("griddepcontrol.wait;\n" ::: "memory");
       std::uint32_t n = 0; // running slot number; the MMA warp walks the same sequence
       bool ok = *abort_flag == 0;
-      for (TileWalk walk(p.tiles, gridDim.x, blockIdx.x); ok && !walk.done(); walk.next()) {
+      for (TileWalk walk(p.tiles, p.query_heads, gridDim.x, blockIdx.x); ok && !walk.done(); walk.next()) {
         const std::uint32_t head = walk.head();
-        const std::uint32_t kv_head = head / kGroup;
+        const std::uint32_t kv_head = head / p.group;
         const std::uint32_t row0 = walk.tile() * kTileRows;
         const std::uint32_t blocks = tile_blocks(walk.tile());
         if (walk.iteration > 0) {
@@ -455,7 +457,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       std::uint32_t n = 0;  // running slot number
       std::uint32_t g0 = 0; // running key-block number of the tile's first block (S buffer = block & 1)
       bool ok = *abort_flag == 0;
-      for (TileWalk walk(p.tiles, gridDim.x, blockIdx.x); ok && !walk.done(); walk.next()) {
+      for (TileWalk walk(p.tiles, p.query_heads, gridDim.x, blockIdx.x); ok && !walk.done(); walk.next()) {
         const std::uint32_t blocks = tile_blocks(walk.tile());
         ok = mbar_wait(bar(kBarQFull), walk.iteration & 1U, abort_flag);
         if (!ok) {
@@ -560,7 +562,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     bool ok = *abort_flag == 0;
     std::uint32_t g0 = 0;
 
-    for (TileWalk walk(p.tiles, gridDim.x, blockIdx.x); ok && !walk.done(); walk.next()) {
+    for (TileWalk walk(p.tiles, p.query_heads, gridDim.x, blockIdx.x); ok && !walk.done(); walk.next()) {
       const std::uint32_t head = walk.head();
       const std::uint32_t row0 = walk.tile() * kTileRows;
       const std::uint32_t rows = tile_rows(walk.tile());
@@ -578,7 +580,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
         const float *src = static_cast<const float *>(query_f32) +
-                           (static_cast<std::size_t>(row0 + row) * kQueryHeads + head) * kHeadDim;
+                           (static_cast<std::size_t>(row0 + row) * p.query_heads + head) * kHeadDim;
         const bool live = row < rows;
 #pragma unroll 4
         for (int cc = 0; cc < 16; ++cc) { // 16 chunks of 8 dims
@@ -728,7 +730,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       const std::uint32_t g_last = g0 + blocks - 1;
       g0 += blocks;
       const std::size_t out_base =
-          (static_cast<std::size_t>(row0 + row) * kQueryHeads + head) * kHeadDim + group * 128;
+          (static_cast<std::size_t>(row0 + row) * p.query_heads + head) * kHeadDim + group * 128;
       const bool live = row < rows;
       uint4 gate_raw[16]; // BF16 gates of this thread's 128 columns, fetched while the last PV is still running
       if constexpr (!F32) {
@@ -875,26 +877,26 @@ template <bool F32> void configure_once() {
 template <bool F32> void launch(const PrefillArgs &a, cudaStream_t stream) {
   configure_once<F32>();
   auto *cache = static_cast<__nv_bfloat16 *>(a.kv_cache);
-  const std::size_t pieces = static_cast<std::size_t>(a.tokens) * kKvHeads * 32 * 2;
+  const std::size_t pieces = static_cast<std::size_t>(a.tokens) * a.kv_heads * 32 * 2;
   prefill_append_kernel<F32><<<static_cast<unsigned int>((pieces + 255) / 256), 256, 0, stream>>>(
-      a.key, a.value, cache, a.tokens, a.past_tokens, a.max_context_tokens);
+      a.key, a.value, cache, a.tokens, a.past_tokens, a.max_context_tokens, a.kv_heads);
   cuda_ok(cudaGetLastError(), "prefill append launch");
 
   const std::uint64_t context = static_cast<std::uint64_t>(a.past_tokens) + a.tokens;
   // K / V: [kv head][row < context][256], rows 512 bytes apart, heads max_ctx rows apart
-  const cuuint64_t kv_dims[3] = {kHeadDim, context, kKvHeads};
+  const cuuint64_t kv_dims[3] = {kHeadDim, context, a.kv_heads};
   const cuuint64_t kv_strides[2] = {kHeadDim * 2, static_cast<cuuint64_t>(a.max_context_tokens) * kHeadDim * 2};
   const cuuint32_t k_box[3] = {kBoxCols, kBlockKeys, 1};
   const cuuint32_t kv_box[3] = {kBoxCols, kHalfKeys, 1};
   const CUtensorMap k_map = make_map(cache, 3, kv_dims, kv_strides, k_box);
   const CUtensorMap v_map =
-      make_map(cache + static_cast<std::size_t>(kKvHeads) * a.max_context_tokens * kHeadDim, 3, kv_dims, kv_strides,
+      make_map(cache + static_cast<std::size_t>(a.kv_heads) * a.max_context_tokens * kHeadDim, 3, kv_dims, kv_strides,
                kv_box);
   // Q: [token][16 * 256] (BF16 activations only; FP32 queries are converted inside the kernel)
   CUtensorMap q_map = k_map;
   if (!F32) {
-    const cuuint64_t q_dims[2] = {kQueryHeads * kHeadDim, a.tokens};
-    const cuuint64_t q_strides[1] = {kQueryHeads * kHeadDim * 2};
+    const cuuint64_t q_dims[2] = {static_cast<cuuint64_t>(a.query_heads) * kHeadDim, a.tokens};
+    const cuuint64_t q_strides[1] = {static_cast<cuuint64_t>(a.query_heads) * kHeadDim * 2};
     const cuuint32_t q_box[2] = {kBoxCols, kTileRows};
     q_map = make_map(const_cast<void *>(a.query), 2, q_dims, q_strides, q_box);
   }
@@ -905,6 +907,8 @@ template <bool F32> void launch(const PrefillArgs &a, cudaStream_t stream) {
   params.tokens = a.tokens;
   params.past = a.past_tokens;
   params.tiles = (a.tokens + kTileRows - 1) / kTileRows;
+  params.query_heads = a.query_heads;
+  params.group = a.query_heads / a.kv_heads;
   params.status = device_status_word();
 
   cudaLaunchConfig_t config{};
@@ -912,7 +916,7 @@ template <bool F32> void launch(const PrefillArgs &a, cudaStream_t stream) {
   int sm_count = 0;
   cuda_ok(cudaGetDevice(&device), "cudaGetDevice");
   cuda_ok(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device), "SM count query");
-  const std::uint32_t total_tiles = params.tiles * kQueryHeads;
+  const std::uint32_t total_tiles = params.tiles * a.query_heads;
   config.gridDim = dim3(std::min<std::uint32_t>(total_tiles, static_cast<std::uint32_t>(sm_count)), 1, 1);
   config.blockDim = dim3(kThreads, 1, 1);
   config.dynamicSmemBytes = kSmemBytes;

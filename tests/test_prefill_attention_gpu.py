@@ -133,3 +133,31 @@ def test_full_4096_token_prefill_on_sampled_rows():
 
 def test_drop_in_chunk_512_after_3584_past():
     run_prefill(512, 3584, 4096, K.DTYPE_BF16, seed=0xB2004700, rows_to_check=[(0, 64), (448, 512)])
+
+
+@pytest.mark.parametrize("hq,hkv", [(8, 2), (2, 1), (3, 3), (12, 4), (4, 1)])
+def test_other_head_counts(hq, hkv):
+    """The prefill signature takes any query_heads that is a multiple of kv_heads (reference
+    cpp/kernels/qwen35_online_attention.cu:33-44); a head-sharded rank passes exactly such a slice."""
+    tokens, past, max_ctx, seed = 150, 20, 256, 0xB2004800 + hq * 16 + hkv
+    q = synth.round_bf16(synth.normal(seed, 0, (tokens, hq, D)))
+    gate = synth.round_bf16(synth.normal(seed, 1, (tokens, hq, D)))
+    k = synth.round_bf16(synth.normal(seed, 2, (past + tokens, hkv, D)))
+    v = synth.round_bf16(synth.normal(seed, 3, (past + tokens, hkv, D)))
+    cache_bits = np.full((2, hkv, max_ctx, D), 0x7FC1, dtype=np.uint16)
+    cache_bits[0, :, :past] = synth.bf16_bits(k[:past]).transpose(1, 0, 2)
+    cache_bits[1, :, :past] = synth.bf16_bits(v[:past]).transpose(1, 0, 2)
+    cache = cache_to_device(cache_bits)
+    out = torch.zeros(tokens, hq, D, device=dev(), dtype=torch.bfloat16)
+    shape = K.Qwen35AttentionShape(tokens, hq, hkv, D, max_ctx, past)
+    assert K.qwen35_online_attention_prefill_supported(shape, K.DTYPE_BF16, POLICY)
+    K.qwen35_online_attention_prefill(act_tensor(q, K.DTYPE_BF16), act_tensor(k[past:], K.DTYPE_BF16),
+                                      act_tensor(v[past:], K.DTYPE_BF16), act_tensor(gate, K.DTYPE_BF16), out, cache,
+                                      cache.numel() * 2, shape, K.DTYPE_BF16, K.KV_BF16, K.HEAD_MAJOR,
+                                      torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    want = ob.attention_core(q, k, v, gate, past=past)
+    gate_bf16_outputs(compare(to_numpy_f32(out), want))
+    got_cache = cache_bits_of(cache).reshape(cache_bits.shape)
+    assert np.array_equal(got_cache[0, :, past:past + tokens], synth.bf16_bits(k[past:]).transpose(1, 0, 2))
+    assert np.array_equal(got_cache[:, :, past + tokens:], cache_bits[:, :, past + tokens:])
