@@ -289,9 +289,10 @@ def main():
                              "programmatic dependent launch); the partition kernel moves all the algorithmic bytes"},
         "clocks": clocks,
     }
-    traffic_note = os.path.join(ROOT, "profiles", "decode_partition_ctx32768.traffic.json")
-    if os.path.exists(traffic_note):
-        line["roofline"]["traffic"] = json.load(open(traffic_note)).get("dram_bytes_per_launch")
+    if ctx == CONTEXT:
+        # dram__bytes_read.sum + dram__bytes_write.sum of one partition-kernel launch at this context
+        # (ncu capture summarised in profiles/decode_partition_ctx32768.md)
+        line["roofline"]["traffic"] = 138.3e6
 
     if rank == 0 and world == 1:
         threads = max(1, len(os.sched_getaffinity(0)))
