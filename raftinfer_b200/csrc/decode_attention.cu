@@ -560,7 +560,7 @@ __global__ void __launch_bounds__(T::kWarps * 32, T::kCtasPerSm) decode_partitio
 // groups of sixteen lanes, a lane owning four consecutive dims of the quarter.
 template <bool F32, bool Batched>
 __global__ void __launch_bounds__(256) decode_combine_kernel(const DecodeParams p) {
-  __shared__ float red[8];
+  __shared__ float group_max[16];
   __shared__ float group_sum[16];
   __shared__ float group_acc[16][64];
 
@@ -593,51 +593,48 @@ __global__ void __launch_bounds__(256) decode_combine_kernel(const DecodeParams 
   const float *pval = p.partial_value +
                       (act_seq * p.partial_stride + static_cast<std::size_t>(head) * p.max_partitions) * kHeadDim;
 
-  const int lane = threadIdx.x & 31;
-  const int warp = threadIdx.x >> 5;
-  float local_max = -INFINITY;
-  for (std::uint32_t i = threadIdx.x; i < parts; i += 256) {
-    local_max = fmaxf(local_max, pmax[i]);
-  }
-#pragma unroll
-  for (int offset = 16; offset > 0; offset >>= 1) {
-    local_max = fmaxf(local_max, __shfl_xor_sync(0xFFFFFFFFU, local_max, offset));
-  }
-  if (lane == 0) {
-    red[warp] = local_max;
-  }
-  __syncthreads();
-  float total_max = red[0];
-#pragma unroll
-  for (int w = 1; w < 8; ++w) {
-    total_max = fmaxf(total_max, red[w]);
-  }
-
+  // One pass: every thread folds its share of the partials into a running (max, sum, acc) - all loads of the
+  // pass are independent, so they are in flight together - then the sixteen groups are folded in shared memory.
   const int group = threadIdx.x >> 4;
   const int sub = threadIdx.x & 15;
-  float sum = 0.0F;
+  float run_max = -INFINITY;
+  float run_sum = 0.0F;
   float4 acc = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+#pragma unroll 4
   for (std::uint32_t i = group; i < parts; i += 16) {
-    const float weight = exp2f((pmax[i] - total_max) * kLog2e);
-    sum += psum[i] * weight;
-    const float4 v = *reinterpret_cast<const float4 *>(pval + static_cast<std::size_t>(i) * kHeadDim + quarter * 64 + sub * 4);
-    acc.x += v.x * weight;
-    acc.y += v.y * weight;
-    acc.z += v.z * weight;
-    acc.w += v.w * weight;
+    const float part_max = pmax[i];
+    const float part_sum = psum[i];
+    const float4 v =
+        *reinterpret_cast<const float4 *>(pval + static_cast<std::size_t>(i) * kHeadDim + quarter * 64 + sub * 4);
+    const float new_max = fmaxf(run_max, part_max);
+    const float keep = exp2f((run_max - new_max) * kLog2e);
+    const float take = exp2f((part_max - new_max) * kLog2e);
+    run_sum = run_sum * keep + part_sum * take;
+    acc.x = acc.x * keep + v.x * take;
+    acc.y = acc.y * keep + v.y * take;
+    acc.z = acc.z * keep + v.z * take;
+    acc.w = acc.w * keep + v.w * take;
+    run_max = new_max;
   }
   if (sub == 0) {
-    group_sum[group] = sum;
+    group_max[group] = run_max;
+    group_sum[group] = run_sum;
   }
   *reinterpret_cast<float4 *>(&group_acc[group][sub * 4]) = acc;
   __syncthreads();
   if (threadIdx.x < 64) {
+    float total_max = group_max[0];
+#pragma unroll
+    for (int gidx = 1; gidx < 16; ++gidx) {
+      total_max = fmaxf(total_max, group_max[gidx]);
+    }
     float total_sum = 0.0F;
     float total = 0.0F;
 #pragma unroll
     for (int gidx = 0; gidx < 16; ++gidx) {
-      total_sum += group_sum[gidx];
-      total += group_acc[gidx][threadIdx.x];
+      const float weight = exp2f((group_max[gidx] - total_max) * kLog2e); // 0 for a group that had no partial
+      total_sum += group_sum[gidx] * weight;
+      total += group_acc[gidx][threadIdx.x] * weight;
     }
     const std::size_t out_index = (act_seq * kQueryHeads + head) * kHeadDim + quarter * 64 + threadIdx.x;
     if constexpr (F32) {

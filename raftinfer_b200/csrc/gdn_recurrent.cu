@@ -18,6 +18,10 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <algorithm>
+#include <cstdint>
+#include <mutex>
+
 namespace rib200 {
 namespace {
 
@@ -126,6 +130,157 @@ __global__ void __launch_bounds__(256, 4) gdn_recurrent_kernel(const RecurrentPa
   }
 }
 
+// Batched decode step: one token for each of many sequences.  A CTA of sixteen warps owns one value head for a
+// strided share of the sequences.  The head's whole 64 KiB state - one contiguous block of memory - streams through
+// a three-stage cp.async ring in shared memory, so the next sequences' states are in flight while the current one
+// is updated; the update is written back into its stage and leaves as full 512-byte rows.  (Splitting a head's
+// columns over two CTAs, as the single-sequence kernel does, makes each of them touch only half of every DRAM
+// page and costs about half of the bandwidth.)  A warp owns 8 state columns, a lane the rows lane, lane+32,
+// lane+64, lane+96; rows sit at a 528-byte pitch, which keeps the 16-byte shared-memory accesses conflict-free.
+constexpr int kStagePitch = 528;                     // bytes per state row in shared memory (512 + 16)
+constexpr int kStageBytes = kDim * kStagePitch;      // 67 584
+constexpr int kStages = 3;
+constexpr int kBatchedThreads = 512;
+constexpr int kBatchedSmemBytes = kStages * kStageBytes;
+
+__device__ __forceinline__ void cp_async_16(std::uint32_t dst, const void *src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+}
+
+__global__ void __launch_bounds__(kBatchedThreads, 1)
+    gdn_batched_decode_kernel(const RecurrentParams p, std::uint32_t sequences) {
+  extern __shared__ __align__(16) unsigned char ring[];
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const std::uint32_t head = blockIdx.x;
+  const std::uint32_t key_head = head % p.key_heads;
+  const int col0 = warp * 8;
+  const std::uint32_t first = blockIdx.y;
+  const std::uint32_t step = gridDim.y;
+  const std::uint32_t count = first < sequences ? (sequences - first + step - 1) / step : 0;
+  const std::uint32_t ring_base = static_cast<std::uint32_t>(__cvta_generic_to_shared(ring));
+
+  // copy the head's 128 x 128 state of this CTA's n-th sequence into stage n % kStages
+  auto issue = [&](std::uint32_t n) {
+    const std::uint32_t seq = first + n * step;
+    const float *src = p.states[seq] + static_cast<std::size_t>(head) * kDim * kDim;
+    const std::uint32_t dst = ring_base + (n % kStages) * kStageBytes;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int idx = threadIdx.x + i * kBatchedThreads; // 4096 chunks of 16 bytes
+      const int row = idx >> 5;
+      const int chunk = idx & 31;
+      cp_async_16(dst + row * kStagePitch + chunk * 16, src + row * kDim + chunk * 4);
+    }
+  };
+
+#pragma unroll
+  for (int n = 0; n < kStages - 1; ++n) {
+    if (static_cast<std::uint32_t>(n) < count) {
+      issue(n);
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+  }
+
+  for (std::uint32_t n = 0; n < count; ++n) {
+    const std::uint32_t seq = first + n * step;
+    // the vectors of this token (small; their latency overlaps the wait below)
+    float kk[4];
+    float qq[4];
+    float vlo[4];
+    float vhi[4];
+    const std::size_t item = seq;
+    {
+      const __nv_bfloat16 *kp = static_cast<const __nv_bfloat16 *>(p.k) + item * p.k_stride + key_head * kDim;
+      const __nv_bfloat16 *qp = static_cast<const __nv_bfloat16 *>(p.q) + item * p.q_stride + key_head * kDim;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        kk[i] = __bfloat162float(kp[lane + 32 * i]);
+        qq[i] = __bfloat162float(qp[lane + 32 * i]);
+      }
+    }
+    load4<false>(p.v, item * p.v_stride + head * kDim + col0, vlo);
+    load4<false>(p.v, item * p.v_stride + head * kDim + col0 + 4, vhi);
+    const float beta = p.beta[item * p.value_heads + head];
+    const float decay = expf(p.log_decay[item * p.value_heads + head]);
+
+    // Stage (n-1) % kStages is refilled next: its write-back was issued by all threads before they arrived here.
+    __syncthreads();
+    if (n + kStages - 1 < count) {
+      issue(n + kStages - 1);
+    }
+    asm volatile("cp.async.commit_group;\n" ::: "memory");
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(kStages - 1) : "memory");
+    __syncthreads(); // the stage was filled by all threads
+
+    unsigned char *stage = ring + (n % kStages) * kStageBytes;
+    float s[4][8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float *row = reinterpret_cast<const float *>(stage + (lane + 32 * i) * kStagePitch) + col0;
+      const float4 lo = *reinterpret_cast<const float4 *>(row);
+      const float4 hi = *reinterpret_cast<const float4 *>(row + 4);
+      s[i][0] = lo.x; s[i][1] = lo.y; s[i][2] = lo.z; s[i][3] = lo.w;
+      s[i][4] = hi.x; s[i][5] = hi.y; s[i][6] = hi.z; s[i][7] = hi.w;
+    }
+    float red[17];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      red[c] = s[0][c] * kk[0] + s[1][c] * kk[1] + s[2][c] * kk[2] + s[3][c] * kk[3];
+      red[8 + c] = s[0][c] * qq[0] + s[1][c] * qq[1] + s[2][c] * qq[2] + s[3][c] * qq[3];
+    }
+    red[16] = kk[0] * qq[0] + kk[1] * qq[1] + kk[2] * qq[2] + kk[3] * qq[3];
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+#pragma unroll
+      for (int c = 0; c < 17; ++c) {
+        red[c] += __shfl_xor_sync(0xFFFFFFFFU, red[c], offset);
+      }
+    }
+    float delta[8];
+    float o[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const float vc = c < 4 ? vlo[c] : vhi[c - 4];
+      delta[c] = (vc - decay * red[c]) * beta;
+      o[c] = decay * red[8 + c] + delta[c] * red[16];
+    }
+    // new state back into the stage, then out as whole rows
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float *row = reinterpret_cast<float *>(stage + (lane + 32 * i) * kStagePitch) + col0;
+      float4 lo;
+      float4 hi;
+      lo.x = decay * s[i][0] + kk[i] * delta[0];
+      lo.y = decay * s[i][1] + kk[i] * delta[1];
+      lo.z = decay * s[i][2] + kk[i] * delta[2];
+      lo.w = decay * s[i][3] + kk[i] * delta[3];
+      hi.x = decay * s[i][4] + kk[i] * delta[4];
+      hi.y = decay * s[i][5] + kk[i] * delta[5];
+      hi.z = decay * s[i][6] + kk[i] * delta[6];
+      hi.w = decay * s[i][7] + kk[i] * delta[7];
+      *reinterpret_cast<float4 *>(row) = lo;
+      *reinterpret_cast<float4 *>(row + 4) = hi;
+    }
+    if (lane == 0) {
+      float *dst = p.out + (item * p.value_heads + head) * kDim + col0;
+      *reinterpret_cast<float4 *>(dst) = make_float4(o[0], o[1], o[2], o[3]);
+      *reinterpret_cast<float4 *>(dst + 4) = make_float4(o[4], o[5], o[6], o[7]);
+    }
+    __syncthreads(); // the whole updated state is in the stage
+    float *state = p.states[seq] + static_cast<std::size_t>(head) * kDim * kDim;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int idx = threadIdx.x + i * kBatchedThreads;
+      const int row = idx >> 5;
+      const int chunk = idx & 31;
+      *reinterpret_cast<float4 *>(state + row * kDim + chunk * 4) =
+          *reinterpret_cast<const float4 *>(stage + row * kStagePitch + chunk * 16);
+    }
+  }
+  asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+}
+
 } // namespace
 
 void launch_gdn_recurrent(const GdnCoreArgs &a, cudaStream_t stream) {
@@ -144,6 +299,26 @@ void launch_gdn_recurrent(const GdnCoreArgs &a, cudaStream_t stream) {
   p.tokens = a.tokens;
   p.key_heads = a.key_heads;
   p.value_heads = a.value_heads;
+  if (a.states != nullptr && a.tokens == 1 && !a.qkv_f32 && a.sequences >= 8) {
+    static std::once_flag flags[64];
+    int device = 0;
+    cuda_ok(cudaGetDevice(&device), "cudaGetDevice");
+    require(device >= 0 && device < 64, "device ordinal out of range", RIB200_STATUS_INTERNAL);
+    std::call_once(flags[device], [] {
+      cuda_ok(cudaFuncSetAttribute(gdn_batched_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   kBatchedSmemBytes),
+              "gated-delta batched decode shared-memory opt-in");
+    });
+    // one CTA per SM: about that many CTAs, each walking at least four sequences when the batch allows
+    int sm_count = 148;
+    cuda_ok(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device), "SM count query");
+    const std::uint32_t groups =
+        std::max(1U, std::min(a.sequences / 4, static_cast<std::uint32_t>(sm_count) / a.value_heads));
+    gdn_batched_decode_kernel<<<dim3(a.value_heads, groups), kBatchedThreads, kBatchedSmemBytes, stream>>>(
+        p, a.sequences);
+    cuda_ok(cudaGetLastError(), "gated-delta batched decode launch");
+    return;
+  }
   const dim3 grid(2, a.value_heads, a.sequences);
   if (a.qkv_f32) {
     gdn_recurrent_kernel<true><<<grid, 256, 0, stream>>>(p);
