@@ -36,6 +36,7 @@
 
 #include <algorithm>
 #include <cstdint>
+#include <cstdlib>
 #include <mutex>
 
 namespace rib200 {
@@ -179,6 +180,75 @@ __device__ __forceinline__ void tma_load_3d(std::uint32_t dst, const CUtensorMap
       : "memory");
 }
 
+// ---- two-CTA (cta_group::2) helpers: the pair's even CTA leads -------------------------------------------
+__device__ __forceinline__ std::uint32_t cluster_rank() {
+  std::uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+  return r;
+}
+
+// shared::cluster address of `addr` (a shared::cta address of this CTA) inside CTA `rank` of the cluster
+__device__ __forceinline__ std::uint32_t map_to_rank(std::uint32_t addr, std::uint32_t rank) {
+  std::uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(out) : "r"(addr), "r"(rank));
+  return out;
+}
+
+__device__ __forceinline__ void mbar_arrive_cluster(std::uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_bar) : "memory");
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+
+// TMA tiled load issued by either CTA of a pair into its own shared memory; the bytes are counted on the
+// leader's barrier (`leader_bar` is a shared::cluster address).
+__device__ __forceinline__ void tma_load_2d_pair(std::uint32_t dst, const CUtensorMap *map, int c0, int c1,
+                                                 std::uint32_t leader_bar) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, "
+               "%3}], [%4];\n" ::"r"(dst),
+               "l"(reinterpret_cast<std::uint64_t>(map)), "r"(c0), "r"(c1), "r"(leader_bar)
+               : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d_pair(std::uint32_t dst, const CUtensorMap *map, int c0, int c1, int c2,
+                                                 std::uint32_t leader_bar) {
+  asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, "
+               "%3, %4}], [%5];\n" ::"r"(dst),
+               "l"(reinterpret_cast<std::uint64_t>(map)), "r"(c0), "r"(c1), "r"(c2), "r"(leader_bar)
+               : "memory");
+}
+
+__device__ __forceinline__ void umma_ss_pair(std::uint32_t d_tmem, std::uint64_t a_desc, std::uint64_t b_desc,
+                                             std::uint32_t idesc, std::uint32_t accumulate) {
+  asm volatile("{\n"
+               ".reg .pred p;\n"
+               "setp.ne.b32 p, %4, 0;\n"
+               "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+               "}\n" ::"r"(d_tmem),
+               "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+
+__device__ __forceinline__ void umma_ts_pair(std::uint32_t d_tmem, std::uint32_t a_tmem, std::uint64_t b_desc,
+                                             std::uint32_t idesc, std::uint32_t accumulate) {
+  asm volatile("{\n"
+               ".reg .pred p;\n"
+               "setp.ne.b32 p, %4, 0;\n"
+               "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n"
+               "}\n" ::"r"(d_tmem),
+               "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+               : "memory");
+}
+
+// completion of all earlier pair MMAs arrives on a barrier given by its shared::cluster address
+__device__ __forceinline__ void umma_commit_pair(std::uint32_t cluster_bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(cluster_bar)
+               : "memory");
+}
+
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 
@@ -194,10 +264,10 @@ __device__ __forceinline__ std::uint64_t smem_desc(std::uint32_t addr, std::uint
   return d;
 }
 
-// Instruction descriptor: BF16 x BF16 -> FP32, M = 128.
-__host__ __device__ constexpr std::uint32_t instr_desc(int n, bool b_mn_major) {
+// Instruction descriptor: BF16 x BF16 -> FP32; M = 128 for one CTA, 256 for a pair.
+__host__ __device__ constexpr std::uint32_t instr_desc(int m, int n, bool b_mn_major) {
   return (1U << 4) | (1U << 7) | (1U << 10) | (b_mn_major ? (1U << 16) : 0U) |
-         (static_cast<std::uint32_t>(n >> 3) << 17) | (static_cast<std::uint32_t>(kTileRows >> 4) << 24);
+         (static_cast<std::uint32_t>(n >> 3) << 17) | (static_cast<std::uint32_t>(m >> 4) << 24);
 }
 
 __device__ __forceinline__ void umma_ss(std::uint32_t d_tmem, std::uint64_t a_desc, std::uint64_t b_desc,
@@ -324,7 +394,11 @@ struct TileWalk {
   __device__ void next() { ++iteration; }
 };
 
-template <bool F32>
+// Pair == true runs two CTAs of a cluster as one tcgen05 cta_group::2 unit: they take two query heads of the same
+// KV head at the same query tile, the even CTA issues every MMA for both (M = 256), and each CTA loads only half
+// of every K and V block (the MMA reads the B operand from both CTAs' shared memory).  That halves the bytes an
+// SM pulls from L2 per block, which is what limits the single-CTA form.  No load is multicast.
+template <bool F32, bool Pair>
 __global__ void __launch_bounds__(kThreads, 1)
     prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                              const __grid_constant__ CUtensorMap v_map, const void *query_f32,
@@ -344,18 +418,30 @@ __global__ void __launch_bounds__(kThreads, 1)
 #endif
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const std::uint32_t rank = Pair ? cluster_rank() : 0U;       // 0 leads the pair
+  const std::uint32_t unit = Pair ? blockIdx.x >> 1 : blockIdx.x; // index of this CTA (or pair) among its peers
+  const std::uint32_t units = Pair ? gridDim.x >> 1 : gridDim.x;
+  constexpr std::uint32_t kRowThreads = Pair ? 2 * kSoftmaxThreads : kSoftmaxThreads; // softmax threads per unit
+  // barriers every softmax thread of the unit arrives on live in the leader
+  auto arrive_on_leader = [&](int index) {
+    if constexpr (Pair) {
+      mbar_arrive_cluster(map_to_rank(bar(index), 0));
+    } else {
+      mbar_arrive(bar(index));
+    }
+  };
 
   if (threadIdx.x == 0) {
-    mbar_init(bar(kBarQFull), F32 ? kSoftmaxThreads : 1);
+    mbar_init(bar(kBarQFull), F32 ? kRowThreads : 1);
     mbar_init(bar(kBarQFree), 1);
-    mbar_init(bar(kBarOFree), kSoftmaxThreads);
+    mbar_init(bar(kBarOFree), kRowThreads);
     for (int s = 0; s < kSlots; ++s) {
       mbar_init(bar(kBarFull + s), 1);
       mbar_init(bar(kBarEmpty + s), 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar(kBarSFull + b), 1);
-      mbar_init(bar(kBarPFull + b), kSoftmaxThreads);
+      mbar_init(bar(kBarPFull + b), kRowThreads);
       mbar_init(bar(kBarPvDone + b), 1);
     }
     *abort_flag = (base & 1023U) != 0 ? 1U : 0U; // a misaligned window would scramble every tile: give up cleanly
@@ -363,13 +449,23 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
   if (warp == kMmaWarp) {
     // the whole tensor memory of the SM: O (256 columns) + two score tiles (128 each)
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;\n" ::"r"(
-                     smem_u32(const_cast<std::uint32_t *>(tmem_slot)))
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    if constexpr (Pair) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], 512;\n" ::"r"(
+                       smem_u32(const_cast<std::uint32_t *>(tmem_slot)))
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;\n" ::"r"(
+                       smem_u32(const_cast<std::uint32_t *>(tmem_slot)))
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
   }
   tcgen05_fence_before();
   __syncthreads();
+  if constexpr (Pair) {
+    cluster_sync_all(); // the partner's barriers exist before anything arrives on them
+  }
   tcgen05_fence_after();
   const std::uint32_t tmem = *tmem_slot;
   const std::uint32_t tmem_o = tmem;         // columns [0, 256)
@@ -390,8 +486,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       asm volatile("griddepcontrol.wait;\n" ::: "memory");
       std::uint32_t n = 0; // running slot number; the MMA warp walks the same sequence
       bool ok = *abort_flag == 0;
-      for (TileWalk walk(p.tiles, p.query_heads, gridDim.x, blockIdx.x); ok && !walk.done(); walk.next()) {
-        const std::uint32_t head = walk.head();
+      for (TileWalk walk(p.tiles, Pair ? p.query_heads / 2 : p.query_heads, units, unit); ok && !walk.done(); walk.next()) {
+        const std::uint32_t head = Pair ? walk.head() * 2 + rank : walk.head();
         const std::uint32_t kv_head = head / p.group;
         const std::uint32_t row0 = walk.tile() * kTileRows;
         const std::uint32_t blocks = tile_blocks(walk.tile());
@@ -403,10 +499,21 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
         if constexpr (!F32) {
-          mbar_expect_tx(bar(kBarQFull), kQBytes);
-          for (int b = 0; b < 4; ++b) {
-            tma_load_2d(q_smem + b * kQBoxBytes, &q_map, static_cast<int>(head * kHeadDim + b * kBoxCols),
-                        static_cast<int>(row0), bar(kBarQFull));
+          if constexpr (Pair) {
+            if (rank == 0) {
+              mbar_expect_tx(bar(kBarQFull), 2 * kQBytes); // both CTAs' Q tiles count on the leader's barrier
+            }
+            const std::uint32_t leader_bar = map_to_rank(bar(kBarQFull), 0);
+            for (int b = 0; b < 4; ++b) {
+              tma_load_2d_pair(q_smem + b * kQBoxBytes, &q_map, static_cast<int>(head * kHeadDim + b * kBoxCols),
+                               static_cast<int>(row0), leader_bar);
+            }
+          } else {
+            mbar_expect_tx(bar(kBarQFull), kQBytes);
+            for (int b = 0; b < 4; ++b) {
+              tma_load_2d(q_smem + b * kQBoxBytes, &q_map, static_cast<int>(head * kHeadDim + b * kBoxCols),
+                          static_cast<int>(row0), bar(kBarQFull));
+            }
           }
         }
         // K travels as two slots per block split by head dims (128 keys x 128 dims each, so that one MMA spans
@@ -418,8 +525,29 @@ __global__ void __launch_bounds__(kThreads, 1)
               return false;
             }
           }
-          mbar_expect_tx(bar(kBarFull + slot), kSlotBytes);
           const std::uint32_t dst = ring + slot * kSlotBytes;
+          if constexpr (Pair) {
+            // one slot per block and operand: this CTA's 64 keys of K (all dims), or its 128 dims of V (all keys)
+            if (rank == 0) {
+              mbar_expect_tx(bar(kBarFull + slot), 2 * kSlotBytes);
+            }
+            const std::uint32_t leader_bar = map_to_rank(bar(kBarFull + slot), 0);
+            const int key0 = static_cast<int>(block * kBlockKeys);
+            if (is_value) {
+              for (int b = 0; b < 2; ++b) {
+                tma_load_3d_pair(dst + b * kKeyBoxBytes, &v_map, static_cast<int>(rank * 128 + b * kBoxCols), key0,
+                                 static_cast<int>(kv_head), leader_bar);
+              }
+            } else {
+              for (int b = 0; b < 4; ++b) {
+                tma_load_3d_pair(dst + b * kSlotBoxBytes, &k_map, b * kBoxCols,
+                                 key0 + static_cast<int>(rank * kHalfKeys), static_cast<int>(kv_head), leader_bar);
+              }
+            }
+            ++n;
+            return true;
+          }
+          mbar_expect_tx(bar(kBarFull + slot), kSlotBytes);
           if (is_value) {
             const int key0 = static_cast<int>(block * kBlockKeys + half * kHalfKeys);
             for (int b = 0; b < 4; ++b) {
@@ -436,28 +564,44 @@ __global__ void __launch_bounds__(kThreads, 1)
           ++n;
           return true;
         };
-        ok = load_half(false, 0, 0) && load_half(false, 0, 1);
+        constexpr std::uint32_t kParts = Pair ? 1 : 2; // ring slots per block and operand
+        for (std::uint32_t h = 0; ok && h < kParts; ++h) {
+          ok = load_half(false, 0, h);
+        }
         for (std::uint32_t j = 0; ok && j < blocks; ++j) {
-          if (j + 1 < blocks) {
-            ok = load_half(false, j + 1, 0) && load_half(false, j + 1, 1);
+          for (std::uint32_t h = 0; ok && h < kParts && j + 1 < blocks; ++h) {
+            ok = load_half(false, j + 1, h);
           }
-          ok = ok && load_half(true, j, 0) && load_half(true, j, 1);
+          for (std::uint32_t h = 0; ok && h < kParts; ++h) {
+            ok = load_half(true, j, h);
+          }
         }
       }
     }
   } else if (warp == kMmaWarp) {
     // ================= MMA issue =================
-    if (lane == 0) {
-      constexpr std::uint32_t kIdescQk = instr_desc(kBlockKeys, false);
-      constexpr std::uint32_t kIdescPv = instr_desc(kHeadDim, true);
+    if (lane == 0 && rank == 0) {
+      constexpr int kUnitRows = Pair ? 2 * kTileRows : kTileRows;
+      constexpr std::uint32_t kIdescQk = instr_desc(kUnitRows, kBlockKeys, false);
+      constexpr std::uint32_t kIdescPv = instr_desc(kUnitRows, kHeadDim, true);
       // Descriptors are built once; inside the loops only a constant is added to the address field.
       const std::uint64_t q_desc = smem_desc(q_smem, 16, 1024);
-      const std::uint64_t k_desc = smem_desc(ring, 16, 1024);            // K-major, 8-row groups 1 KiB apart
-      const std::uint64_t v_desc = smem_desc(ring, kSlotBoxBytes, 1024); // dim-major, 64-dim boxes 8 KiB apart
+      const std::uint64_t k_desc = smem_desc(ring, 16, 1024); // K-major, 8-row groups 1 KiB apart
+      // dim-major V: 64-dim boxes of 64 keys (8 KiB) in the single-CTA form, of 128 keys (16 KiB) in the pair form
+      const std::uint64_t v_desc = smem_desc(ring, Pair ? kKeyBoxBytes : kSlotBoxBytes, 1024);
+      // completion of everything issued so far, signalled to this CTA and, in a pair, to the partner as well
+      auto commit = [&](int index) {
+        if constexpr (Pair) {
+          umma_commit_pair(map_to_rank(bar(index), 0));
+          umma_commit_pair(map_to_rank(bar(index), 1));
+        } else {
+          umma_commit(bar(index));
+        }
+      };
       std::uint32_t n = 0;  // running slot number
       std::uint32_t g0 = 0; // running key-block number of the tile's first block (S buffer = block & 1)
       bool ok = *abort_flag == 0;
-      for (TileWalk walk(p.tiles, p.query_heads, gridDim.x, blockIdx.x); ok && !walk.done(); walk.next()) {
+      for (TileWalk walk(p.tiles, Pair ? p.query_heads / 2 : p.query_heads, units, unit); ok && !walk.done(); walk.next()) {
         const std::uint32_t blocks = tile_blocks(walk.tile());
         ok = mbar_wait(bar(kBarQFull), walk.iteration & 1U, abort_flag);
         if (!ok) {
@@ -471,28 +615,46 @@ __global__ void __launch_bounds__(kThreads, 1)
             RIB200_STAMP(j, 0); // QK issue begins
           }
           const std::uint32_t d = tmem_s + (g & 1U) * kBlockKeys;
-          for (std::uint32_t half = 0; half < 2 && ok; ++half) {
+          if constexpr (Pair) {
+            // one slot: each CTA holds 64 of the block's 128 keys, all 256 dims in four 64-dim boxes
             const std::uint32_t slot = n % kSlots;
             ok = mbar_wait(bar(kBarFull + slot), (n / kSlots) & 1U, abort_flag);
-            if (!ok) {
-              break;
-            }
-            tcgen05_fence_after();
-            const std::uint64_t a0 = q_desc + ((half * 2 * kQBoxBytes) >> 4);
-            const std::uint64_t b0 = k_desc + ((slot * kSlotBytes) >> 4);
+            if (ok) {
+              tcgen05_fence_after();
+              const std::uint64_t b0 = k_desc + ((slot * kSlotBytes) >> 4);
 #pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {
-              const std::uint32_t a_off = ((ks >> 2) * kQBoxBytes + (ks & 3) * 32) >> 4;
-              const std::uint32_t b_off = ((ks >> 2) * kKeyBoxBytes + (ks & 3) * 32) >> 4;
-              umma_ss(d, a0 + a_off, b0 + b_off, kIdescQk, (half > 0 || ks > 0) ? 1U : 0U);
+              for (int ks = 0; ks < 16; ++ks) {
+                const std::uint32_t a_off = ((ks >> 2) * kQBoxBytes + (ks & 3) * 32) >> 4;
+                const std::uint32_t b_off = ((ks >> 2) * kSlotBoxBytes + (ks & 3) * 32) >> 4;
+                umma_ss_pair(d, q_desc + a_off, b0 + b_off, kIdescQk, ks > 0 ? 1U : 0U);
+              }
+              commit(kBarEmpty + slot);
+              ++n;
             }
-            umma_commit(bar(kBarEmpty + slot));
-            ++n;
+          } else {
+            for (std::uint32_t half = 0; half < 2 && ok; ++half) {
+              const std::uint32_t slot = n % kSlots;
+              ok = mbar_wait(bar(kBarFull + slot), (n / kSlots) & 1U, abort_flag);
+              if (!ok) {
+                break;
+              }
+              tcgen05_fence_after();
+              const std::uint64_t a0 = q_desc + ((half * 2 * kQBoxBytes) >> 4);
+              const std::uint64_t b0 = k_desc + ((slot * kSlotBytes) >> 4);
+#pragma unroll
+              for (int ks = 0; ks < 8; ++ks) {
+                const std::uint32_t a_off = ((ks >> 2) * kQBoxBytes + (ks & 3) * 32) >> 4;
+                const std::uint32_t b_off = ((ks >> 2) * kKeyBoxBytes + (ks & 3) * 32) >> 4;
+                umma_ss(d, a0 + a_off, b0 + b_off, kIdescQk, (half > 0 || ks > 0) ? 1U : 0U);
+              }
+              commit(kBarEmpty + slot);
+              ++n;
+            }
           }
           if (ok) {
-            umma_commit(bar(kBarSFull + (g & 1U)));
+            commit(kBarSFull + (g & 1U));
             if (j + 1 == blocks) {
-              umma_commit(bar(kBarQFree)); // the tile's last read of Q
+              commit(kBarQFree); // the tile's last read of Q
             }
           }
           if (walk.iteration == 0) {
@@ -524,24 +686,41 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           tcgen05_fence_after();
           // O += P_j V_j, P from tensor memory (BF16 pairs: 16 keys = 8 columns), V dim-major from the ring
-          for (std::uint32_t half = 0; half < 2 && ok; ++half) {
+          if constexpr (Pair) {
+            // one slot: each CTA holds 128 of the 256 dims for all 128 keys
             const std::uint32_t slot = n % kSlots;
             ok = mbar_wait(bar(kBarFull + slot), (n / kSlots) & 1U, abort_flag);
-            if (!ok) {
-              break;
-            }
-            tcgen05_fence_after();
-            const std::uint64_t b0 = v_desc + ((slot * kSlotBytes) >> 4);
+            if (ok) {
+              tcgen05_fence_after();
+              const std::uint64_t b0 = v_desc + ((slot * kSlotBytes) >> 4);
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-              const std::uint32_t a = tmem_s + (g & 1U) * kBlockKeys + half * 32 + ks * 8;
-              umma_ts(tmem_o, a, b0 + ((ks * 2048) >> 4), kIdescPv, (j > 0 || half > 0 || ks > 0) ? 1U : 0U);
+              for (int ks = 0; ks < 8; ++ks) {
+                const std::uint32_t a = tmem_s + (g & 1U) * kBlockKeys + ks * 8;
+                umma_ts_pair(tmem_o, a, b0 + ((ks * 2048) >> 4), kIdescPv, (j > 0 || ks > 0) ? 1U : 0U);
+              }
+              commit(kBarEmpty + slot);
+              ++n;
             }
-            umma_commit(bar(kBarEmpty + slot));
-            ++n;
+          } else {
+            for (std::uint32_t half = 0; half < 2 && ok; ++half) {
+              const std::uint32_t slot = n % kSlots;
+              ok = mbar_wait(bar(kBarFull + slot), (n / kSlots) & 1U, abort_flag);
+              if (!ok) {
+                break;
+              }
+              tcgen05_fence_after();
+              const std::uint64_t b0 = v_desc + ((slot * kSlotBytes) >> 4);
+#pragma unroll
+              for (int ks = 0; ks < 4; ++ks) {
+                const std::uint32_t a = tmem_s + (g & 1U) * kBlockKeys + half * 32 + ks * 8;
+                umma_ts(tmem_o, a, b0 + ((ks * 2048) >> 4), kIdescPv, (j > 0 || half > 0 || ks > 0) ? 1U : 0U);
+              }
+              commit(kBarEmpty + slot);
+              ++n;
+            }
           }
           if (ok) {
-            umma_commit(bar(kBarPvDone + (g & 1U)));
+            commit(kBarPvDone + (g & 1U));
           }
           if (walk.iteration == 0) {
             RIB200_STAMP(j, 4); // PV issued
@@ -562,8 +741,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     bool ok = *abort_flag == 0;
     std::uint32_t g0 = 0;
 
-    for (TileWalk walk(p.tiles, p.query_heads, gridDim.x, blockIdx.x); ok && !walk.done(); walk.next()) {
-      const std::uint32_t head = walk.head();
+    for (TileWalk walk(p.tiles, Pair ? p.query_heads / 2 : p.query_heads, units, unit); ok && !walk.done(); walk.next()) {
+      const std::uint32_t head = Pair ? walk.head() * 2 + rank : walk.head();
       const std::uint32_t row0 = walk.tile() * kTileRows;
       const std::uint32_t rows = tile_rows(walk.tile());
       const std::uint32_t blocks = tile_blocks(walk.tile());
@@ -601,7 +780,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           *reinterpret_cast<uint4 *>(smem + box * kQBoxBytes + row * 128 + chunk * 16) = raw;
         }
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-        mbar_arrive(bar(kBarQFull));
+        arrive_on_leader(kBarQFull);
       }
 
       float m_used = -INFINITY; // maximum the exponentials are taken against (scaled, base 2); same in both groups
@@ -717,7 +896,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         l_sum += (part0 + part1) + (part2 + part3);
         tmem_wait_st();
         tcgen05_fence_before();
-        mbar_arrive(bar(kBarPFull + buf));
+        arrive_on_leader(kBarPFull + buf);
         if (threadIdx.x == 0 && walk.iteration == 0) {
           RIB200_STAMP(j, 13); // P published
         }
@@ -764,7 +943,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (c == 3) {
           // O has been read: the next tile's first PV may overwrite it
           tcgen05_fence_before();
-          mbar_arrive(bar(kBarOFree));
+          arrive_on_leader(kBarOFree);
         }
         if (live) {
           if constexpr (F32) {
@@ -808,6 +987,9 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   tcgen05_fence_before();
   __syncthreads();
+  if constexpr (Pair) {
+    cluster_sync_all(); // neither CTA leaves (or frees tensor memory) while the other may still use it
+  }
   if (threadIdx.x == 0 && *abort_flag != 0) {
     atomicOr(p.status, static_cast<unsigned int>(RIB200_DEVICE_WAIT_TIMED_OUT));
   }
@@ -826,7 +1008,11 @@ __global__ void __launch_bounds__(kThreads, 1)
 #endif
   if (warp == kMmaWarp) {
     tcgen05_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;\n" ::"r"(tmem) : "memory");
+    if constexpr (Pair) {
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, 512;\n" ::"r"(tmem) : "memory");
+    } else {
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;\n" ::"r"(tmem) : "memory");
+    }
   }
 }
 
@@ -862,20 +1048,29 @@ CUtensorMap make_map(void *base, int rank, const cuuint64_t *dims, const cuuint6
   return map;
 }
 
-template <bool F32> void configure_once() {
+template <bool F32, bool Pair> void configure_once() {
   static std::once_flag flags[64];
   int device = 0;
   cuda_ok(cudaGetDevice(&device), "cudaGetDevice");
   require(device >= 0 && device < 64, "device ordinal out of range", RIB200_STATUS_INTERNAL);
   std::call_once(flags[device], [] {
-    cuda_ok(cudaFuncSetAttribute(prefill_attention_kernel<F32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cuda_ok(cudaFuncSetAttribute(prefill_attention_kernel<F32, Pair>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  kSmemBytes),
             "prefill attention shared-memory opt-in");
   });
 }
 
-template <bool F32> void launch(const PrefillArgs &a, cudaStream_t stream) {
-  configure_once<F32>();
+// RIB200_PREFILL_PAIR=0 keeps every shape on the single-CTA form (a tuning aid, not an interface).
+bool pair_form_enabled() {
+  static const bool enabled = [] {
+    const char *env = std::getenv("RIB200_PREFILL_PAIR");
+    return env == nullptr || env[0] != '0';
+  }();
+  return enabled;
+}
+
+template <bool F32, bool Pair> void launch(const PrefillArgs &a, cudaStream_t stream) {
+  configure_once<F32, Pair>();
   auto *cache = static_cast<__nv_bfloat16 *>(a.kv_cache);
   const std::size_t pieces = static_cast<std::size_t>(a.tokens) * a.kv_heads * 32 * 2;
   prefill_append_kernel<F32><<<static_cast<unsigned int>((pieces + 255) / 256), 256, 0, stream>>>(
@@ -883,16 +1078,18 @@ template <bool F32> void launch(const PrefillArgs &a, cudaStream_t stream) {
   cuda_ok(cudaGetLastError(), "prefill append launch");
 
   const std::uint64_t context = static_cast<std::uint64_t>(a.past_tokens) + a.tokens;
-  // K / V: [kv head][row < context][256], rows 512 bytes apart, heads max_ctx rows apart
+  // K / V: [kv head][row < context][256], rows 512 bytes apart, heads max_ctx rows apart.  The single-CTA form
+  // loads K in boxes of 128 keys and V in boxes of 64; the pair form the other way round (each CTA takes 64 keys
+  // of K and all 128 keys of half of V's dims).
   const cuuint64_t kv_dims[3] = {kHeadDim, context, a.kv_heads};
   const cuuint64_t kv_strides[2] = {kHeadDim * 2, static_cast<cuuint64_t>(a.max_context_tokens) * kHeadDim * 2};
-  const cuuint32_t k_box[3] = {kBoxCols, kBlockKeys, 1};
-  const cuuint32_t kv_box[3] = {kBoxCols, kHalfKeys, 1};
-  const CUtensorMap k_map = make_map(cache, 3, kv_dims, kv_strides, k_box);
+  const cuuint32_t tall_box[3] = {kBoxCols, kBlockKeys, 1};
+  const cuuint32_t short_box[3] = {kBoxCols, kHalfKeys, 1};
+  const CUtensorMap k_map = make_map(cache, 3, kv_dims, kv_strides, Pair ? short_box : tall_box);
   const CUtensorMap v_map =
       make_map(cache + static_cast<std::size_t>(a.kv_heads) * a.max_context_tokens * kHeadDim, 3, kv_dims, kv_strides,
-               kv_box);
-  // Q: [token][16 * 256] (BF16 activations only; FP32 queries are converted inside the kernel)
+               Pair ? tall_box : short_box);
+  // Q: [token][query_heads * 256] (BF16 activations only; FP32 queries are converted inside the kernel)
   CUtensorMap q_map = k_map;
   if (!F32) {
     const cuuint64_t q_dims[2] = {static_cast<cuuint64_t>(a.query_heads) * kHeadDim, a.tokens};
@@ -916,17 +1113,26 @@ template <bool F32> void launch(const PrefillArgs &a, cudaStream_t stream) {
   int sm_count = 0;
   cuda_ok(cudaGetDevice(&device), "cudaGetDevice");
   cuda_ok(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device), "SM count query");
-  const std::uint32_t total_tiles = params.tiles * a.query_heads;
-  config.gridDim = dim3(std::min<std::uint32_t>(total_tiles, static_cast<std::uint32_t>(sm_count)), 1, 1);
+  const std::uint32_t sms = static_cast<std::uint32_t>(sm_count);
+  if (Pair) {
+    const std::uint32_t pair_items = params.tiles * (a.query_heads / 2);
+    config.gridDim = dim3(2 * std::min<std::uint32_t>(pair_items, sms / 2), 1, 1);
+  } else {
+    config.gridDim = dim3(std::min<std::uint32_t>(params.tiles * a.query_heads, sms), 1, 1);
+  }
   config.blockDim = dim3(kThreads, 1, 1);
   config.dynamicSmemBytes = kSmemBytes;
   config.stream = stream;
-  cudaLaunchAttribute attribute{};
-  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attribute.val.programmaticStreamSerializationAllowed = 1;
-  config.attrs = &attribute;
-  config.numAttrs = 1;
-  cuda_ok(cudaLaunchKernelEx(&config, prefill_attention_kernel<F32>, q_map, k_map, v_map, a.query, params),
+  cudaLaunchAttribute attributes[2]{};
+  attributes[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attributes[0].val.programmaticStreamSerializationAllowed = 1;
+  attributes[1].id = cudaLaunchAttributeClusterDimension;
+  attributes[1].val.clusterDim.x = 2;
+  attributes[1].val.clusterDim.y = 1;
+  attributes[1].val.clusterDim.z = 1;
+  config.attrs = attributes;
+  config.numAttrs = Pair ? 2 : 1;
+  cuda_ok(cudaLaunchKernelEx(&config, prefill_attention_kernel<F32, Pair>, q_map, k_map, v_map, a.query, params),
           "prefill attention launch");
 }
 
@@ -943,10 +1149,12 @@ extern "C" int rib200_debug_read_cta_trace(long long *host, std::size_t count) {
 
 void launch_prefill_attention(const PrefillArgs &args, cudaStream_t stream) {
   require(args.tokens <= 65535U * kTileRows, "prefill attention: too many tokens for one launch");
+  // Two query heads of one KV head form a pair; an odd group size keeps the single-CTA form.
+  const bool pair = pair_form_enabled() && (args.query_heads / args.kv_heads) % 2 == 0;
   if (args.activations_f32) {
-    launch<true>(args, stream);
+    pair ? launch<true, true>(args, stream) : launch<true, false>(args, stream);
   } else {
-    launch<false>(args, stream);
+    pair ? launch<false, true>(args, stream) : launch<false, false>(args, stream);
   }
 }
 
