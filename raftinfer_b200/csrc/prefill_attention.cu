@@ -397,7 +397,8 @@ struct TileWalk {
 // Pair == true runs two CTAs of a cluster as one tcgen05 cta_group::2 unit: they take two query heads of the same
 // KV head at the same query tile, the even CTA issues every MMA for both (M = 256), and each CTA loads only half
 // of every K and V block (the MMA reads the B operand from both CTAs' shared memory).  That halves the bytes an
-// SM pulls from L2 per block, which is what limits the single-CTA form.  No load is multicast.
+// SM pulls from L2 per block.  Every TMA load has one destination CTA; the completion signals that both CTAs need
+// are two plain tcgen05.commit instructions, one per CTA's barrier.
 template <bool F32, bool Pair>
 __global__ void __launch_bounds__(kThreads, 1)
     prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
