@@ -77,7 +77,8 @@ enum : int {
   kBarPvDone = 5 + 2 * kSlots, // 2
   kBarQFree = 7 + 2 * kSlots,  // the tile's last score product has read Q
   kBarOFree = 8 + 2 * kSlots,  // the tile's epilogue has read O
-  kBarCount = 9 + 2 * kSlots
+  kBarDrain = 9 + 2 * kSlots,  // used once, by a CTA that has given up: its MMAs have drained
+  kBarCount = 10 + 2 * kSlots
 };
 
 // Optional timeline probe (compile with -DRIB200_TRACE): the first CTA of the grid stamps clock64() at the
@@ -161,6 +162,40 @@ __device__ __forceinline__ bool mbar_wait(std::uint32_t bar, std::uint32_t parit
     }
   }
   return true;
+}
+
+// Bounded wait that never makes its caller leave: when it runs out it flags the CTA, and once the CTA is flagged it
+// returns at once.
+__device__ __forceinline__ void mbar_wait_through(std::uint32_t bar, std::uint32_t parity,
+                                                  volatile std::uint32_t *abort_flag) {
+  if (mbar_try_wait(bar, parity) || *abort_flag != 0) {
+    return;
+  }
+  const long long started = clock64();
+  std::uint32_t polls = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++polls & 255U) == 0) {
+      if (*abort_flag != 0) {
+        return;
+      }
+      if (clock64() - started > kWaitLimitCycles) {
+        *abort_flag = 1;
+        return;
+      }
+    }
+  }
+}
+
+// One lane of the (converged) warp, the same one every time.
+__device__ __forceinline__ bool elect_one() {
+  std::uint32_t chosen;
+  asm volatile("{\n"
+               ".reg .pred p;\n"
+               "elect.sync _|p, 0xFFFFFFFF;\n"
+               "selp.u32 %0, 1, 0, p;\n"
+               "}\n"
+               : "=r"(chosen));
+  return chosen != 0;
 }
 
 __device__ __forceinline__ void tma_load_2d(std::uint32_t dst, const CUtensorMap *map, int c0, int c1,
@@ -417,7 +452,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   const long long cta_started = global_ns();
   std::uint32_t traced_blocks = 0;
 #endif
-  const int warp = threadIdx.x >> 5;
+  const int warp = __shfl_sync(0xFFFFFFFFU, threadIdx.x >> 5, 0); // a value the compiler knows to be warp-uniform
   const int lane = threadIdx.x & 31;
   const std::uint32_t rank = Pair ? cluster_rank() : 0U;       // 0 leads the pair
   const std::uint32_t unit = Pair ? blockIdx.x >> 1 : blockIdx.x; // index of this CTA (or pair) among its peers
@@ -435,6 +470,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (threadIdx.x == 0) {
     mbar_init(bar(kBarQFull), F32 ? kRowThreads : 1);
     mbar_init(bar(kBarQFree), 1);
+    mbar_init(bar(kBarDrain), 1);
     mbar_init(bar(kBarOFree), kRowThreads);
     for (int s = 0; s < kSlots; ++s) {
       mbar_init(bar(kBarFull + s), 1);
@@ -581,7 +617,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else if (warp == kMmaWarp) {
     // ================= MMA issue =================
-    if (lane == 0 && rank == 0) {
+    // The whole warp walks the loops, so that control flow, ring positions and descriptors are the same in every
+    // lane and can live in uniform registers (where tcgen05.mma takes its operands from); one elected lane issues
+    // the MMAs and the commits.  A wait that runs out flags the CTA, and from then on nothing waits: the warp runs
+    // through its remaining tiles on stale operands rather than leave a loop early.
+    if (rank == 0) {
+      const bool leader = elect_one();
       constexpr int kUnitRows = Pair ? 2 * kTileRows : kTileRows;
       constexpr std::uint32_t kIdescQk = instr_desc(kUnitRows, kBlockKeys, false);
       constexpr std::uint32_t kIdescPv = instr_desc(kUnitRows, kHeadDim, true);
@@ -590,26 +631,37 @@ __global__ void __launch_bounds__(kThreads, 1)
       const std::uint64_t k_desc = smem_desc(ring, 16, 1024); // K-major, 8-row groups 1 KiB apart
       // dim-major V: 64-dim boxes of 64 keys (8 KiB) in the single-CTA form, of 128 keys (16 KiB) in the pair form
       const std::uint64_t v_desc = smem_desc(ring, Pair ? kKeyBoxBytes : kSlotBoxBytes, 1024);
+      const std::uint32_t remote_bars = Pair ? map_to_rank(bars, 1) : 0U;
+      const std::uint32_t local_bars = Pair ? map_to_rank(bars, 0) : bars;
       // completion of everything issued so far, signalled to this CTA and, in a pair, to the partner as well
-      auto commit = [&](int index) {
-        if constexpr (Pair) {
-          umma_commit_pair(map_to_rank(bar(index), 0));
-          umma_commit_pair(map_to_rank(bar(index), 1));
-        } else {
-          umma_commit(bar(index));
+      auto commit = [&](std::uint32_t index) {
+        if (leader) {
+          if constexpr (Pair) {
+            umma_commit_pair(local_bars + index * 8U);
+            umma_commit_pair(remote_bars + index * 8U);
+          } else {
+            umma_commit(bars + index * 8U);
+          }
         }
       };
-      std::uint32_t n = 0;  // running slot number
-      std::uint32_t g0 = 0; // running key-block number of the tile's first block (S buffer = block & 1)
-      bool ok = *abort_flag == 0;
-      for (TileWalk walk(p.tiles, Pair ? p.query_heads / 2 : p.query_heads, units, unit); ok && !walk.done(); walk.next()) {
-        const std::uint32_t blocks = tile_blocks(walk.tile());
-        ok = mbar_wait(bar(kBarQFull), walk.iteration & 1U, abort_flag);
-        if (!ok) {
-          break;
-        }
+      auto wait = [&](std::uint32_t index, std::uint32_t parity) {
+        mbar_wait_through(bars + index * 8U, parity, abort_flag);
         tcgen05_fence_after();
-        // S[g & 1] = Q K_block^T: two slots, each holding all 128 keys for half of the head dims
+      };
+      std::uint32_t slot = 0;       // ring position: the producer walks the same sequence
+      std::uint32_t slot_parity = 0;
+      auto next_slot = [&] {
+        if (++slot == kSlots) {
+          slot = 0;
+          slot_parity ^= 1U;
+        }
+      };
+      std::uint32_t g0 = 0; // running key-block number of the tile's first block (S buffer = block & 1)
+      for (TileWalk walk(p.tiles, Pair ? p.query_heads / 2 : p.query_heads, units, unit); !walk.done(); walk.next()) {
+        const std::uint32_t blocks = tile_blocks(walk.tile());
+        wait(kBarQFull, walk.iteration & 1U);
+        // S[g & 1] = Q K_block^T.  Pair form: one slot, each CTA holding 64 of the block's 128 keys with all 256
+        // dims in four 64-dim boxes.  Single form: two slots, each holding all 128 keys for half of the dims.
         auto issue_qk = [&](std::uint32_t j) {
           const std::uint32_t g = g0 + j;
           if (walk.iteration == 0) {
@@ -617,117 +669,102 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           const std::uint32_t d = tmem_s + (g & 1U) * kBlockKeys;
           if constexpr (Pair) {
-            // one slot: each CTA holds 64 of the block's 128 keys, all 256 dims in four 64-dim boxes
-            const std::uint32_t slot = n % kSlots;
-            ok = mbar_wait(bar(kBarFull + slot), (n / kSlots) & 1U, abort_flag);
-            if (ok) {
-              tcgen05_fence_after();
-              const std::uint64_t b0 = k_desc + ((slot * kSlotBytes) >> 4);
+            wait(kBarFull + slot, slot_parity);
+            const std::uint64_t b0 = k_desc + ((slot * kSlotBytes) >> 4);
+            if (leader) {
 #pragma unroll
               for (int ks = 0; ks < 16; ++ks) {
                 const std::uint32_t a_off = ((ks >> 2) * kQBoxBytes + (ks & 3) * 32) >> 4;
                 const std::uint32_t b_off = ((ks >> 2) * kSlotBoxBytes + (ks & 3) * 32) >> 4;
                 umma_ss_pair(d, q_desc + a_off, b0 + b_off, kIdescQk, ks > 0 ? 1U : 0U);
               }
-              commit(kBarEmpty + slot);
-              ++n;
             }
+            commit(kBarEmpty + slot);
+            next_slot();
           } else {
-            for (std::uint32_t half = 0; half < 2 && ok; ++half) {
-              const std::uint32_t slot = n % kSlots;
-              ok = mbar_wait(bar(kBarFull + slot), (n / kSlots) & 1U, abort_flag);
-              if (!ok) {
-                break;
-              }
-              tcgen05_fence_after();
+#pragma unroll
+            for (std::uint32_t half = 0; half < 2; ++half) {
+              wait(kBarFull + slot, slot_parity);
               const std::uint64_t a0 = q_desc + ((half * 2 * kQBoxBytes) >> 4);
               const std::uint64_t b0 = k_desc + ((slot * kSlotBytes) >> 4);
+              if (leader) {
 #pragma unroll
-              for (int ks = 0; ks < 8; ++ks) {
-                const std::uint32_t a_off = ((ks >> 2) * kQBoxBytes + (ks & 3) * 32) >> 4;
-                const std::uint32_t b_off = ((ks >> 2) * kKeyBoxBytes + (ks & 3) * 32) >> 4;
-                umma_ss(d, a0 + a_off, b0 + b_off, kIdescQk, (half > 0 || ks > 0) ? 1U : 0U);
+                for (int ks = 0; ks < 8; ++ks) {
+                  const std::uint32_t a_off = ((ks >> 2) * kQBoxBytes + (ks & 3) * 32) >> 4;
+                  const std::uint32_t b_off = ((ks >> 2) * kKeyBoxBytes + (ks & 3) * 32) >> 4;
+                  umma_ss(d, a0 + a_off, b0 + b_off, kIdescQk, (half > 0 || ks > 0) ? 1U : 0U);
+                }
               }
               commit(kBarEmpty + slot);
-              ++n;
+              next_slot();
             }
           }
-          if (ok) {
-            commit(kBarSFull + (g & 1U));
-            if (j + 1 == blocks) {
-              commit(kBarQFree); // the tile's last read of Q
-            }
+          commit(kBarSFull + (g & 1U));
+          if (j + 1 == blocks) {
+            commit(kBarQFree); // the tile's last read of Q
           }
           if (walk.iteration == 0) {
             RIB200_STAMP(j, 1); // QK issued
           }
         };
         issue_qk(0);
-        for (std::uint32_t j = 0; ok && j < blocks; ++j) {
+        for (std::uint32_t j = 0; j < blocks; ++j) {
           const std::uint32_t g = g0 + j;
           if (j + 1 < blocks) {
             issue_qk(j + 1);
           }
-          if (!ok) {
-            break;
-          }
           if (walk.iteration == 0) {
             RIB200_STAMP(j, 2); // waiting for P
           }
-          ok = mbar_wait(bar(kBarPFull + (g & 1U)), (g >> 1) & 1U, abort_flag);
-          if (ok && j == 0 && walk.iteration > 0) {
+          wait(kBarPFull + (g & 1U), (g >> 1) & 1U);
+          if (j == 0 && walk.iteration > 0) {
             // the first PV of a tile overwrites O: the previous tile's epilogue must have read it
-            ok = mbar_wait(bar(kBarOFree), (walk.iteration - 1) & 1U, abort_flag);
-          }
-          if (!ok) {
-            break;
+            wait(kBarOFree, (walk.iteration - 1) & 1U);
           }
           if (walk.iteration == 0) {
             RIB200_STAMP(j, 3); // P arrived
           }
-          tcgen05_fence_after();
           // O += P_j V_j, P from tensor memory (BF16 pairs: 16 keys = 8 columns), V dim-major from the ring
           if constexpr (Pair) {
             // one slot: each CTA holds 128 of the 256 dims for all 128 keys
-            const std::uint32_t slot = n % kSlots;
-            ok = mbar_wait(bar(kBarFull + slot), (n / kSlots) & 1U, abort_flag);
-            if (ok) {
-              tcgen05_fence_after();
-              const std::uint64_t b0 = v_desc + ((slot * kSlotBytes) >> 4);
+            wait(kBarFull + slot, slot_parity);
+            const std::uint64_t b0 = v_desc + ((slot * kSlotBytes) >> 4);
+            if (leader) {
 #pragma unroll
               for (int ks = 0; ks < 8; ++ks) {
                 const std::uint32_t a = tmem_s + (g & 1U) * kBlockKeys + ks * 8;
                 umma_ts_pair(tmem_o, a, b0 + ((ks * 2048) >> 4), kIdescPv, (j > 0 || ks > 0) ? 1U : 0U);
               }
-              commit(kBarEmpty + slot);
-              ++n;
             }
+            commit(kBarEmpty + slot);
+            next_slot();
           } else {
-            for (std::uint32_t half = 0; half < 2 && ok; ++half) {
-              const std::uint32_t slot = n % kSlots;
-              ok = mbar_wait(bar(kBarFull + slot), (n / kSlots) & 1U, abort_flag);
-              if (!ok) {
-                break;
-              }
-              tcgen05_fence_after();
-              const std::uint64_t b0 = v_desc + ((slot * kSlotBytes) >> 4);
 #pragma unroll
-              for (int ks = 0; ks < 4; ++ks) {
-                const std::uint32_t a = tmem_s + (g & 1U) * kBlockKeys + half * 32 + ks * 8;
-                umma_ts(tmem_o, a, b0 + ((ks * 2048) >> 4), kIdescPv, (j > 0 || half > 0 || ks > 0) ? 1U : 0U);
+            for (std::uint32_t half = 0; half < 2; ++half) {
+              wait(kBarFull + slot, slot_parity);
+              const std::uint64_t b0 = v_desc + ((slot * kSlotBytes) >> 4);
+              if (leader) {
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                  const std::uint32_t a = tmem_s + (g & 1U) * kBlockKeys + half * 32 + ks * 8;
+                  umma_ts(tmem_o, a, b0 + ((ks * 2048) >> 4), kIdescPv, (j > 0 || half > 0 || ks > 0) ? 1U : 0U);
+                }
               }
               commit(kBarEmpty + slot);
-              ++n;
+              next_slot();
             }
           }
-          if (ok) {
-            commit(kBarPvDone + (g & 1U));
-          }
+          commit(kBarPvDone + (g & 1U));
           if (walk.iteration == 0) {
             RIB200_STAMP(j, 4); // PV issued
           }
         }
         g0 += blocks;
+      }
+      if (*abort_flag != 0) {
+        // after giving up: every MMA issued above has left the tensor pipe before tensor memory is freed
+        commit(kBarDrain);
+        mbar_wait_through(bars + kBarDrain * 8U, 0, abort_flag);
       }
     }
   } else {
