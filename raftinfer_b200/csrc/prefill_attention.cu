@@ -238,6 +238,19 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
 }
 
+// TMA tiled store shared -> global (bulk async group of the issuing thread)
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *map, int c0, int c1, int c2, std::uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];\n" ::"l"(
+                   reinterpret_cast<std::uint64_t>(map)),
+               "r"(c0), "r"(c1), "r"(c2), "r"(src)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;\n" ::: "memory"); }
+// the stores of this thread have read their shared-memory source
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory"); }
+// the stores of this thread are complete
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory"); }
+
 // TMA tiled load issued by either CTA of a pair into its own shared memory; the bytes are counted on the
 // leader's barrier (`leader_bar` is a shared::cluster address).
 __device__ __forceinline__ void tma_load_2d_pair(std::uint32_t dst, const CUtensorMap *map, int c0, int c1,
@@ -437,7 +450,8 @@ struct TileWalk {
 template <bool F32, bool Pair>
 __global__ void __launch_bounds__(kThreads, 1)
     prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
-                             const __grid_constant__ CUtensorMap v_map, const void *query_f32,
+                             const __grid_constant__ CUtensorMap v_map, const __grid_constant__ CUtensorMap k_new_map,
+                             const __grid_constant__ CUtensorMap v_new_map, const void *query_f32,
                              const PrefillParams p) {
   extern __shared__ __align__(1024) unsigned char smem[];
   const std::uint32_t base = smem_u32(smem); // the 128-byte swizzle needs 1 KiB alignment; checked below
@@ -519,8 +533,59 @@ __global__ void __launch_bounds__(kThreads, 1)
   if (warp == kProducerWarp) {
     // ================= producer =================
     if (lane == 0) {
-      // the cache rows of this chunk are written by the append kernel that precedes this launch
-      asm volatile("griddepcontrol.wait;\n" ::: "memory");
+      // Key blocks that lie wholly inside this chunk are read from the BF16 key / value inputs, so they need
+      // nothing from the append kernel that precedes this launch; the first block that needs cache rows of this
+      // chunk (a block that straddles the past, or any block when the inputs are FP32) waits for that kernel.
+      bool append_done = false;
+      auto wait_for_append = [&] {
+        if (!append_done) {
+          asm volatile("griddepcontrol.wait;\n" ::: "memory");
+          append_done = true;
+        }
+      };
+      // In-kernel append.  A key block read from the inputs is also this chunk's contribution to the cache: the
+      // CTA that serves the first query head of the KV group, on the tile whose last block it is, writes the
+      // slot back to the cache with a TMA store (same box, so the swizzled slot is exactly its source) once the
+      // MMAs have consumed it, i.e. when the slot's turn to be refilled comes, or at the end of the walk.
+      // pending[slot]: bit 31 set | bit 30 value | bit 29 half | bits 16-23 KV head | bits 0-15 block
+      std::uint32_t pending[kSlots];
+      for (std::uint32_t i = 0; i < kSlots; ++i) {
+        pending[i] = 0;
+      }
+      auto store_slot = [&](std::uint32_t slot) {
+        const std::uint32_t entry = pending[slot];
+        pending[slot] = 0;
+        const bool is_value = (entry >> 30) & 1U;
+        const std::uint32_t half = (entry >> 29) & 1U;
+        const int kv = static_cast<int>((entry >> 16) & 0xFFU);
+        const int key0 = static_cast<int>((entry & 0xFFFFU) * kBlockKeys);
+        const std::uint32_t src = ring + slot * kSlotBytes;
+        if constexpr (Pair) {
+          if (is_value) {
+            for (int b = 0; b < 2; ++b) {
+              tma_store_3d(&v_map, static_cast<int>(rank * 128 + b * kBoxCols), key0, kv, src + b * kKeyBoxBytes);
+            }
+          } else {
+            for (int b = 0; b < 4; ++b) {
+              tma_store_3d(&k_map, b * kBoxCols, key0 + static_cast<int>(rank * kHalfKeys), kv,
+                           src + b * kSlotBoxBytes);
+            }
+          }
+        } else {
+          if (is_value) {
+            for (int b = 0; b < 4; ++b) {
+              tma_store_3d(&v_map, b * kBoxCols, key0 + static_cast<int>(half * kHalfKeys), kv,
+                           src + b * kSlotBoxBytes);
+            }
+          } else {
+            for (int b = 0; b < 2; ++b) {
+              tma_store_3d(&k_map, static_cast<int>((half * 2 + b) * kBoxCols), key0, kv, src + b * kKeyBoxBytes);
+            }
+          }
+        }
+        tma_store_commit();
+        tma_store_wait_read(); // the slot may be overwritten now
+      };
       std::uint32_t n = 0; // running slot number; the MMA warp walks the same sequence
       bool ok = *abort_flag == 0;
       for (TileWalk walk(p.tiles, Pair ? p.query_heads / 2 : p.query_heads, units, unit); ok && !walk.done(); walk.next()) {
@@ -555,29 +620,43 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         // K travels as two slots per block split by head dims (128 keys x 128 dims each, so that one MMA spans
         // all 128 keys); V as two slots split by keys (64 keys x 256 dims each).
+        const bool appends = !F32 && head % p.group == (Pair ? rank : 0U); // serves the group's first head
         auto load_half = [&](bool is_value, std::uint32_t block, std::uint32_t half) {
           const std::uint32_t slot = n % kSlots;
           if (n >= kSlots) {
             if (!mbar_wait(bar(kBarEmpty + slot), ((n / kSlots) - 1) & 1U, abort_flag)) {
               return false;
             }
+            if (pending[slot] != 0) {
+              store_slot(slot);
+            }
           }
           const std::uint32_t dst = ring + slot * kSlotBytes;
+          const bool from_inputs = !F32 && block * kBlockKeys >= p.past;
+          if (!from_inputs && (block + 1) * kBlockKeys > p.past) {
+            wait_for_append();
+          }
+          const CUtensorMap *k_src = from_inputs ? &k_new_map : &k_map;
+          const CUtensorMap *v_src = from_inputs ? &v_new_map : &v_map;
+          const int block_key0 = static_cast<int>(block * kBlockKeys - (from_inputs ? p.past : 0U));
+          if (appends && from_inputs && block + 1 == blocks) {
+            pending[slot] = 0x80000000U | (is_value ? 0x40000000U : 0U) | (half << 29) | (kv_head << 16) | block;
+          }
           if constexpr (Pair) {
             // one slot per block and operand: this CTA's 64 keys of K (all dims), or its 128 dims of V (all keys)
             if (rank == 0) {
               mbar_expect_tx(bar(kBarFull + slot), 2 * kSlotBytes);
             }
             const std::uint32_t leader_bar = map_to_rank(bar(kBarFull + slot), 0);
-            const int key0 = static_cast<int>(block * kBlockKeys);
+            const int key0 = block_key0;
             if (is_value) {
               for (int b = 0; b < 2; ++b) {
-                tma_load_3d_pair(dst + b * kKeyBoxBytes, &v_map, static_cast<int>(rank * 128 + b * kBoxCols), key0,
+                tma_load_3d_pair(dst + b * kKeyBoxBytes, v_src, static_cast<int>(rank * 128 + b * kBoxCols), key0,
                                  static_cast<int>(kv_head), leader_bar);
               }
             } else {
               for (int b = 0; b < 4; ++b) {
-                tma_load_3d_pair(dst + b * kSlotBoxBytes, &k_map, b * kBoxCols,
+                tma_load_3d_pair(dst + b * kSlotBoxBytes, k_src, b * kBoxCols,
                                  key0 + static_cast<int>(rank * kHalfKeys), static_cast<int>(kv_head), leader_bar);
               }
             }
@@ -586,15 +665,15 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           mbar_expect_tx(bar(kBarFull + slot), kSlotBytes);
           if (is_value) {
-            const int key0 = static_cast<int>(block * kBlockKeys + half * kHalfKeys);
+            const int key0 = block_key0 + static_cast<int>(half * kHalfKeys);
             for (int b = 0; b < 4; ++b) {
-              tma_load_3d(dst + b * kSlotBoxBytes, &v_map, b * kBoxCols, key0, static_cast<int>(kv_head),
+              tma_load_3d(dst + b * kSlotBoxBytes, v_src, b * kBoxCols, key0, static_cast<int>(kv_head),
                           bar(kBarFull + slot));
             }
           } else {
-            const int key0 = static_cast<int>(block * kBlockKeys);
+            const int key0 = block_key0;
             for (int b = 0; b < 2; ++b) {
-              tma_load_3d(dst + b * kKeyBoxBytes, &k_map, static_cast<int>((half * 2 + b) * kBoxCols), key0,
+              tma_load_3d(dst + b * kKeyBoxBytes, k_src, static_cast<int>((half * 2 + b) * kBoxCols), key0,
                           static_cast<int>(kv_head), bar(kBarFull + slot));
             }
           }
@@ -614,6 +693,20 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
       }
+      // slots still waiting to be written back: the last fill of slot s was number m, m % kSlots == s
+      for (std::uint32_t back = 1; ok && back <= kSlots && back <= n; ++back) {
+        const std::uint32_t m = n - back;
+        const std::uint32_t slot = m % kSlots;
+        if (pending[slot] != 0) {
+          ok = mbar_wait(bar(kBarEmpty + slot), (m / kSlots) & 1U, abort_flag);
+          if (ok) {
+            store_slot(slot);
+          }
+        }
+      }
+      tma_store_wait_all();
+      // this grid never completes before the append kernel has: work queued behind it sees the cache rows
+      wait_for_append();
     }
   } else if (warp == kMmaWarp) {
     // ================= MMA issue =================
@@ -1110,10 +1203,17 @@ bool pair_form_enabled() {
 template <bool F32, bool Pair> void launch(const PrefillArgs &a, cudaStream_t stream) {
   configure_once<F32, Pair>();
   auto *cache = static_cast<__nv_bfloat16 *>(a.kv_cache);
-  const std::size_t pieces = static_cast<std::size_t>(a.tokens) * a.kv_heads * 32 * 2;
-  prefill_append_kernel<F32><<<static_cast<unsigned int>((pieces + 255) / 256), 256, 0, stream>>>(
-      a.key, a.value, cache, a.tokens, a.past_tokens, a.max_context_tokens, a.kv_heads);
-  cuda_ok(cudaGetLastError(), "prefill append launch");
+  // The attention kernel itself writes the key blocks that lie wholly inside this chunk into the cache (BF16
+  // inputs).  The append kernel covers the rest: every row for FP32 inputs, else the chunk's rows that share a key
+  // block with the past.
+  const std::uint32_t ragged = a.past_tokens % kBlockKeys == 0 ? 0U : kBlockKeys - a.past_tokens % kBlockKeys;
+  const std::uint32_t append_rows = F32 ? a.tokens : std::min<std::uint32_t>(a.tokens, ragged);
+  if (append_rows > 0) {
+    const std::size_t pieces = static_cast<std::size_t>(append_rows) * a.kv_heads * 32 * 2;
+    prefill_append_kernel<F32><<<static_cast<unsigned int>((pieces + 255) / 256), 256, 0, stream>>>(
+        a.key, a.value, cache, append_rows, a.past_tokens, a.max_context_tokens, a.kv_heads);
+    cuda_ok(cudaGetLastError(), "prefill append launch");
+  }
 
   const std::uint64_t context = static_cast<std::uint64_t>(a.past_tokens) + a.tokens;
   // K / V: [kv head][row < context][256], rows 512 bytes apart, heads max_ctx rows apart.  The single-CTA form
@@ -1127,6 +1227,15 @@ template <bool F32, bool Pair> void launch(const PrefillArgs &a, cudaStream_t st
   const CUtensorMap v_map =
       make_map(cache + static_cast<std::size_t>(a.kv_heads) * a.max_context_tokens * kHeadDim, 3, kv_dims, kv_strides,
                Pair ? tall_box : short_box);
+  // BF16 key / value inputs, [token][kv head][256]: the same boxes over this chunk's own rows
+  CUtensorMap k_new_map = k_map;
+  CUtensorMap v_new_map = v_map;
+  if (!F32) {
+    const cuuint64_t new_dims[3] = {kHeadDim, a.tokens, a.kv_heads};
+    const cuuint64_t new_strides[2] = {static_cast<cuuint64_t>(a.kv_heads) * kHeadDim * 2, kHeadDim * 2};
+    k_new_map = make_map(const_cast<void *>(a.key), 3, new_dims, new_strides, Pair ? short_box : tall_box);
+    v_new_map = make_map(const_cast<void *>(a.value), 3, new_dims, new_strides, Pair ? tall_box : short_box);
+  }
   // Q: [token][query_heads * 256] (BF16 activations only; FP32 queries are converted inside the kernel)
   CUtensorMap q_map = k_map;
   if (!F32) {
@@ -1168,9 +1277,11 @@ template <bool F32, bool Pair> void launch(const PrefillArgs &a, cudaStream_t st
   attributes[1].val.clusterDim.x = 2;
   attributes[1].val.clusterDim.y = 1;
   attributes[1].val.clusterDim.z = 1;
-  config.attrs = attributes;
-  config.numAttrs = Pair ? 2 : 1;
-  cuda_ok(cudaLaunchKernelEx(&config, prefill_attention_kernel<F32, Pair>, q_map, k_map, v_map, a.query, params),
+  // attribute 0 (overlap with the append kernel) only when that kernel was launched
+  config.attrs = append_rows > 0 ? attributes : attributes + 1;
+  config.numAttrs = (Pair ? 1 : 0) + (append_rows > 0 ? 1 : 0);
+  cuda_ok(cudaLaunchKernelEx(&config, prefill_attention_kernel<F32, Pair>, q_map, k_map, v_map, k_new_map, v_new_map, a.query,
+                             params),
           "prefill attention launch");
 }
 
