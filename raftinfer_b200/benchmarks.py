@@ -301,6 +301,7 @@ def main(argv=None):
     ap.add_argument("sections", nargs="*", default=[])
     ap.add_argument("--tokens", type=int, nargs="*", default=None, help="prefill token counts")
     ap.add_argument("--contexts", type=int, nargs="*", default=None, help="decode contexts")
+    ap.add_argument("--gdn-tokens", type=int, default=4096, help="gated-delta prefill length")
     args = ap.parse_args(argv)
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
@@ -319,7 +320,7 @@ def main(argv=None):
     if "serving" in want:
         out["batched_serving_decode"] = batched_serving_decode(dev, stream, hbm)
     if "gdn" in want:
-        out["gated_delta"] = gdn_layer(dev, stream, hbm, tensor)
+        out["gated_delta"] = gdn_layer(dev, stream, hbm, tensor, tokens=args.gdn_tokens)
     if "prefill" in want:
         out["prefill_attention"] = prefill_attention(dev, stream, tensor, tuple(args.tokens or (128, 512, 4096)))
     print(json.dumps(out))
