@@ -1,19 +1,23 @@
-// Causal GQA prefill attention with online softmax and a sigmoid output gate, for 16 query heads / 4 KV heads /
-// head_dim 256, BF16 head-major KV cache (replaces cpp/kernels/qwen35_online_attention.cu:296-322 append and
-// :499-600 prefill; CPU form cpp/reference/qwen35.cpp:316-370).
+// Causal GQA prefill attention with online softmax and a sigmoid output gate, head_dim 256, BF16 head-major KV
+// cache, any number of query heads that is a multiple of the KV heads (replaces
+// cpp/kernels/qwen35_online_attention.cu:296-322 append and :499-600 prefill; CPU form
+// cpp/reference/qwen35.cpp:316-370).
 //
-// Two launches: a small append kernel writes this chunk's K and V rows into the cache (BF16, nearest even, as
-// the reference's append does), then the attention kernel reads every key and value - past and new - from the
-// cache, which is exactly what the reference's prefill kernel sees.  The second launch uses programmatic
-// dependent launch so that its set-up overlaps the append.
-//
-// Attention kernel (one CTA per 128 query rows of one head, 320 threads):
-//   warp 8   producer.  TMA tiled loads with the 128-byte swizzle: the Q tile once (64 KiB), then K and V in
-//            half blocks of 64 keys (32 KiB each) through a ring of five slots, which is what lets a load be
-//            issued four half-blocks (one and a half microseconds of tensor work) ahead of its use.  The tensor maps end at the
-//            live context, so rows the cache has never held arrive as zeros.
-//   warp 9   issues tcgen05.mma (BF16 in, FP32 accumulate in tensor memory).  Tensor memory holds the output
-//            tile O (128 lanes x 256 columns) and two score tiles S (128 x 128 each): 512 columns in all.
+// One persistent kernel, one CTA per SM, 320 threads.  The (128-query tile, head) items of the launch are sorted
+// long-first and dealt to the CTAs in snake order; a CTA walks its items without leaving, and the first loads and
+// score products of an item overlap the epilogue of the one before.
+//   warp 8   producer (one lane).  TMA tiled loads with the 128-byte swizzle: the Q tile (64 KiB), then K and V
+//            through a ring of five 32 KiB slots.  Key blocks that lie wholly inside this chunk come straight
+//            from the BF16 key / value inputs; older blocks come from the cache (the tensor maps end at the live
+//            context, so rows the cache has never held arrive as zeros).  The CTA that serves the first query head
+//            of a KV group, on the tile whose last block it is, also writes such a block to the cache with TMA
+//            stores once the MMAs have consumed it: that is this chunk's append (BF16 inputs are stored as they
+//            are, which is what the reference's append writes).  A separate append kernel runs first only for
+//            FP32 inputs (converted nearest-even) and for the rows that share a key block with the past; the
+//            producer waits for it (programmatic dependent launch) before it reads such rows.
+//   warp 9   MMA issue.  The whole warp walks the loops and one elected lane issues tcgen05.mma (BF16 in, FP32
+//            accumulate in tensor memory), so ring positions and descriptors stay warp-uniform.  Tensor memory holds
+//            the output tile O (128 lanes x 256 columns) and two score tiles S (128 x 128 each): 512 columns in all.
 //            S = Q K^T takes both operands from shared memory (K-major); O += P V takes P from tensor memory
 //            (written over the S tile it came from, as BF16) and V from shared memory (dim-major).
 //            The issue order QK(j+1), PV(j) keeps the tensor pipe busy while the softmax of block j runs.
@@ -23,10 +27,12 @@
 //            moves when it falls more than 8 (base-2) behind, at which point the threads rescale their rows of
 //            O in tensor memory; this is rare after the first blocks.  The same threads normalise, gate and
 //            store the tile at the end.
+// Pair form (GQA group even): the two CTAs of a cluster take two query heads of one KV head at the same tile and
+// run as one tcgen05 cta_group::2 unit (M = 256); each CTA loads half of every K block and half of every V block.
 //
-// Work per launch: 4 * 16 * 256 * (T * P + T (T + 1) / 2) flops for T new tokens after P past tokens.
-// Every wait on an mbarrier is bounded; when one runs out the CTA records RIB200_DEVICE_WAIT_TIMED_OUT, all
-// roles leave their loops, tensor memory is released and the kernel returns.
+// Work per launch: 4 * heads * 256 * (T * P + T (T + 1) / 2) flops for T new tokens after P past tokens.
+// Every wait on an mbarrier is bounded; when one runs out the CTA records RIB200_DEVICE_WAIT_TIMED_OUT, nothing
+// waits any more, tensor memory is released and the kernel returns.
 
 #include "common.hpp"
 
