@@ -37,6 +37,30 @@
 namespace rib200 {
 namespace {
 
+// Optional timeline probe (compile with -DRIB200_TRACE): every partition CTA records, in nanoseconds of the global
+// timer, when it started, when its first slot had landed, when its stream ended and when it left; every combine CTA
+// when it started, when the partition grid had completed and when it left.
+#ifdef RIB200_TRACE
+__device__ long long g_decode_trace[4096 * 4];
+__device__ long long g_combine_trace[256 * 4];
+__device__ __forceinline__ long long global_ns() {
+  long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define RIB200_DECODE_STAMP(array, cta, slot)                          \
+  do {                                                                 \
+    if (threadIdx.x == 0 && (cta) < sizeof(array) / 32) {              \
+      array[(cta) * 4 + (slot)] = global_ns();                         \
+    }                                                                  \
+  } while (0)
+#else
+#define RIB200_DECODE_STAMP(array, cta, slot) \
+  do {                                        \
+  } while (0)
+#endif
+
+
 constexpr int kHeadDim = 256;
 constexpr int kQueryHeads = 16;
 constexpr int kKvHeads = 4;
@@ -209,9 +233,15 @@ __global__ void __launch_bounds__(T::kWarps * 32, T::kCtasPerSm) decode_partitio
   constexpr int kRingSlots = T::kRingSlots;
   constexpr int kRingBytes = T::kRingBytes;
   extern __shared__ __align__(128) unsigned char smem[];
-  // The combine kernel is launched with programmatic stream serialisation: let it become resident now;
-  // it blocks in griddepcontrol.wait until this whole grid has finished and flushed.
+  // Both kernels of a decode step are launched with programmatic stream serialisation.  This grid may have been
+  // made resident early by the kernel before it (the combine kernel of a preceding step does that); nothing is read
+  // or written before that kernel has completed, so the ordering is that of a plain launch, minus the launch latency.
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
+  // Let the combine kernel become resident now; it blocks in griddepcontrol.wait until this whole grid has
+  // finished and flushed.
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+  const unsigned int trace_cta = blockIdx.x + gridDim.x * blockIdx.y;
+  RIB200_DECODE_STAMP(g_decode_trace, trace_cta, 0);
 
   const int seq = Batched ? static_cast<int>(blockIdx.z) : 0;
   const std::uint32_t max_ctx = Batched ? p.max_ctx_array[seq] : p.max_ctx;
@@ -301,6 +331,9 @@ __global__ void __launch_bounds__(T::kWarps * 32, T::kCtasPerSm) decode_partitio
       }
     }
     healthy = __all_sync(0xFFFFFFFFU, healthy);
+    if (n == 0) {
+      RIB200_DECODE_STAMP(g_decode_trace, trace_cta, 1);
+    }
     return healthy;
   };
 
@@ -490,6 +523,7 @@ __global__ void __launch_bounds__(T::kWarps * 32, T::kCtasPerSm) decode_partitio
 
   // cross-warp combine through shared memory.  Lane (g, t) holds, for head t and every 16-dim tile mt,
   // dims 16mt + g and 16mt + g + 8 (high-part column + residual column).
+  RIB200_DECODE_STAMP(g_decode_trace, trace_cta, 2);
   __syncthreads(); // every warp has left its ring: the merge area may now overwrite it
   float *merge = reinterpret_cast<float *>(smem);
   float *warp_max = merge;                       // [kWarps][4]
@@ -554,6 +588,7 @@ __global__ void __launch_bounds__(T::kWarps * 32, T::kCtasPerSm) decode_partitio
     *reinterpret_cast<float4 *>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
     *reinterpret_cast<float4 *>(dst + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
   }
+  RIB200_DECODE_STAMP(g_decode_trace, trace_cta, 3);
 }
 
 // Combine kernel.  grid = (16 query heads, 4 dim quarters, sequences), 256 threads: sixteen partition
@@ -565,7 +600,24 @@ __global__ void __launch_bounds__(256) decode_combine_kernel(const DecodeParams 
   __shared__ float group_acc[16][64];
 
   // wait until the partition grid has completed and its partials are visible
+  const unsigned int trace_cta = blockIdx.x + gridDim.x * blockIdx.y;
+  RIB200_DECODE_STAMP(g_combine_trace, trace_cta, 0);
+  // a kernel launched behind this one with programmatic serialisation may become resident (it waits for this grid)
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+  // the gate does not come from the partition grid: fetch it while that grid is still running
+  float gate_value = 0.0F;
+  if (threadIdx.x < 64) {
+    const std::size_t gate_index =
+        ((Batched ? static_cast<std::size_t>(blockIdx.z) : 0) * kQueryHeads + blockIdx.x) * kHeadDim + blockIdx.y * 64 +
+        threadIdx.x;
+    if constexpr (F32) {
+      gate_value = static_cast<const float *>(p.gate)[gate_index];
+    } else {
+      gate_value = __bfloat162float(static_cast<const __nv_bfloat16 *>(p.gate)[gate_index]);
+    }
+  }
   asm volatile("griddepcontrol.wait;\n" ::: "memory");
+  RIB200_DECODE_STAMP(g_combine_trace, trace_cta, 1);
 
   const int seq = Batched ? static_cast<int>(blockIdx.z) : 0;
   const std::uint32_t max_ctx = Batched ? p.max_ctx_array[seq] : p.max_ctx;
@@ -600,7 +652,7 @@ __global__ void __launch_bounds__(256) decode_combine_kernel(const DecodeParams 
   float run_max = -INFINITY;
   float run_sum = 0.0F;
   float4 acc = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
-#pragma unroll 4
+#pragma unroll 8
   for (std::uint32_t i = group; i < parts; i += 16) {
     const float part_max = pmax[i];
     const float part_sum = psum[i];
@@ -638,14 +690,13 @@ __global__ void __launch_bounds__(256) decode_combine_kernel(const DecodeParams 
     }
     const std::size_t out_index = (act_seq * kQueryHeads + head) * kHeadDim + quarter * 64 + threadIdx.x;
     if constexpr (F32) {
-      const float gate = static_cast<const float *>(p.gate)[out_index];
-      static_cast<float *>(p.output)[out_index] = (total / total_sum) / (1.0F + expf(-gate));
+      static_cast<float *>(p.output)[out_index] = (total / total_sum) / (1.0F + expf(-gate_value));
     } else {
-      const float gate = __bfloat162float(static_cast<const __nv_bfloat16 *>(p.gate)[out_index]);
       static_cast<__nv_bfloat16 *>(p.output)[out_index] =
-          __float2bfloat16_rn((total / total_sum) / (1.0F + expf(-gate)));
+          __float2bfloat16_rn((total / total_sum) / (1.0F + expf(-gate_value)));
     }
   }
+  RIB200_DECODE_STAMP(g_combine_trace, trace_cta, 2);
 }
 
 // CTA shapes.  Shared memory bounds the bytes in flight per SM (the rings fill it either way), so the shape
@@ -668,21 +719,24 @@ template <bool F32, bool Batched, class T>
 void launch_pair_tiled(const DecodeParams &params, dim3 partition_grid, dim3 combine_grid, bool combine,
                        cudaStream_t stream) {
   configure_once<F32, Batched, T>();
-  decode_partition_kernel<F32, Batched, T><<<partition_grid, T::kWarps * 32, T::kSmemBytes, stream>>>(params);
-  cuda_ok(cudaGetLastError(), "decode attention partition launch");
-  if (!combine) {
-    return;
-  }
-  cudaLaunchConfig_t config{};
-  config.gridDim = combine_grid;
-  config.blockDim = dim3(256, 1, 1);
-  config.dynamicSmemBytes = 0;
-  config.stream = stream;
   cudaLaunchAttribute attribute{};
   attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attribute.val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t config{};
+  config.gridDim = partition_grid;
+  config.blockDim = dim3(T::kWarps * 32, 1, 1);
+  config.dynamicSmemBytes = T::kSmemBytes;
+  config.stream = stream;
   config.attrs = &attribute;
   config.numAttrs = 1;
+  cuda_ok(cudaLaunchKernelEx(&config, decode_partition_kernel<F32, Batched, T>, params),
+          "decode attention partition launch");
+  if (!combine) {
+    return;
+  }
+  config.gridDim = combine_grid;
+  config.blockDim = dim3(256, 1, 1);
+  config.dynamicSmemBytes = 0;
   cuda_ok(cudaLaunchKernelEx(&config, decode_combine_kernel<F32, Batched>, params),
           "decode attention combine launch");
 }
@@ -715,6 +769,15 @@ void launch_pair(const DecodeParams &params, dim3 partition_grid, dim3 combine_g
   case 24:
     launch_pair_tiled<F32, Batched, Tile<2, 4>>(params, partition_grid, combine_grid, combine, stream);
     return;
+  case 26:
+    launch_pair_tiled<F32, Batched, Tile<2, 6>>(params, partition_grid, combine_grid, combine, stream);
+    return;
+  case 44:
+    launch_pair_tiled<F32, Batched, Tile<4, 4>>(params, partition_grid, combine_grid, combine, stream);
+    return;
+  case 46:
+    launch_pair_tiled<F32, Batched, Tile<4, 6>>(params, partition_grid, combine_grid, combine, stream);
+    return;
   case 42:
     launch_pair_tiled<F32, Batched, Tile<4, 2>>(params, partition_grid, combine_grid, combine, stream);
     return;
@@ -743,6 +806,14 @@ void launch_pair(const DecodeParams &params, dim3 partition_grid, dim3 combine_g
 }
 
 } // namespace
+
+#ifdef RIB200_TRACE
+extern "C" int rib200_debug_read_decode_trace(long long *partition, long long *combine) {
+  const int first = static_cast<int>(cudaMemcpyFromSymbol(partition, g_decode_trace, sizeof(g_decode_trace)));
+  const int second = static_cast<int>(cudaMemcpyFromSymbol(combine, g_combine_trace, sizeof(g_combine_trace)));
+  return first != 0 ? first : second;
+}
+#endif
 
 void launch_decode_attention(const DecodeArgs &a, cudaStream_t stream) {
   DecodeParams params{};
