@@ -146,6 +146,9 @@ constexpr int kBatchedSmemBytes = kStages * kStageBytes;
 __device__ __forceinline__ void cp_async_16(std::uint32_t dst, const void *src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
 }
+__device__ __forceinline__ void cp_async_4(std::uint32_t dst, const void *src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(src) : "memory");
+}
 
 __global__ void __launch_bounds__(kBatchedThreads, 1)
     gdn_batched_decode_kernel(const RecurrentParams p, std::uint32_t sequences) {
@@ -172,6 +175,23 @@ __global__ void __launch_bounds__(kBatchedThreads, 1)
       const int chunk = idx & 31;
       cp_async_16(dst + row * kStagePitch + chunk * 16, src + row * kDim + chunk * 4);
     }
+    // The token's own vectors ride in the 16 spare bytes at the end of the rows (k: rows 0-15, q: 16-31,
+    // this head's v: 32-47, beta and the log decay: row 48), so that they arrive with the state, two sequences
+    // ahead of their use, instead of as loads queued behind the stream when they are needed.
+    const std::size_t item = seq;
+    if (threadIdx.x < 48) {
+      const int which = threadIdx.x >> 4;
+      const int chunk = threadIdx.x & 15;
+      const __nv_bfloat16 *vec =
+          which == 0   ? static_cast<const __nv_bfloat16 *>(p.k) + item * p.k_stride + key_head * kDim
+          : which == 1 ? static_cast<const __nv_bfloat16 *>(p.q) + item * p.q_stride + key_head * kDim
+                       : static_cast<const __nv_bfloat16 *>(p.v) + item * p.v_stride + head * kDim;
+      cp_async_16(dst + threadIdx.x * kStagePitch + 512, vec + chunk * 8);
+    } else if (threadIdx.x == 48) {
+      cp_async_4(dst + 48 * kStagePitch + 512, p.beta + item * p.value_heads + head);
+    } else if (threadIdx.x == 49) {
+      cp_async_4(dst + 48 * kStagePitch + 516, p.log_decay + item * p.value_heads + head);
+    }
   };
 
 #pragma unroll
@@ -184,25 +204,7 @@ __global__ void __launch_bounds__(kBatchedThreads, 1)
 
   for (std::uint32_t n = 0; n < count; ++n) {
     const std::uint32_t seq = first + n * step;
-    // the vectors of this token (small; their latency overlaps the wait below)
-    float kk[4];
-    float qq[4];
-    float vlo[4];
-    float vhi[4];
     const std::size_t item = seq;
-    {
-      const __nv_bfloat16 *kp = static_cast<const __nv_bfloat16 *>(p.k) + item * p.k_stride + key_head * kDim;
-      const __nv_bfloat16 *qp = static_cast<const __nv_bfloat16 *>(p.q) + item * p.q_stride + key_head * kDim;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        kk[i] = __bfloat162float(kp[lane + 32 * i]);
-        qq[i] = __bfloat162float(qp[lane + 32 * i]);
-      }
-    }
-    load4<false>(p.v, item * p.v_stride + head * kDim + col0, vlo);
-    load4<false>(p.v, item * p.v_stride + head * kDim + col0 + 4, vhi);
-    const float beta = p.beta[item * p.value_heads + head];
-    const float decay = expf(p.log_decay[item * p.value_heads + head]);
 
     // Stage (n-1) % kStages is refilled next: its write-back was issued by all threads before they arrived here.
     __syncthreads();
@@ -214,6 +216,32 @@ __global__ void __launch_bounds__(kBatchedThreads, 1)
     __syncthreads(); // the stage was filled by all threads
 
     unsigned char *stage = ring + (n % kStages) * kStageBytes;
+    // the token's vectors, from the spare bytes of the stage
+    float kk[4];
+    float qq[4];
+    float vlo[4];
+    float vhi[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int e = lane + 32 * i;
+      kk[i] = __bfloat162float(
+          *reinterpret_cast<const __nv_bfloat16 *>(stage + (e >> 3) * kStagePitch + 512 + (e & 7) * 2));
+      qq[i] = __bfloat162float(
+          *reinterpret_cast<const __nv_bfloat16 *>(stage + (16 + (e >> 3)) * kStagePitch + 512 + (e & 7) * 2));
+    }
+    {
+      const uint4 raw = *reinterpret_cast<const uint4 *>(stage + (32 + warp) * kStagePitch + 512);
+      vlo[0] = __uint_as_float(raw.x << 16);
+      vlo[1] = __uint_as_float(raw.x & 0xFFFF0000U);
+      vlo[2] = __uint_as_float(raw.y << 16);
+      vlo[3] = __uint_as_float(raw.y & 0xFFFF0000U);
+      vhi[0] = __uint_as_float(raw.z << 16);
+      vhi[1] = __uint_as_float(raw.z & 0xFFFF0000U);
+      vhi[2] = __uint_as_float(raw.w << 16);
+      vhi[3] = __uint_as_float(raw.w & 0xFFFF0000U);
+    }
+    const float beta = *reinterpret_cast<const float *>(stage + 48 * kStagePitch + 512);
+    const float decay = expf(*reinterpret_cast<const float *>(stage + 48 * kStagePitch + 516));
     float s[4][8];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
