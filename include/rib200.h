@@ -268,6 +268,34 @@ Rib200Status rib200_online_attention_decode_static_scratch(const void *query, co
                                                            int32_t activation_dtype, const uint32_t *device_position,
                                                            void *stream);
 
+/* ---- head-sharded prefill across the GPUs of one box (no counterpart in the reference) --------------
+ * Each rank runs the prefill kernel on its own slice of the heads (its own query/key/value/gate and its
+ * own KV cache holding its KV heads) and the kernel's epilogue stores every output tile straight into
+ * the full-width output buffer of every rank - peer stores over NVLink, no separate all-gather.
+ * outputs[r] (host array, `world` device pointers valid on this device) is rank r's buffer
+ * [tokens][total_query_heads][head_dim] in the activation dtype, outputs[rank] this rank's own; this
+ * rank's shape->query_heads heads land at head index head_offset.  world <= 8. */
+Rib200Status rib200_online_attention_prefill_scatter(const void *query, const void *key, const void *value,
+                                                     const void *gate, void *const *outputs, size_t world,
+                                                     size_t rank, size_t total_query_heads, size_t head_offset,
+                                                     void *kv_cache,
+                                                     size_t kv_cache_bytes, const Rib200AttentionShape *shape,
+                                                     int32_t activation_dtype, uint8_t cache_dtype,
+                                                     uint8_t cache_layout, void *stream);
+/* Rendezvous of the ranks after such a step, on the device: stores `epoch` into slot `rank` of every
+ * rank's flag array (flags[r], host array of `world` device pointers to uint32[world], zero at start),
+ * then waits, for a bounded time, until every slot of this rank's own array holds at least `epoch`.
+ * Enqueued behind the prefill on `stream`: when it completes, every peer's tiles are in this rank's
+ * buffer.  epoch must grow from call to call.  A wait that runs out sets RIB200_DEVICE_WAIT_TIMED_OUT. */
+Rib200Status rib200_peer_rendezvous(uint32_t *const *flags, size_t world, size_t rank, uint32_t epoch,
+                                    void *stream);
+/* Device memory that other processes on the box can map: allocation (zero-filled) with its 64-byte
+ * handle, mapping of a peer's handle, and their releases. */
+Rib200Status rib200_shared_alloc(size_t bytes, void **pointer, uint8_t handle[64]);
+Rib200Status rib200_shared_open(const uint8_t handle[64], void **pointer);
+Rib200Status rib200_shared_close(void *pointer);
+Rib200Status rib200_shared_free(void *pointer);
+
 /* Reads and clears the status word the kernels of this library set on the current device.  It
  * synchronises `stream` first, so it is not for use inside a graph capture. */
 Rib200Status rib200_device_status(void *stream, uint32_t *bits);

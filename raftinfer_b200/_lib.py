@@ -80,6 +80,13 @@ PROTOTYPES = {
                                         C.c_uint8, C.c_uint8, vp],
     "rib200_online_attention_decode": [vp, vp, vp, vp, vp, vp, sz, vp, sz, C.POINTER(AttentionShape), C.c_int32,
                                        C.c_uint8, C.c_uint8, C.POINTER(OnlineDecodePlan), vp, vp],
+    "rib200_online_attention_prefill_scatter": [vp, vp, vp, vp, C.POINTER(vp), sz, sz, sz, sz, vp, sz,
+                                                C.POINTER(AttentionShape), C.c_int32, C.c_uint8, C.c_uint8, vp],
+    "rib200_peer_rendezvous": [C.POINTER(vp), sz, sz, C.c_uint32, vp],
+    "rib200_shared_alloc": [sz, C.POINTER(vp), C.POINTER(C.c_uint8)],
+    "rib200_shared_open": [C.POINTER(C.c_uint8), C.POINTER(vp)],
+    "rib200_shared_close": [vp],
+    "rib200_shared_free": [vp],
     "rib200_gated_delta": [vp, vp, vp, vp, vp, vp, vp, vp, vp, sz, C.POINTER(GatedDeltaShape),
                            GatedDeltaLaunchPolicy, C.c_int32, C.c_int32, vp],
     "rib200_gdn_core_workspace_bytes": [sz, sz, sz, sz, sz, C.POINTER(sz)],

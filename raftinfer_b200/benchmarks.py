@@ -244,7 +244,11 @@ def sharded_serving_decode(dev, stream, hbm_peak, rank, world, dist, batch=64, l
 
 def head_split_prefill(dev, stream, tensor_peak, rank, world, dist, tokens=4096):
     """Prefill split by KV-head group: a rank computes 16/world query heads (with 8 ranks two ranks share a KV
-    head, each holding a copy), then one NCCL all-gather assembles [tokens][16][256] on every rank."""
+    head, each holding a copy).  Two ways to assemble [tokens][16][256] on every rank: one NCCL all-gather plus a
+    layout permute (the baseline), and the fused form, whose epilogue stores every tile into all ranks' buffers
+    over NVLink, followed by a device-side rendezvous."""
+    from .peer import SharedBuffer
+
     hq = HQ // world
     hkv = max(1, HKV // world)
     gen = torch.Generator(device=dev).manual_seed(23 + rank)
@@ -265,15 +269,36 @@ def head_split_prefill(dev, stream, tensor_peak, rank, world, dist, tokens=4096)
         dist.all_gather_into_tensor(gathered, local)
         full.view(tokens, world, hq, D).copy_(gathered.permute(1, 0, 2, 3))
 
+    shared_out = SharedBuffer((tokens, HQ, D), torch.bfloat16, rank, world, dist, dev)
+    shared_flags = SharedBuffer((world,), torch.int32, rank, world, dist, dev)
+    epoch = [0]
+
+    def fused(i):
+        epoch[0] += 1
+        K.online_attention_prefill_scatter(q, k, v, gate, shared_out.pointers, rank, HQ, rank * hq, cache,
+                                           cache.numel() * 2, shape, K.DTYPE_BF16, K.KV_BF16, K.HEAD_MAJOR, stream)
+        K.peer_rendezvous(shared_flags.pointers, rank, epoch[0], stream)
+
     flops = 4 * HQ * D * (tokens * (tokens + 1) // 2)
     ms_kernel = _timed_max_over_ranks(kernel_only, stream, dist, dev)
     ms_total = _timed_max_over_ranks(with_gather, stream, dist, dev)
+    ms_fused = _timed_max_over_ranks(fused, stream, dist, dev)
+    torch.cuda.synchronize()
+    same = bool(torch.equal(shared_out.local, full))
+    status = K.device_status(stream)
+    shared_flags.close()
+    shared_out.close()
+    if not same or status != 0:
+        raise K.Qwen35PrimitiveError(f"fused head-split prefill differs from the all-gather form (status {status})")
     return {"tokens": tokens, "ranks": world, "query_heads_per_rank": hq, "kv_heads_per_rank": hkv,
-            "ms_kernel": ms_kernel, "ms_with_all_gather": ms_total, "flops": flops,
-            "TFLOP/s": flops / ms_total / 1e9, "TFLOP/s_kernel_only": flops / ms_kernel / 1e9,
-            "frac_of_measured_bf16_peak_all_ranks": flops / ms_total / 1e9 / (tensor_peak * world),
-            "collective": "ncclAllGather of outputs + layout permute",
-            "all_gather_bytes_per_rank": tokens * hq * D * 2}
+            "ms_kernel": ms_kernel, "ms_with_all_gather": ms_total, "ms_fused_peer_stores": ms_fused, "flops": flops,
+            "TFLOP/s": flops / ms_fused / 1e9, "TFLOP/s_with_all_gather": flops / ms_total / 1e9,
+            "TFLOP/s_kernel_only": flops / ms_kernel / 1e9,
+            "frac_of_measured_bf16_peak_all_ranks": flops / ms_fused / 1e9 / (tensor_peak * world),
+            "fused_matches_all_gather": same,
+            "collective": "fused: tile stores into every rank's buffer + device-side rendezvous; "
+                          "baseline: ncclAllGather of outputs + layout permute",
+            "peer_store_bytes_per_rank": (world - 1) * tokens * hq * D * 2}
 
 
 def run_distributed(dev, stream, hbm_peak, tensor_peak, rank, world, dist):

@@ -203,15 +203,17 @@ void require_aligned16(const void *ptr, const char *message) {
   require(reinterpret_cast<std::uintptr_t>(ptr) % 16 == 0, message);
 }
 
+// `outputs` non-null: the head-sharded form, tiles go to `world` full-width buffers at `head_offset`.
 void online_prefill(const void *query, const void *key, const void *value, const void *gate, void *output,
                     void *kv_cache, std::size_t kv_cache_bytes, const Rib200AttentionShape &s,
                     int32_t activation_dtype, std::uint8_t cache_dtype, std::uint8_t cache_layout,
-                    cudaStream_t stream) {
+                    cudaStream_t stream, void *const *outputs = nullptr, std::size_t world = 0, std::size_t rank = 0,
+                    std::size_t total_query_heads = 0, std::size_t head_offset = 0) {
   require(query != nullptr, "online attention: query pointer is null");
   require(key != nullptr, "online attention: key pointer is null");
   require(value != nullptr, "online attention: value pointer is null");
   require(gate != nullptr, "online attention: gate pointer is null");
-  require(output != nullptr, "online attention: output pointer is null");
+  require(output != nullptr || outputs != nullptr, "online attention: output pointer is null");
   require(kv_cache != nullptr, "online attention: KV cache pointer is null");
   require(stream != nullptr, "online attention: CUDA stream is null");
   require(prefill_signature_ok(s, activation_dtype, cache_dtype, cache_layout),
@@ -226,9 +228,26 @@ void online_prefill(const void *query, const void *key, const void *value, const
   require_aligned16(key, "online attention: key is not 16-byte aligned");
   require_aligned16(value, "online attention: value is not 16-byte aligned");
   require_aligned16(gate, "online attention: gate is not 16-byte aligned");
-  require_aligned16(output, "online attention: output is not 16-byte aligned");
+  if (outputs == nullptr) {
+    require_aligned16(output, "online attention: output is not 16-byte aligned");
+  }
   require_aligned16(kv_cache, "online attention: KV cache is not 16-byte aligned");
   PrefillArgs args{};
+  if (outputs != nullptr) {
+    require(world >= 1 && world <= 8, "head-sharded prefill: world must be between 1 and 8");
+    require(rank < world, "head-sharded prefill: rank is out of range");
+    require(head_offset + s.query_heads <= total_query_heads,
+            "head-sharded prefill: this rank's heads do not fit in the output row");
+    for (std::size_t r = 0; r < world; ++r) {
+      require(outputs[r] != nullptr, "head-sharded prefill: an output pointer is null");
+      require_aligned16(outputs[r], "head-sharded prefill: an output is not 16-byte aligned");
+      args.outputs[r] = outputs[r];
+    }
+    args.output_count = static_cast<std::uint32_t>(world);
+    args.output_self = static_cast<std::uint32_t>(rank);
+    args.output_heads = static_cast<std::uint32_t>(total_query_heads);
+    args.output_head_offset = static_cast<std::uint32_t>(head_offset);
+  }
   args.query = query;
   args.key = key;
   args.value = value;
@@ -400,6 +419,21 @@ Rib200Status rib200_online_attention_prefill(const void *query, const void *key,
   return guarded([&] {
     online_prefill(query, key, value, gate, output, kv_cache, kv_cache_bytes, deref(shape), activation_dtype,
                    cache_dtype, cache_layout, static_cast<cudaStream_t>(stream));
+  });
+}
+
+Rib200Status rib200_online_attention_prefill_scatter(const void *query, const void *key, const void *value,
+                                                     const void *gate, void *const *outputs, size_t world,
+                                                     size_t rank, size_t total_query_heads, size_t head_offset,
+                                                     void *kv_cache,
+                                                     size_t kv_cache_bytes, const Rib200AttentionShape *shape,
+                                                     int32_t activation_dtype, uint8_t cache_dtype,
+                                                     uint8_t cache_layout, void *stream) {
+  return guarded([&] {
+    require(outputs != nullptr, "head-sharded prefill: output list is null");
+    online_prefill(query, key, value, gate, nullptr, kv_cache, kv_cache_bytes, deref(shape), activation_dtype,
+                   cache_dtype, cache_layout, static_cast<cudaStream_t>(stream), outputs, world, rank,
+                   total_query_heads, head_offset);
   });
 }
 

@@ -116,8 +116,19 @@ struct PrefillArgs {
   std::uint32_t query_heads;
   std::uint32_t kv_heads;
   bool activations_f32;
+  // Head-sharded form: the tile stores go to `output_count` buffers (this rank's and its peers'), each
+  // [tokens][output_heads][256], at head index output_head_offset.  output_count == 0 means `output` alone.
+  // The tile is stored into the rank's own buffer and forwarded from there to the others.
+  void *outputs[8];
+  std::uint32_t output_count;
+  std::uint32_t output_self; // index of this rank's own buffer
+  std::uint32_t output_heads;
+  std::uint32_t output_head_offset;
 };
 void launch_prefill_attention(const PrefillArgs &args, cudaStream_t stream);
+// device-side rendezvous of the ranks of one box (peer.cu)
+void launch_peer_rendezvous(std::uint32_t *const *flags, std::uint32_t world, std::uint32_t rank, std::uint32_t epoch,
+                            cudaStream_t stream);
 
 // ---- gated delta rule (gdn_recurrent.cu, gdn_chunk.cu, gdn_layer.cu) -------------------------
 // Operands of the recurrence for `sequences` independent sequences of `tokens` tokens each.

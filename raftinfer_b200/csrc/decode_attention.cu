@@ -240,7 +240,7 @@ __global__ void __launch_bounds__(T::kWarps * 32, T::kCtasPerSm) decode_partitio
   // Let the combine kernel become resident now; it blocks in griddepcontrol.wait until this whole grid has
   // finished and flushed.
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
-  const unsigned int trace_cta = blockIdx.x + gridDim.x * blockIdx.y;
+  [[maybe_unused]] const unsigned int trace_cta = blockIdx.x + gridDim.x * blockIdx.y;
   RIB200_DECODE_STAMP(g_decode_trace, trace_cta, 0);
 
   const int seq = Batched ? static_cast<int>(blockIdx.z) : 0;
@@ -600,7 +600,7 @@ __global__ void __launch_bounds__(256) decode_combine_kernel(const DecodeParams 
   __shared__ float group_acc[16][64];
 
   // wait until the partition grid has completed and its partials are visible
-  const unsigned int trace_cta = blockIdx.x + gridDim.x * blockIdx.y;
+  [[maybe_unused]] const unsigned int trace_cta = blockIdx.x + gridDim.x * blockIdx.y;
   RIB200_DECODE_STAMP(g_combine_trace, trace_cta, 0);
   // a kernel launched behind this one with programmatic serialisation may become resident (it waits for this grid)
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");

@@ -111,7 +111,11 @@ __device__ __forceinline__ long long global_ns() {
 
 struct PrefillParams {
   const void *gate;
-  void *output;
+  void *output;                // this GPU's output buffer
+  void *peers[7];              // head-sharded form: the other ranks' buffers, which receive a copy of every tile
+  std::uint32_t peer_count;
+  std::uint32_t output_heads;  // heads per row of a destination buffer
+  std::uint32_t output_head_offset;
   std::uint32_t tokens;
   std::uint32_t past;
   std::uint32_t tiles;
@@ -1047,6 +1051,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       g0 += blocks;
       const std::size_t out_base =
           (static_cast<std::size_t>(row0 + row) * p.query_heads + head) * kHeadDim + group * 128;
+      const std::size_t dst_base =
+          (static_cast<std::size_t>(row0 + row) * p.output_heads + p.output_head_offset + head) * kHeadDim +
+          group * 128;
       const bool live = row < rows;
       uint4 gate_raw[16]; // BF16 gates of this thread's 128 columns, fetched while the last PV is still running
       if constexpr (!F32) {
@@ -1085,7 +1092,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (live) {
           if constexpr (F32) {
             const float *gsrc = static_cast<const float *>(p.gate) + out_base + c * 32;
-            float *o = static_cast<float *>(p.output) + out_base + c * 32;
 #pragma unroll
             for (int e = 0; e < 32; e += 4) {
               const float4 gv = *reinterpret_cast<const float4 *>(gsrc + e);
@@ -1094,10 +1100,9 @@ __global__ void __launch_bounds__(kThreads, 1)
               r.y = __uint_as_float(v[e + 1]) * inv * fast_sigmoid(gv.y);
               r.z = __uint_as_float(v[e + 2]) * inv * fast_sigmoid(gv.z);
               r.w = __uint_as_float(v[e + 3]) * inv * fast_sigmoid(gv.w);
-              *reinterpret_cast<float4 *>(o + e) = r;
+              *reinterpret_cast<float4 *>(static_cast<float *>(p.output) + dst_base + c * 32 + e) = r;
             }
           } else {
-            __nv_bfloat16 *o = static_cast<__nv_bfloat16 *>(p.output) + out_base + c * 32;
 #pragma unroll
             for (int e = 0; e < 32; e += 8) {
               const uint4 gv = gate_raw[c * 4 + e / 8];
@@ -1111,7 +1116,37 @@ __global__ void __launch_bounds__(kThreads, 1)
                 const float r1 = __uint_as_float(v[e + 2 * h + 1]) * inv * fast_sigmoid(g1f);
                 ow[h] = pack_bf16(r0, r1);
               }
-              *reinterpret_cast<uint4 *>(o + e) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+              *reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.output) + dst_base + c * 32 + e) =
+                  make_uint4(ow[0], ow[1], ow[2], ow[3]);
+            }
+          }
+        }
+      }
+      if (p.peer_count > 0) {
+        // Head-sharded form: forward the tile to the other ranks' buffers.  A thread wrote one row's 128 columns;
+        // the warp now re-reads its 32 rows (they are in L2) so that every store instruction covers whole
+        // contiguous row segments, which is what peer stores over NVLink need to be efficient.
+        __syncwarp();
+        constexpr int kSegmentBytes = F32 ? 512 : 256;     // this group's share of a row
+        constexpr int kChunksPerRow = kSegmentBytes / 16;  // 32 or 16
+        constexpr int kRowsPerStep = 32 / kChunksPerRow;   // 1 or 2
+        const std::size_t element = F32 ? 4 : 2;
+        const std::size_t row_pitch = static_cast<std::size_t>(p.output_heads) * kHeadDim * element;
+        const std::size_t column_offset =
+            (static_cast<std::size_t>(p.output_head_offset + head) * kHeadDim + group * 128) * element;
+        const std::uint32_t chunk = lane % kChunksPerRow;
+        const unsigned char *own = static_cast<const unsigned char *>(p.output);
+#pragma unroll 4
+        for (int step = 0; step < 32 / kRowsPerStep; ++step) {
+          const std::uint32_t r = (warp & 3) * 32 + step * kRowsPerStep + lane / kChunksPerRow;
+          if (r < rows) {
+            const std::size_t at = static_cast<std::size_t>(row0 + r) * row_pitch + column_offset + chunk * 16;
+            const uint4 piece = *reinterpret_cast<const uint4 *>(own + at);
+#pragma unroll
+            for (std::uint32_t d = 0; d < 7; ++d) { // static indices: the pointers stay in the parameter bank
+              if (d < p.peer_count) {
+                *reinterpret_cast<uint4 *>(static_cast<unsigned char *>(p.peers[d]) + at) = piece;
+              }
             }
           }
         }
@@ -1253,7 +1288,22 @@ template <bool F32, bool Pair> void launch(const PrefillArgs &a, cudaStream_t st
 
   PrefillParams params{};
   params.gate = a.gate;
-  params.output = a.output;
+  if (a.output_count == 0) {
+    params.output = a.output;
+    params.peer_count = 0;
+    params.output_heads = a.query_heads;
+    params.output_head_offset = 0;
+  } else {
+    params.output = a.outputs[a.output_self];
+    params.peer_count = 0;
+    for (std::uint32_t d = 0; d < a.output_count; ++d) {
+      if (d != a.output_self) {
+        params.peers[params.peer_count++] = a.outputs[d];
+      }
+    }
+    params.output_heads = a.output_heads;
+    params.output_head_offset = a.output_head_offset;
+  }
   params.tokens = a.tokens;
   params.past = a.past_tokens;
   params.tiles = (a.tokens + kTileRows - 1) / kTileRows;

@@ -203,6 +203,49 @@ def qwen35_online_attention_prefill(query, key, value, gate, output, kv_cache, k
                                                cache_dtype, cache_layout, _stream(stream)))
 
 
+def online_attention_prefill_scatter(query, key, value, gate, outputs, rank, total_query_heads, head_offset, kv_cache,
+                                     kv_cache_bytes, shape, activation_dtype, cache_dtype, cache_layout, stream):
+    """Head-sharded prefill: `outputs` lists every rank's full-width output buffer (pointers or tensors valid on
+    this device), outputs[rank] being this rank's own; this rank's heads land at `head_offset` in each of them.
+    No counterpart in the reference."""
+    s = shape.c()
+    array = (C.c_void_p * len(outputs))(*[_ptr(o) for o in outputs])
+    _check(lib.rib200_online_attention_prefill_scatter(_ptr(query), _ptr(key), _ptr(value), _ptr(gate), array,
+                                                       len(outputs), rank, total_query_heads, head_offset,
+                                                       _ptr(kv_cache),
+                                                       kv_cache_bytes, C.byref(s), activation_dtype, cache_dtype,
+                                                       cache_layout, _stream(stream)))
+
+
+def peer_rendezvous(flag_arrays, rank, epoch, stream):
+    """Device-side rendezvous of the ranks behind the work already queued on `stream`."""
+    array = (C.c_void_p * len(flag_arrays))(*[_ptr(f) for f in flag_arrays])
+    _check(lib.rib200_peer_rendezvous(array, len(flag_arrays), rank, epoch, _stream(stream)))
+
+
+def shared_alloc(nbytes):
+    """Zero-filled device memory other processes can map: (pointer, 64-byte handle)."""
+    ptr = C.c_void_p()
+    handle = (C.c_uint8 * 64)()
+    _check(lib.rib200_shared_alloc(nbytes, C.byref(ptr), handle))
+    return ptr.value, bytes(handle)
+
+
+def shared_open(handle):
+    ptr = C.c_void_p()
+    raw = (C.c_uint8 * 64)(*handle)
+    _check(lib.rib200_shared_open(raw, C.byref(ptr)))
+    return ptr.value
+
+
+def shared_close(pointer):
+    _check(lib.rib200_shared_close(pointer))
+
+
+def shared_free(pointer):
+    _check(lib.rib200_shared_free(pointer))
+
+
 def qwen35_online_attention_decode(query, key, value, gate, output, kv_cache, kv_cache_bytes, workspace,
                                    workspace_bytes, shape, activation_dtype, cache_dtype, cache_layout, plan,
                                    device_position, stream):
