@@ -10,10 +10,11 @@
 // Bandwidth plan.  One CTA serves one (partition, KV head) and all four query heads of the group, so
 // every K and V byte is read from HBM once (the reference streams each KV head four times).  Each warp
 // owns 16-token steps of the partition.  Lane 0 of the warp is its producer: it moves the 512-byte K (or V)
-// rows of a step from the cache into a private ring of shared-memory slots with TMA bulk copies
-// (cp.async.bulk, completion counted on an mbarrier), several slots ahead of the consumer.  Rows sit at a
-// 528-byte pitch, which makes every ldmatrix of eight rows hit eight different bank groups.  Because ring,
-// barriers and producer are private to the warp, no block-level barrier is needed while streaming.
+// rows of a step, two at a time, from the cache into a private ring of shared-memory slots with TMA bulk
+// copies (cp.async.bulk, completion counted on an mbarrier), several slots ahead of the consumer.  Row pairs sit
+// at a 1040-byte pitch and the tensor-core row index is a permutation of the token order, which makes every
+// ldmatrix of eight rows hit eight different bank groups.  Because ring, barriers and producer are private to
+// the warp, no block-level barrier is needed while streaming.
 //
 // Arithmetic plan.  Tokens are the M dimension of mma.sync.m16n8k16 (BF16 in, FP32 accumulate) and the
 // eight N columns carry the four query heads twice: column 2h holds the BF16 high part and column 2h+1
@@ -67,8 +68,15 @@ constexpr int kKvHeads = 4;
 constexpr int kGroup = kQueryHeads / kKvHeads;
 constexpr int kStepTokens = 16;
 constexpr int kRowBytes = kHeadDim * 2;                // one cached K or V row
-constexpr int kRowPitch = kRowBytes + 16;              // shared-memory pitch of a row (bank-conflict-free ldmatrix)
-constexpr int kSlotBytes = kStepTokens * kRowPitch;    // the K rows or the V rows of one step
+// A slot holds the 16 rows of a step as 8 pairs: rows 2p and 2p+1 back to back (1 KiB, one bulk copy) at a pitch of
+// 1040 bytes.  The issue of a bulk copy costs the warp about as much for 1 KiB as for 512 bytes, so pairs halve the
+// time a warp spends feeding its ring.  The MMA row index m stands for token 2 (m % 8) + m / 8 of the step: the
+// eight rows of one ldmatrix then sit 1040 bytes apart, which is free of bank conflicts.
+constexpr int kPairPitch = 2 * kRowBytes + 16;
+constexpr int kSlotBytes = (kStepTokens / 2) * kPairPitch; // the K rows or the V rows of one step
+__host__ __device__ constexpr std::uint32_t row_offset(std::uint32_t row) { // byte offset of a step's row in its slot
+  return (row >> 1) * kPairPitch + (row & 1U) * kRowBytes;
+}
 constexpr int kMergePitch = kHeadDim + 8;              // floats per (warp, head) row of the merge area
 constexpr long long kWaitLimitCycles = 1LL << 28;      // SM cycles an mbarrier wait may take before giving up
 
@@ -309,9 +317,10 @@ __global__ void __launch_bounds__(T::kWarps * 32, T::kCtasPerSm) decode_partitio
     fence_proxy_async(); // earlier reads of this ring position are ordered before the TMA write
     mbarrier_expect_tx(bar, rows * kRowBytes);
 #pragma unroll
-    for (int r = 0; r < kStepTokens; ++r) {
-      if (static_cast<std::uint32_t>(r) < rows) {
-        bulk_copy_g2s(slot + r * kRowPitch, src + r * kHeadDim, kRowBytes, bar);
+    for (int pair = 0; pair < kStepTokens / 2; ++pair) {
+      if (static_cast<std::uint32_t>(2 * pair) < rows) {
+        const std::uint32_t live = min(2U, rows - 2 * pair);
+        bulk_copy_g2s(slot + pair * kPairPitch, src + 2 * pair * kHeadDim, live * kRowBytes, bar);
       }
     }
   };
@@ -345,14 +354,14 @@ __global__ void __launch_bounds__(T::kWarps * 32, T::kCtasPerSm) decode_partitio
     bool touched = false;
     if (pos >= tok0 && pos < tok0 + kStepTokens && pos < end) {
       const uint4 raw = load8_as_bf16<F32>(is_value ? p.value : p.key, kv_in_base + 8 * lane);
-      sts128(slot + (pos - tok0) * kRowPitch + lane * 16, raw);
+      sts128(slot + row_offset(pos - tok0) + lane * 16, raw);
       __nv_bfloat16 *plane = is_value ? v_plane : k_plane;
       *reinterpret_cast<uint4 *>(plane + static_cast<std::size_t>(pos) * kHeadDim + 8 * lane) = raw;
       touched = true;
     }
     if (tok0 + kStepTokens > end) {
       for (std::uint32_t r = end - tok0; r < kStepTokens; ++r) {
-        sts128(slot + r * kRowPitch + lane * 16, make_uint4(0U, 0U, 0U, 0U));
+        sts128(slot + row_offset(r) + lane * 16, make_uint4(0U, 0U, 0U, 0U));
       }
       touched = true;
     }
@@ -399,12 +408,12 @@ __global__ void __launch_bounds__(T::kWarps * 32, T::kCtasPerSm) decode_partitio
     }
   }
 
-  // ldmatrix lane addressing.  K (A operand, tokens x dims): matrix mi = lane>>3 covers token rows
+  // ldmatrix lane addressing.  K (A operand, tokens x dims): matrix mi = lane>>3 covers MMA rows
   // (mi&1)*8.., 16-byte chunk (mi>>1) of the k-step.  V (A operand transposed, dims x tokens): matrix mi
-  // covers token rows (mi>>1)*8.., chunk (mi&1) of the 16-dim tile.
+  // covers MMA k indices (mi>>1)*8.., chunk (mi&1) of the 16-dim tile.  MMA index m is token 2 (m % 8) + m / 8.
   const int mi = lane >> 3;
-  const std::uint32_t k_lane = ((lane & 7) + 8 * (mi & 1)) * kRowPitch + (mi >> 1) * 16;
-  const std::uint32_t v_lane = ((lane & 7) + 8 * (mi >> 1)) * kRowPitch + (mi & 1) * 16;
+  const std::uint32_t k_lane = (lane & 7) * kPairPitch + (mi & 1) * kRowBytes + (mi >> 1) * 16;
+  const std::uint32_t v_lane = (lane & 7) * kPairPitch + (mi >> 1) * kRowBytes + (mi & 1) * 16;
 
   float oacc[16][4];
 #pragma unroll
@@ -446,13 +455,13 @@ __global__ void __launch_bounds__(T::kWarps * 32, T::kCtasPerSm) decode_partitio
       mma_bf16(s2, a[2][0], a[2][1], a[2][2], a[2][3], qf[2 * ks + 4], qf[2 * ks + 5]);
       mma_bf16(s3, a[3][0], a[3][1], a[3][2], a[3][3], qf[2 * ks + 6], qf[2 * ks + 7]);
     }
-    // lane (g, t): head t, tokens tok0 + g and tok0 + g + 8 (high part + residual columns)
+    // lane (g, t): head t, MMA rows g and g + 8 = tokens tok0 + 2g and tok0 + 2g + 1 (high part + residual columns)
     float score_a = ((s0[0] + s1[0]) + (s2[0] + s3[0])) + ((s0[1] + s1[1]) + (s2[1] + s3[1]));
     float score_b = ((s0[2] + s1[2]) + (s2[2] + s3[2])) + ((s0[3] + s1[3]) + (s2[3] + s3[3]));
-    if (tok0 + g >= end) {
+    if (tok0 + 2 * g >= end) {
       score_a = -INFINITY;
     }
-    if (tok0 + g + 8 >= end) {
+    if (tok0 + 2 * g + 1 >= end) {
       score_b = -INFINITY;
     }
     float step_max = fmaxf(score_a, score_b);
