@@ -17,7 +17,9 @@ HQ, HKV, D = 16, 4, 256
 HK, HV, DK = 16, 32, 128
 
 
-def _median_ms(fn, stream, warmup=5, reps=20):
+def _median_ms(fn, stream, warmup=5, reps=20, calls=1):
+    """Median over `reps` of the CUDA-event time of `calls` consecutive fn() calls, per call.  calls > 1 keeps the
+    stream fed, so that a kernel of a few microseconds is not measured as the host's launch latency."""
     for i in range(warmup):
         fn(i)
     torch.cuda.synchronize()
@@ -25,11 +27,26 @@ def _median_ms(fn, stream, warmup=5, reps=20):
     for i in range(reps):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record(stream)
-        fn(i)
+        for c in range(calls):
+            fn(i * calls + c)
         b.record(stream)
         torch.cuda.synchronize()
-        times.append(a.elapsed_time(b))
+        times.append(a.elapsed_time(b) / calls)
     return statistics.median(times), (statistics.pstdev(times) / statistics.mean(times) if len(times) > 1 else 0.0)
+
+
+def _graph_ms(fn, stream, calls, warmup=3, reps=10):
+    """Per-call device time of `calls` consecutive fn() calls captured into one CUDA graph and replayed: for kernels
+    of a few microseconds, whose launch from Python costs more host time than they run."""
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        for i in range(calls):
+            fn(i)
+    ms, cv = _median_ms(lambda i: graph.replay(), stream, warmup=2, reps=reps)
+    return ms / calls, cv
 
 
 def _bf16(gen, dev, *shape):
@@ -54,7 +71,8 @@ def decode_contexts(dev, stream, hbm_peak, contexts=(4096, 131072)):
                                              layout.bytes, shape, K.DTYPE_BF16, K.KV_BF16, K.HEAD_MAJOR, plan, None,
                                              stream)
 
-        ms, cv = _median_ms(fn, stream)
+        ms, cv = _graph_ms(fn, stream, max(8, rotation)) if ctx <= 8192 else _median_ms(fn, stream, warmup=5, reps=10,
+                                                                                          calls=8)
         nbytes = 4096 * ctx + 24576
         out[f"decode_ctx{ctx}"] = {"ms": ms, "cv": cv, "bytes": nbytes, "GB/s": nbytes / ms / 1e6,
                                    "frac_of_measured_hbm": nbytes / ms / 1e6 / hbm_peak, "caches_rotated": rotation}
@@ -103,7 +121,7 @@ def batched_serving_decode(dev, stream, hbm_peak, batch=64, lo=1024, hi=32768, s
     res = {"sequences": batch, "total_context_tokens": sum(lengths)}
     for name, fn, nbytes in (("attention", attn, attn_bytes), ("gdn_decode", gdn, gdn_bytes),
                              ("attention+gdn_decode", both, attn_bytes + gdn_bytes)):
-        ms, cv = _median_ms(fn, stream, warmup=3, reps=10)
+        ms, cv = _median_ms(fn, stream, warmup=3, reps=10, calls=4)
         res[name] = {"ms": ms, "cv": cv, "bytes": nbytes, "GB/s": nbytes / ms / 1e6,
                      "frac_of_measured_hbm": nbytes / ms / 1e6 / hbm_peak}
     return res
@@ -138,9 +156,11 @@ def gdn_layer(dev, stream, hbm_peak, tensor_peak, tokens=4096, decode_steps=128)
     res = {"prefill": {"tokens": tokens, "ms": ms, "cv": cv, "flops": flops, "TFLOP/s": flops / ms / 1e9,
                        "frac_of_measured_bf16_peak": flops / ms / 1e9 / tensor_peak,
                        "note": "time includes a 2 MiB state memset"}}
-    ms, cv = _median_ms(decode, stream, warmup=5, reps=decode_steps)
+    # a step is a few microseconds of device time, less than one launch from Python costs on the host
+    ms, cv = _graph_ms(decode, stream, decode_steps, warmup=3, reps=8)
     nbytes = 2 * HV * DK * DK * 4
     res["decode_step"] = {"ms": ms, "cv": cv, "bytes": nbytes, "effective GB/s": nbytes / ms / 1e6,
+                          "steps_per_graph": decode_steps,
                           "note": "single sequence: the 2 MiB state is L2-resident, this is latency not HBM bandwidth"}
     return res
 
@@ -161,7 +181,7 @@ def prefill_attention(dev, stream, tensor_peak, token_counts=(128, 512, 4096)):
             K.qwen35_online_attention_prefill(q, k, v, gate, o, cache, cache.numel() * 2, shape, K.DTYPE_BF16, K.KV_BF16,
                                               K.HEAD_MAJOR, stream)
 
-        ms, cv = _median_ms(fn, stream, warmup=3, reps=10)
+        ms, cv = _graph_ms(fn, stream, 8) if tokens <= 512 else _median_ms(fn, stream, warmup=3, reps=10, calls=4)
         flops = 4 * HQ * D * (tokens * past + tokens * (tokens + 1) // 2)
         res[f"T{tokens}_past{past}"] = {"ms": ms, "cv": cv, "flops": flops, "TFLOP/s": flops / ms / 1e9,
                                         "frac_of_measured_bf16_peak": flops / ms / 1e9 / tensor_peak}
