@@ -221,6 +221,47 @@ def test_decode_replays_inside_a_cuda_graph():
     assert np.array_equal(cache_bits_of(cache).reshape(full.shape), full)
 
 
+def test_back_to_back_steps_keep_stream_order():
+    """Both kernels of a step are launched with programmatic stream serialisation and wait for their predecessor on
+    the device.  A chain in which every step's query is made, by a kernel on the same stream and with no host
+    synchronisation, from the previous step's output must give what the same chain gives with a synchronisation
+    after every operation."""
+    max_ctx, ctx0, steps = 4096, 3000, 6
+    q, gate, k, v = decode_operands(0xB2000900, ctx0 + steps)
+    shape_of = lambda pos: K.Qwen35AttentionShape(1, HQ, HKV, D, max_ctx, pos)
+    plan = K.qwen35_online_decode_plan(shape_of(ctx0), K.SPLIT_K_256, ctx0 + steps)
+    layout = K.qwen35_online_decode_workspace_layout(shape_of(ctx0), plan.resolved_mode)
+    dg = act_tensor(gate, K.DTYPE_BF16)
+    rows_k = [act_tensor(k[ctx0 + i], K.DTYPE_BF16) for i in range(steps)]
+    rows_v = [act_tensor(v[ctx0 + i], K.DTYPE_BF16) for i in range(steps)]
+    stream = torch.cuda.current_stream()
+
+    def chain(synchronise):
+        cache = cache_to_device(make_cache(k, v, max_ctx, ctx0))
+        ws = torch.zeros(layout.bytes // 4, device=dev())
+        dq = act_tensor(q, K.DTYPE_BF16).clone()
+        outs = []
+        for i in range(steps):
+            out = torch.zeros(HQ, D, device=dev(), dtype=torch.bfloat16)
+            K.qwen35_online_attention_decode(dq, rows_k[i], rows_v[i], dg, out, cache, cache.numel() * 2, ws,
+                                             layout.bytes, shape_of(ctx0 + i), K.DTYPE_BF16, K.KV_BF16, K.HEAD_MAJOR,
+                                             plan, None, stream)
+            if synchronise:
+                torch.cuda.synchronize()
+            dq = (dq.float() * 0.5 + out.float() * 4.0).to(torch.bfloat16)  # the next query depends on this output
+            if synchronise:
+                torch.cuda.synchronize()
+            outs.append(out)
+        torch.cuda.synchronize()
+        return torch.stack(outs), cache
+
+    loose, loose_cache = chain(False)
+    strict, strict_cache = chain(True)
+    assert K.device_status(stream) == 0
+    assert torch.equal(loose, strict)
+    assert torch.equal(loose_cache, strict_cache)
+
+
 def test_batched_ragged_decode():
     """Five independent sequences with ragged contexts in one launch pair (the batched serving entry point)."""
     contexts = [1, 200, 256, 1000, 2049]
