@@ -78,6 +78,16 @@ typedef struct Rib200AttentionLaunchPolicy {
   uint8_t kv_cache_layout;
 } Rib200AttentionLaunchPolicy;
 
+/* QkNormRopeShape, cpp/kernels/qwen35_primitives.cuh:32-39 */
+typedef struct Rib200QkNormRopeShape {
+  size_t tokens;
+  size_t heads;
+  size_t head_dim;
+  size_t rotary_dim;
+  size_t position_offset;
+  float rope_base;
+} Rib200QkNormRopeShape;
+
 /* cpp/kernels/qwen35_online_attention.cuh:12-21 */
 typedef struct Rib200OnlineDecodePlan {
   uint8_t resolved_mode;
@@ -267,6 +277,33 @@ Rib200Status rib200_online_attention_decode_static_scratch(const void *query, co
                                                            size_t kv_cache_bytes, const Rib200AttentionShape *shape,
                                                            int32_t activation_dtype, const uint32_t *device_position,
                                                            void *stream);
+
+/* ---- the step in front of the attention kernels ----------------------------------------------------
+ * qwen35_qk_norm_rope, cpp/kernels/qwen35_primitives.cuh:61-66 (cpp/kernels/qwen35_primitives.cu:574-626):
+ * per head vector RMSNorm (mean square + epsilon) times weight[head_dim], then NeoX-style RoPE on the first
+ * rotary_dim dims, pairs (i, i + rotary_dim / 2), angle (position_offset or *device_position, plus the token
+ * index) / rope_base^(2 i / rotary_dim).  input, output [tokens][heads][head_dim] in `dtype`.
+ * head_dim 128 or 256; FP32 or BF16 weights. */
+Rib200Status rib200_qk_norm_rope(const void *input, const void *weight, void *output,
+                                 const Rib200QkNormRopeShape *shape, float epsilon, int32_t dtype,
+                                 int32_t weight_dtype, void *stream, const uint32_t *device_position);
+/* qwen35_split_full_query_gate, cpp/kernels/qwen35_primitives.cuh:90-93
+ * (cpp/kernels/qwen35_primitives.cu:743-766): query_gate [tokens][heads][2 * head_dim] -> query, gate
+ * [tokens][heads][head_dim]. */
+Rib200Status rib200_split_full_query_gate(const void *query_gate, void *query, void *gate, size_t tokens,
+                                          size_t heads, size_t head_dim, int32_t dtype, void *stream);
+/* The three calls the executor makes in front of attention (cpp/execution/qwen35_executor.cu:1989-2015:
+ * split_full_query_gate, qk_norm_rope on q, qk_norm_rope on k) as one launch, which also casts v: reads
+ * query_gate [tokens][query_heads][2 * head_dim], key and value [tokens][kv_heads][head_dim] in `dtype`
+ * once and writes query, gate, key_out, value_out in output_dtype (BF16, or `dtype`), ready for
+ * rib200_online_attention_prefill / _decode.  Positions start at shape->past_tokens or *device_position.
+ * No counterpart in the reference as a single entry point. */
+Rib200Status rib200_attention_prologue(const void *query_gate, const void *key, const void *value,
+                                       const void *query_norm_weight, const void *key_norm_weight, void *query,
+                                       void *gate, void *key_out, void *value_out,
+                                       const Rib200AttentionShape *shape, size_t rotary_dim, float rope_base,
+                                       float epsilon, int32_t dtype, int32_t weight_dtype, int32_t output_dtype,
+                                       const uint32_t *device_position, void *stream);
 
 /* ---- head-sharded prefill across the GPUs of one box (no counterpart in the reference) --------------
  * Each rank runs the prefill kernel on its own slice of the heads (its own query/key/value/gate and its

@@ -24,6 +24,11 @@ class AttentionShape(C.Structure):
                 ("max_context_tokens", sz), ("past_tokens", sz)]
 
 
+class QkNormRopeShape(C.Structure):
+    _fields_ = [("tokens", sz), ("heads", sz), ("head_dim", sz), ("rotary_dim", sz), ("position_offset", sz),
+                ("rope_base", C.c_float)]
+
+
 class AttentionLaunchPolicy(C.Structure):
     _fields_ = [("implementation", C.c_uint8), ("kv_cache_dtype", C.c_uint8), ("kv_cache_layout", C.c_uint8)]
 
@@ -83,6 +88,10 @@ PROTOTYPES = {
     "rib200_online_attention_prefill_scatter": [vp, vp, vp, vp, C.POINTER(vp), sz, sz, sz, sz, vp, sz,
                                                 C.POINTER(AttentionShape), C.c_int32, C.c_uint8, C.c_uint8, vp],
     "rib200_peer_rendezvous": [C.POINTER(vp), sz, sz, C.c_uint32, vp],
+    "rib200_qk_norm_rope": [vp, vp, vp, C.POINTER(QkNormRopeShape), C.c_float, C.c_int32, C.c_int32, vp, vp],
+    "rib200_split_full_query_gate": [vp, vp, vp, sz, sz, sz, C.c_int32, vp],
+    "rib200_attention_prologue": [vp, vp, vp, vp, vp, vp, vp, vp, vp, C.POINTER(AttentionShape), sz, C.c_float,
+                                  C.c_float, C.c_int32, C.c_int32, C.c_int32, vp, vp],
     "rib200_shared_alloc": [sz, C.POINTER(vp), C.POINTER(C.c_uint8)],
     "rib200_shared_open": [C.POINTER(C.c_uint8), C.POINTER(vp)],
     "rib200_shared_close": [vp],

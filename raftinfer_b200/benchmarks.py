@@ -188,12 +188,53 @@ def prefill_attention(dev, stream, tensor_peak, token_counts=(128, 512, 4096)):
     return res
 
 
+def attention_prologue(dev, stream, hbm_peak, tokens=4096, rotary=64):
+    """The step in front of attention on FP32 projections (what the executor's full layers produce): query/gate
+    split, RMSNorm with weight and partial RoPE on q and k, casts of gate and v to BF16 - as one launch, and as the
+    reference's sequence of three calls (split, qk_norm_rope on q, qk_norm_rope on k) in FP32."""
+    gen = torch.Generator(device=dev).manual_seed(29)
+    packed = torch.randn(tokens, HQ, 2 * D, device=dev, generator=gen)
+    k = torch.randn(tokens, HKV, D, device=dev, generator=gen)
+    v = torch.randn(tokens, HKV, D, device=dev, generator=gen)
+    qw = 1.0 + 0.1 * torch.randn(D, device=dev, generator=gen)
+    kw = 1.0 + 0.1 * torch.randn(D, device=dev, generator=gen)
+    bf = lambda *shape: torch.zeros(*shape, device=dev, dtype=torch.bfloat16)
+    fq, fg, fk, fv = bf(tokens, HQ, D), bf(tokens, HQ, D), bf(tokens, HKV, D), bf(tokens, HKV, D)
+    shape = K.Qwen35AttentionShape(tokens, HQ, HKV, D, tokens, 0)
+
+    def fused(i):
+        K.attention_prologue(packed, k, v, qw, kw, fq, fg, fk, fv, shape, rotary, 1.0e7, 1.0e-6, K.DTYPE_F32,
+                             K.DTYPE_F32, K.DTYPE_BF16, stream)
+
+    q0, g0 = torch.zeros(tokens, HQ, D, device=dev), torch.zeros(tokens, HQ, D, device=dev)
+    qn, kn = torch.zeros_like(q0), torch.zeros_like(k)
+
+    def three_calls(i):
+        K.qwen35_split_full_query_gate(packed, q0, g0, tokens, HQ, D, K.DTYPE_F32, stream)
+        K.qwen35_qk_norm_rope(q0, qw, qn, K.QkNormRopeShape(tokens, HQ, D, rotary, 0, 1.0e7), 1.0e-6, K.DTYPE_F32,
+                              K.DTYPE_F32, stream)
+        K.qwen35_qk_norm_rope(k, kw, kn, K.QkNormRopeShape(tokens, HKV, D, rotary, 0, 1.0e7), 1.0e-6, K.DTYPE_F32,
+                              K.DTYPE_F32, stream)
+
+    elements = tokens * (2 * HQ + 2 * HKV) * D
+    fused_bytes = elements * 4 + elements * 2          # every projection element read once, written once as BF16
+    three_bytes = tokens * HQ * D * 4 * (2 + 2 + 2) + tokens * HKV * D * 4 * 2  # split r+w, q r+w, k r+w
+    ms, cv = _median_ms(fused, stream, warmup=3, reps=10, calls=4)
+    ms3, cv3 = _median_ms(three_calls, stream, warmup=3, reps=10, calls=4)
+    return {"tokens": tokens,
+            "fused": {"ms": ms, "cv": cv, "bytes": fused_bytes, "GB/s": fused_bytes / ms / 1e6,
+                      "frac_of_measured_hbm": fused_bytes / ms / 1e6 / hbm_peak},
+            "three_calls_f32": {"ms": ms3, "cv": cv3, "bytes": three_bytes, "GB/s": three_bytes / ms3 / 1e6,
+                                "frac_of_measured_hbm": three_bytes / ms3 / 1e6 / hbm_peak}}
+
+
 def run(dev, stream, hbm_peak, tensor_peak):
     extra = {}
     for name, fn in (("decode_attention", lambda: decode_contexts(dev, stream, hbm_peak)),
                      ("batched_serving_decode", lambda: batched_serving_decode(dev, stream, hbm_peak)),
                      ("gated_delta", lambda: gdn_layer(dev, stream, hbm_peak, tensor_peak)),
-                     ("prefill_attention", lambda: prefill_attention(dev, stream, tensor_peak))):
+                     ("prefill_attention", lambda: prefill_attention(dev, stream, tensor_peak)),
+                     ("attention_prologue", lambda: attention_prologue(dev, stream, hbm_peak))):
         try:
             extra[name] = fn()
         except (K.Qwen35PrimitiveError, K.Qwen35DeltaError) as err:
@@ -358,7 +399,7 @@ def main(argv=None):
     if os.path.exists(peaks_path):
         peaks = json.load(open(peaks_path))
         hbm, tensor = float(peaks["hbm_gbs"]), float(peaks["bf16_tflops"])
-    want = set(args.sections) or {"decode", "serving", "gdn", "prefill"}
+    want = set(args.sections) or {"decode", "serving", "gdn", "prefill", "prologue"}
     out = {}
     if "decode" in want:
         out["decode_attention"] = decode_contexts(dev, stream, hbm, tuple(args.contexts or (4096, 32768, 131072)))
@@ -368,6 +409,8 @@ def main(argv=None):
         out["gated_delta"] = gdn_layer(dev, stream, hbm, tensor, tokens=args.gdn_tokens)
     if "prefill" in want:
         out["prefill_attention"] = prefill_attention(dev, stream, tensor, tuple(args.tokens or (128, 512, 4096)))
+    if "prologue" in want:
+        out["attention_prologue"] = attention_prologue(dev, stream, hbm)
     print(json.dumps(out))
     return out
 

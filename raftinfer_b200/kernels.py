@@ -203,6 +203,45 @@ def qwen35_online_attention_prefill(query, key, value, gate, output, kv_cache, k
                                                cache_dtype, cache_layout, _stream(stream)))
 
 
+@dataclass(frozen=True)
+class QkNormRopeShape:
+    """cpp/kernels/qwen35_primitives.cuh:32-39"""
+    tokens: int
+    heads: int
+    head_dim: int
+    rotary_dim: int
+    position_offset: int
+    rope_base: float
+
+    def c(self):
+        return _lib.QkNormRopeShape(self.tokens, self.heads, self.head_dim, self.rotary_dim, self.position_offset,
+                                    self.rope_base)
+
+
+def qwen35_qk_norm_rope(input, weight, output, shape, epsilon, dtype, weight_dtype, stream, device_position=None):
+    """cpp/kernels/qwen35_primitives.cuh:61-66"""
+    s = shape.c()
+    _check(lib.rib200_qk_norm_rope(_ptr(input), _ptr(weight), _ptr(output), C.byref(s), epsilon, dtype, weight_dtype,
+                                   _stream(stream), _ptr(device_position)))
+
+
+def qwen35_split_full_query_gate(query_gate, query, gate, tokens, heads, head_dim, dtype, stream):
+    """cpp/kernels/qwen35_primitives.cuh:90-93"""
+    _check(lib.rib200_split_full_query_gate(_ptr(query_gate), _ptr(query), _ptr(gate), tokens, heads, head_dim, dtype,
+                                            _stream(stream)))
+
+
+def attention_prologue(query_gate, key, value, query_norm_weight, key_norm_weight, query, gate, key_out, value_out,
+                       shape, rotary_dim, rope_base, epsilon, dtype, weight_dtype, output_dtype, stream,
+                       device_position=None):
+    """The executor's three pre-attention calls (cpp/execution/qwen35_executor.cu:1989-2015) as one launch."""
+    s = shape.c()
+    _check(lib.rib200_attention_prologue(_ptr(query_gate), _ptr(key), _ptr(value), _ptr(query_norm_weight),
+                                         _ptr(key_norm_weight), _ptr(query), _ptr(gate), _ptr(key_out),
+                                         _ptr(value_out), C.byref(s), rotary_dim, rope_base, epsilon, dtype,
+                                         weight_dtype, output_dtype, _ptr(device_position), _stream(stream)))
+
+
 def online_attention_prefill_scatter(query, key, value, gate, outputs, rank, total_query_heads, head_offset, kv_cache,
                                      kv_cache_bytes, shape, activation_dtype, cache_dtype, cache_layout, stream):
     """Head-sharded prefill: `outputs` lists every rank's full-width output buffer (pointers or tensors valid on
