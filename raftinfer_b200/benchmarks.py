@@ -185,6 +185,20 @@ def prefill_attention(dev, stream, tensor_peak, token_counts=(128, 512, 4096)):
         flops = 4 * HQ * D * (tokens * past + tokens * (tokens + 1) // 2)
         res[f"T{tokens}_past{past}"] = {"ms": ms, "cv": cv, "flops": flops, "TFLOP/s": flops / ms / 1e9,
                                         "frac_of_measured_bf16_peak": flops / ms / 1e9 / tensor_peak}
+        if tokens == max(token_counts) and past == 0:
+            # the same call on FP32 activations (what the reference's executor passes): Q is rounded to BF16 inside
+            # the kernel, K and V by the append kernel in front of it
+            q32, g32, k32, v32 = q.float(), gate.float(), k.float(), v.float()
+            o32 = torch.zeros(tokens, HQ, D, device=dev)
+
+            def fn32(i):
+                K.qwen35_online_attention_prefill(q32, k32, v32, g32, o32, cache, cache.numel() * 2, shape, K.DTYPE_F32,
+                                                  K.KV_BF16, K.HEAD_MAJOR, stream)
+
+            ms, cv = _median_ms(fn32, stream, warmup=3, reps=10, calls=4)
+            res[f"T{tokens}_past{past}_f32_activations"] = {
+                "ms": ms, "cv": cv, "flops": flops, "TFLOP/s": flops / ms / 1e9,
+                "frac_of_measured_bf16_peak": flops / ms / 1e9 / tensor_peak}
     return res
 
 

@@ -1079,10 +1079,32 @@ __global__ void __launch_bounds__(kThreads, 1)
       exchange[(sums + group) * kTileRows + row] = l_sum;
       asm volatile("bar.sync 1, 256;\n" ::: "memory");
       const float inv = 1.0F / (l_sum + exchange[(sums + (group ^ 1)) * kTileRows + row]);
+      // FP32 gates cannot all wait in registers as the BF16 ones do: they are fetched one 32-column piece ahead
+      float4 gate_now[F32 ? 8 : 1];
+      if constexpr (F32) {
+        if (live) {
+          const float4 *gsrc = reinterpret_cast<const float4 *>(static_cast<const float *>(p.gate) + out_base);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            gate_now[i] = gsrc[i];
+          }
+        }
+      }
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         std::uint32_t v[32];
         tmem_ld32(tmem_o + lane_base + group * 128 + c * 32, v);
+        float4 gate_next[F32 ? 8 : 1];
+        if constexpr (F32) {
+          if (live && c < 3) {
+            const float4 *gsrc =
+                reinterpret_cast<const float4 *>(static_cast<const float *>(p.gate) + out_base + (c + 1) * 32);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              gate_next[i] = gsrc[i];
+            }
+          }
+        }
         tmem_wait_ld();
         if (c == 3) {
           // O has been read: the next tile's first PV may overwrite it
@@ -1091,10 +1113,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         if (live) {
           if constexpr (F32) {
-            const float *gsrc = static_cast<const float *>(p.gate) + out_base + c * 32;
 #pragma unroll
             for (int e = 0; e < 32; e += 4) {
-              const float4 gv = *reinterpret_cast<const float4 *>(gsrc + e);
+              const float4 gv = gate_now[e / 4];
               float4 r;
               r.x = __uint_as_float(v[e + 0]) * inv * fast_sigmoid(gv.x);
               r.y = __uint_as_float(v[e + 1]) * inv * fast_sigmoid(gv.y);
@@ -1119,6 +1140,12 @@ __global__ void __launch_bounds__(kThreads, 1)
               *reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.output) + dst_base + c * 32 + e) =
                   make_uint4(ow[0], ow[1], ow[2], ow[3]);
             }
+          }
+        }
+        if constexpr (F32) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            gate_now[i] = gate_next[i];
           }
         }
       }
