@@ -14,7 +14,9 @@
 //            stores once the MMAs have consumed it: that is this chunk's append (BF16 inputs are stored as they
 //            are, which is what the reference's append writes).  A separate append kernel runs first only for
 //            FP32 inputs (converted nearest-even) and for the rows that share a key block with the past; the
-//            producer waits for it (programmatic dependent launch) before it reads such rows.
+//            producer waits for it (programmatic dependent launch) before it reads such rows.  For FP32 inputs
+//            that kernel also rounds the queries to BF16 and parks each Q tile in the rows of the output buffer
+//            that the same tile will overwrite with its result, which is where the producer loads it from.
 //   warp 9   MMA issue.  The whole warp walks the loops and one elected lane issues tcgen05.mma (BF16 in, FP32
 //            accumulate in tensor memory), so ring positions and descriptors stay warp-uniform.  Tensor memory holds
 //            the output tile O (128 lanes x 256 columns) and two score tiles S (128 x 128 each): 512 columns in all.
@@ -398,16 +400,41 @@ __device__ __forceinline__ std::uint32_t pack_bf16(float lo, float hi) {
 }
 
 // ---- append: K and V of this chunk into the cache -----------------------------------------------------
+// For FP32 activations it also rounds the queries to BF16.  There is no workspace on this path, so the BF16 copy of
+// the Q tile of (tile, head) is parked in the first half of that tile's own rows of the output buffer: the attention
+// kernel loads it from there with TMA at the start of the tile and overwrites it with the FP32 result at its end.
 template <bool F32>
 __global__ void __launch_bounds__(256) prefill_append_kernel(const void *key, const void *value,
                                                              __nv_bfloat16 *cache, std::uint32_t tokens,
                                                              std::uint32_t past, std::uint32_t max_ctx,
-                                                             std::uint32_t kv_heads) {
+                                                             std::uint32_t kv_heads, const float *query,
+                                                             void *q_parking, std::uint32_t q_tokens,
+                                                             std::uint32_t q_heads, std::uint32_t out_heads,
+                                                             std::uint32_t out_head_offset) {
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   // one thread per 8 elements: [plane][token][kv head][32 pieces of 8]
   const std::size_t pieces = static_cast<std::size_t>(tokens) * kv_heads * 32;
   const std::size_t id = static_cast<std::size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (id >= 2 * pieces) {
+    if constexpr (F32) {
+      const std::size_t q_id = id - 2 * pieces;
+      if (q_id < static_cast<std::size_t>(q_tokens) * q_heads * 32) {
+        const std::uint32_t piece = static_cast<std::uint32_t>(q_id % 32);
+        const std::uint32_t head = static_cast<std::uint32_t>((q_id / 32) % q_heads);
+        const std::size_t token = q_id / (32 * static_cast<std::size_t>(q_heads));
+        const float *src = query + (token * q_heads + head) * kHeadDim + piece * 8;
+        const float4 a = *reinterpret_cast<const float4 *>(src);
+        const float4 b = *reinterpret_cast<const float4 *>(src + 4);
+        uint4 raw;
+        raw.x = pack_bf16(a.x, a.y);
+        raw.y = pack_bf16(a.z, a.w);
+        raw.z = pack_bf16(b.x, b.y);
+        raw.w = pack_bf16(b.z, b.w);
+        unsigned char *row = static_cast<unsigned char *>(q_parking) +
+                             (token * out_heads + out_head_offset + head) * (kHeadDim * 4);
+        *reinterpret_cast<uint4 *>(row + piece * 16) = raw;
+      }
+    }
     return;
   }
   const bool is_value = id >= pieces;
@@ -492,7 +519,7 @@ __global__ void __launch_bounds__(kThreads, 1)
   };
 
   if (threadIdx.x == 0) {
-    mbar_init(bar(kBarQFull), F32 ? kRowThreads : 1);
+    mbar_init(bar(kBarQFull), 1);
     mbar_init(bar(kBarQFree), 1);
     mbar_init(bar(kBarDrain), 1);
     mbar_init(bar(kBarOFree), kRowThreads);
@@ -610,7 +637,28 @@ __global__ void __launch_bounds__(kThreads, 1)
             break;
           }
         }
-        if constexpr (!F32) {
+        if constexpr (F32) {
+          // the BF16 queries wait in the output buffer, where the kernel in front of this one parked them:
+          // q_map is [256][output heads][token] there
+          wait_for_append();
+          const int parked_head = static_cast<int>(p.output_head_offset + head);
+          if constexpr (Pair) {
+            if (rank == 0) {
+              mbar_expect_tx(bar(kBarQFull), 2 * kQBytes);
+            }
+            const std::uint32_t leader_bar = map_to_rank(bar(kBarQFull), 0);
+            for (int b = 0; b < 4; ++b) {
+              tma_load_3d_pair(q_smem + b * kQBoxBytes, &q_map, b * kBoxCols, parked_head, static_cast<int>(row0),
+                               leader_bar);
+            }
+          } else {
+            mbar_expect_tx(bar(kBarQFull), kQBytes);
+            for (int b = 0; b < 4; ++b) {
+              tma_load_3d(q_smem + b * kQBoxBytes, &q_map, b * kBoxCols, parked_head, static_cast<int>(row0),
+                          bar(kBarQFull));
+            }
+          }
+        } else {
           if constexpr (Pair) {
             if (rank == 0) {
               mbar_expect_tx(bar(kBarQFull), 2 * kQBytes); // both CTAs' Q tiles count on the leader's barrier
@@ -888,41 +936,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       const std::uint32_t rows = tile_rows(walk.tile());
       const std::uint32_t blocks = tile_blocks(walk.tile());
       const std::uint32_t q_pos = p.past + row0 + row; // position of this row's query (rows past the tile are idle)
-
-      if constexpr (F32) {
-        // FP32 queries: round to BF16 and lay the tile out by hand in the swizzled form TMA would have produced.
-        // Each group converts its 128 of the 256 dims.
-        if (walk.iteration > 0) {
-          ok = mbar_wait(bar(kBarQFree), (walk.iteration - 1) & 1U, abort_flag);
-          ok = __all_sync(0xFFFFFFFFU, ok);
-          if (!ok) {
-            break;
-          }
-        }
-        const float *src = static_cast<const float *>(query_f32) +
-                           (static_cast<std::size_t>(row0 + row) * p.query_heads + head) * kHeadDim;
-        const bool live = row < rows;
-#pragma unroll 4
-        for (int cc = 0; cc < 16; ++cc) { // 16 chunks of 8 dims
-          const int c = group * 16 + cc;
-          float4 a = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
-          float4 b = a;
-          if (live) {
-            a = *reinterpret_cast<const float4 *>(src + 8 * c);
-            b = *reinterpret_cast<const float4 *>(src + 8 * c + 4);
-          }
-          uint4 raw;
-          raw.x = pack_bf16(a.x, a.y);
-          raw.y = pack_bf16(a.z, a.w);
-          raw.z = pack_bf16(b.x, b.y);
-          raw.w = pack_bf16(b.z, b.w);
-          const std::uint32_t box = c >> 3;
-          const std::uint32_t chunk = (c & 7) ^ (row & 7);
-          *reinterpret_cast<uint4 *>(smem + box * kQBoxBytes + row * 128 + chunk * 16) = raw;
-        }
-        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-        arrive_on_leader(kBarQFull);
-      }
 
       float m_used = -INFINITY; // maximum the exponentials are taken against (scaled, base 2); same in both groups
       float l_sum = 0.0F;       // this thread's share of the row sum
@@ -1276,10 +1289,16 @@ template <bool F32, bool Pair> void launch(const PrefillArgs &a, cudaStream_t st
   // block with the past.
   const std::uint32_t ragged = a.past_tokens % kBlockKeys == 0 ? 0U : kBlockKeys - a.past_tokens % kBlockKeys;
   const std::uint32_t append_rows = F32 ? a.tokens : std::min<std::uint32_t>(a.tokens, ragged);
+  // where this GPU's output tiles go (the head-sharded form writes into a wider buffer at a head offset)
+  void *own_output = a.output_count == 0 ? a.output : a.outputs[a.output_self];
+  const std::uint32_t out_heads = a.output_count == 0 ? a.query_heads : a.output_heads;
+  const std::uint32_t out_head_offset = a.output_count == 0 ? 0U : a.output_head_offset;
   if (append_rows > 0) {
-    const std::size_t pieces = static_cast<std::size_t>(append_rows) * a.kv_heads * 32 * 2;
-    prefill_append_kernel<F32><<<static_cast<unsigned int>((pieces + 255) / 256), 256, 0, stream>>>(
-        a.key, a.value, cache, append_rows, a.past_tokens, a.max_context_tokens, a.kv_heads);
+    const std::size_t kv_pieces = static_cast<std::size_t>(append_rows) * a.kv_heads * 32 * 2;
+    const std::size_t q_pieces = F32 ? static_cast<std::size_t>(a.tokens) * a.query_heads * 32 : 0; // parked queries
+    prefill_append_kernel<F32><<<static_cast<unsigned int>((kv_pieces + q_pieces + 255) / 256), 256, 0, stream>>>(
+        a.key, a.value, cache, append_rows, a.past_tokens, a.max_context_tokens, a.kv_heads,
+        static_cast<const float *>(a.query), own_output, a.tokens, a.query_heads, out_heads, out_head_offset);
     cuda_ok(cudaGetLastError(), "prefill append launch");
   }
 
@@ -1304,9 +1323,15 @@ template <bool F32, bool Pair> void launch(const PrefillArgs &a, cudaStream_t st
     k_new_map = make_map(const_cast<void *>(a.key), 3, new_dims, new_strides, Pair ? short_box : tall_box);
     v_new_map = make_map(const_cast<void *>(a.value), 3, new_dims, new_strides, Pair ? tall_box : short_box);
   }
-  // Q: [token][query_heads * 256] (BF16 activations only; FP32 queries are converted inside the kernel)
+  // Q: [token][query_heads * 256] for BF16 activations; for FP32 the BF16 copy parked in the output buffer,
+  // [256][output heads][token] with 1024-byte head slots
   CUtensorMap q_map = k_map;
-  if (!F32) {
+  if (F32) {
+    const cuuint64_t q_dims[3] = {kHeadDim, out_heads, a.tokens};
+    const cuuint64_t q_strides[2] = {kHeadDim * 4, static_cast<cuuint64_t>(out_heads) * kHeadDim * 4};
+    const cuuint32_t q_box[3] = {kBoxCols, 1, kTileRows};
+    q_map = make_map(own_output, 3, q_dims, q_strides, q_box);
+  } else {
     const cuuint64_t q_dims[2] = {static_cast<cuuint64_t>(a.query_heads) * kHeadDim, a.tokens};
     const cuuint64_t q_strides[1] = {static_cast<cuuint64_t>(a.query_heads) * kHeadDim * 2};
     const cuuint32_t q_box[2] = {kBoxCols, kTileRows};
