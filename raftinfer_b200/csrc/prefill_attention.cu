@@ -31,6 +31,9 @@
 //            store the tile at the end.
 // Pair form (GQA group even): the two CTAs of a cluster take two query heads of one KV head at the same tile and
 // run as one tcgen05 cta_group::2 unit (M = 256); each CTA loads half of every K block and half of every V block.
+// Split form (few items, many key blocks each: a 512-token chunk against a long past): a second CTA (or pair)
+// of the cluster takes the second half of an item's key blocks and hands its partial tile over through
+// distributed shared memory at the end.
 //
 // Work per launch: 4 * heads * 256 * (T * P + T (T + 1) / 2) flops for T new tokens after P past tokens.
 // Every wait on an mbarrier is bounded; when one runs out the CTA records RIB200_DEVICE_WAIT_TIMED_OUT, nothing
@@ -46,6 +49,7 @@
 #include <cstdint>
 #include <cstdlib>
 #include <mutex>
+#include <type_traits>
 
 namespace rib200 {
 namespace {
@@ -86,7 +90,10 @@ enum : int {
   kBarQFree = 7 + 2 * kSlots,  // the tile's last score product has read Q
   kBarOFree = 8 + 2 * kSlots,  // the tile's epilogue has read O
   kBarDrain = 9 + 2 * kSlots,  // used once, by a CTA that has given up: its MMAs have drained
-  kBarCount = 10 + 2 * kSlots
+  kBarPeerFull = 10 + 2 * kSlots, // split form: the partner's partial result has landed in this CTA's ring
+  kBarPeerFree = 11 + 2 * kSlots, // split form: the partner's ring may be written
+  kBarStoresDone = 12 + 2 * kSlots, // split form: the producer's write-backs to the cache have read their slots
+  kBarCount = 13 + 2 * kSlots
 };
 
 // Optional timeline probe (compile with -DRIB200_TRACE): the first CTA of the grid stamps clock64() at the
@@ -105,8 +112,17 @@ __device__ __forceinline__ long long global_ns() {
       g_trace[(block) * 16 + (slot)] = clock64();                                   \
     }                                                                               \
   } while (0)
+#define RIB200_STAMP_CTA2(slot)                                                     \
+  do {                                                                              \
+    if (blockIdx.x == 2 && blockIdx.y == 0) {                                       \
+      g_trace[120 * 16 + (slot)] = clock64();                                       \
+    }                                                                               \
+  } while (0)
 #else
 #define RIB200_STAMP(block, slot)                                                   \
+  do {                                                                              \
+  } while (0)
+#define RIB200_STAMP_CTA2(slot)                                                     \
   do {                                                                              \
   } while (0)
 #endif
@@ -243,6 +259,29 @@ __device__ __forceinline__ std::uint32_t map_to_rank(std::uint32_t addr, std::ui
 
 __device__ __forceinline__ void mbar_arrive_cluster(std::uint32_t cluster_bar) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_bar) : "memory");
+}
+
+// arrive that publishes this thread's earlier writes (also those into the partner's shared memory) to the cluster
+__device__ __forceinline__ void mbar_arrive_cluster_release(std::uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void fence_cluster() { asm volatile("fence.acq_rel.cluster;\n" ::: "memory"); }
+__device__ __forceinline__ void st_cluster_v4(std::uint32_t cluster_addr, float a, float b, float c, float d) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"r"(cluster_addr), "f"(a), "f"(b), "f"(c),
+               "f"(d)
+               : "memory");
+}
+__device__ __forceinline__ void st_cluster_f32(std::uint32_t cluster_addr, float a) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(cluster_addr), "f"(a) : "memory");
+}
+
+// bulk copy from this CTA's shared memory into another CTA of the cluster; the bytes count on a barrier there
+__device__ __forceinline__ void bulk_copy_to_cluster(std::uint32_t cluster_dst, std::uint32_t cta_src,
+                                                     std::uint32_t bytes, std::uint32_t cluster_bar) {
+  asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+                   cluster_dst),
+               "r"(cta_src), "r"(bytes), "r"(cluster_bar)
+               : "memory");
 }
 
 __device__ __forceinline__ void cluster_sync_all() {
@@ -484,7 +523,18 @@ struct TileWalk {
 // of every K and V block (the MMA reads the B operand from both CTAs' shared memory).  That halves the bytes an
 // SM pulls from L2 per block.  Every TMA load has one destination CTA; the completion signals that both CTAs need
 // are two plain tcgen05.commit instructions, one per CTA's barrier.
-template <bool F32, bool Pair>
+//
+// Split == true is for launches with so few (tile, head) items that half of the SMs would idle (a 512-token chunk
+// against a long past): the two CTAs of a cluster take the same item and each runs the ordinary single-CTA loop
+// over half of its key blocks; at the end the second CTA ships its unnormalised O tile and its (maximum, row sum)
+// into the first one's ring through distributed shared memory, and the first merges the two and writes the tile.
+// One item per cluster, so the ring is free when the partial arrives.
+constexpr int kLandingPitch = kHeadDim * 4 + 16;                 // bytes per row of a partial O tile in the ring
+constexpr int kLandingMeta = kTileRows * kLandingPitch;          // then [group][row] maximum, [group][row] row sum
+constexpr int kLandingBytes = kLandingMeta + 4 * kTileRows * 4;
+static_assert(kLandingBytes <= kSlots * kSlotBytes && kLandingBytes % 16 == 0, "partial tile must fit in the ring");
+
+template <bool F32, bool Pair, bool Split>
 __global__ void __launch_bounds__(kThreads, 1)
     prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                              const __grid_constant__ CUtensorMap v_map, const __grid_constant__ CUtensorMap k_new_map,
@@ -505,14 +555,22 @@ __global__ void __launch_bounds__(kThreads, 1)
 #endif
   const int warp = __shfl_sync(0xFFFFFFFFU, threadIdx.x >> 5, 0); // a value the compiler knows to be warp-uniform
   const int lane = threadIdx.x & 31;
-  const std::uint32_t rank = Pair ? cluster_rank() : 0U;       // 0 leads the pair
-  const std::uint32_t unit = Pair ? blockIdx.x >> 1 : blockIdx.x; // index of this CTA (or pair) among its peers
-  const std::uint32_t units = Pair ? gridDim.x >> 1 : gridDim.x;
+  // A cluster is a pair of heads, a split of one item, or both: CTAs 0, 1 the pair that takes the first half of
+  // the keys, CTAs 2, 3 the pair that takes the second half.
+  constexpr bool kCluster = Pair || Split;
+  constexpr std::uint32_t kClusterSize = (Pair ? 2U : 1U) * (Split ? 2U : 1U);
+  const std::uint32_t cta = kCluster ? cluster_rank() : 0U;
+  const std::uint32_t rank = Pair ? cta & 1U : 0U;                  // place in the pair: 0 leads it
+  const std::uint32_t lead_cta = Pair ? cta & ~1U : cta;            // cluster rank of the pair's leader
+  const std::uint32_t half = Split ? (Pair ? cta >> 1 : cta) : 0U;  // which half of the keys
+  const std::uint32_t half_stride = Pair ? 2U : 1U;                 // cluster ranks between the two halves
+  const std::uint32_t unit = blockIdx.x / kClusterSize;             // index of this cluster among its peers
+  const std::uint32_t units = gridDim.x / kClusterSize;
   constexpr std::uint32_t kRowThreads = Pair ? 2 * kSoftmaxThreads : kSoftmaxThreads; // softmax threads per unit
   // barriers every softmax thread of the unit arrives on live in the leader
   auto arrive_on_leader = [&](int index) {
     if constexpr (Pair) {
-      mbar_arrive_cluster(map_to_rank(bar(index), 0));
+      mbar_arrive_cluster(map_to_rank(bar(index), lead_cta));
     } else {
       mbar_arrive(bar(index));
     }
@@ -522,6 +580,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     mbar_init(bar(kBarQFull), 1);
     mbar_init(bar(kBarQFree), 1);
     mbar_init(bar(kBarDrain), 1);
+    mbar_init(bar(kBarPeerFull), 1);
+    mbar_init(bar(kBarPeerFree), kSoftmaxThreads);
+    mbar_init(bar(kBarStoresDone), 1);
     mbar_init(bar(kBarOFree), kRowThreads);
     for (int s = 0; s < kSlots; ++s) {
       mbar_init(bar(kBarFull + s), 1);
@@ -551,10 +612,18 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
   tcgen05_fence_before();
   __syncthreads();
-  if constexpr (Pair) {
+  if constexpr (kCluster) {
     cluster_sync_all(); // the partner's barriers exist before anything arrives on them
   }
   tcgen05_fence_after();
+  if constexpr (Split) {
+    if (half == 0 && threadIdx.x == 0) {
+      mbar_expect_tx(bar(kBarPeerFull), kLandingBytes); // the partner's partial tile, one bulk copy
+    }
+  }
+  if (threadIdx.x == 0) {
+    RIB200_STAMP(0, 14); // set-up done
+  }
   const std::uint32_t tmem = *tmem_slot;
   const std::uint32_t tmem_o = tmem;         // columns [0, 256)
   const std::uint32_t tmem_s = tmem + 256;   // two tiles of 128 columns
@@ -565,6 +634,12 @@ __global__ void __launch_bounds__(kThreads, 1)
   };
   auto tile_blocks = [&](std::uint32_t tile) {
     return (p.past + tile * kTileRows + tile_rows(tile) - 1) / kBlockKeys + 1; // newest visible key / 128 + 1
+  };
+  // the key blocks this CTA walks: all of them, or its half in the split form
+  auto first_block = [&](std::uint32_t tile) { return Split && half == 1 ? (tile_blocks(tile) + 1) / 2 : 0U; };
+  auto my_blocks = [&](std::uint32_t tile) {
+    const std::uint32_t all = tile_blocks(tile);
+    return Split ? (half == 0 ? (all + 1) / 2 : all - (all + 1) / 2) : all;
   };
 
   if (warp == kProducerWarp) {
@@ -629,7 +704,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         const std::uint32_t head = Pair ? walk.head() * 2 + rank : walk.head();
         const std::uint32_t kv_head = head / p.group;
         const std::uint32_t row0 = walk.tile() * kTileRows;
-        const std::uint32_t blocks = tile_blocks(walk.tile());
+        const std::uint32_t all_blocks = tile_blocks(walk.tile());
+        const std::uint32_t block0 = first_block(walk.tile()); // this CTA walks blocks block0 .. block0 + blocks - 1
+        const std::uint32_t blocks = my_blocks(walk.tile());
         if (walk.iteration > 0) {
           // the previous tile's last score product has finished reading Q
           ok = mbar_wait(bar(kBarQFree), (walk.iteration - 1) & 1U, abort_flag);
@@ -646,7 +723,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (rank == 0) {
               mbar_expect_tx(bar(kBarQFull), 2 * kQBytes);
             }
-            const std::uint32_t leader_bar = map_to_rank(bar(kBarQFull), 0);
+            const std::uint32_t leader_bar = map_to_rank(bar(kBarQFull), lead_cta);
             for (int b = 0; b < 4; ++b) {
               tma_load_3d_pair(q_smem + b * kQBoxBytes, &q_map, b * kBoxCols, parked_head, static_cast<int>(row0),
                                leader_bar);
@@ -663,7 +740,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (rank == 0) {
               mbar_expect_tx(bar(kBarQFull), 2 * kQBytes); // both CTAs' Q tiles count on the leader's barrier
             }
-            const std::uint32_t leader_bar = map_to_rank(bar(kBarQFull), 0);
+            const std::uint32_t leader_bar = map_to_rank(bar(kBarQFull), lead_cta);
             for (int b = 0; b < 4; ++b) {
               tma_load_2d_pair(q_smem + b * kQBoxBytes, &q_map, static_cast<int>(head * kHeadDim + b * kBoxCols),
                                static_cast<int>(row0), leader_bar);
@@ -697,7 +774,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           const CUtensorMap *k_src = from_inputs ? &k_new_map : &k_map;
           const CUtensorMap *v_src = from_inputs ? &v_new_map : &v_map;
           const int block_key0 = static_cast<int>(block * kBlockKeys - (from_inputs ? p.past : 0U));
-          if (appends && from_inputs && block + 1 == blocks) {
+          if (appends && from_inputs && block + 1 == all_blocks) {
             pending[slot] = 0x80000000U | (is_value ? 0x40000000U : 0U) | (half << 29) | (kv_head << 16) | block;
           }
           if constexpr (Pair) {
@@ -705,7 +782,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (rank == 0) {
               mbar_expect_tx(bar(kBarFull + slot), 2 * kSlotBytes);
             }
-            const std::uint32_t leader_bar = map_to_rank(bar(kBarFull + slot), 0);
+            const std::uint32_t leader_bar = map_to_rank(bar(kBarFull + slot), lead_cta);
             const int key0 = block_key0;
             if (is_value) {
               for (int b = 0; b < 2; ++b) {
@@ -739,15 +816,15 @@ __global__ void __launch_bounds__(kThreads, 1)
           return true;
         };
         constexpr std::uint32_t kParts = Pair ? 1 : 2; // ring slots per block and operand
-        for (std::uint32_t h = 0; ok && h < kParts; ++h) {
-          ok = load_half(false, 0, h);
+        for (std::uint32_t h = 0; ok && h < kParts && blocks > 0; ++h) {
+          ok = load_half(false, block0, h);
         }
         for (std::uint32_t j = 0; ok && j < blocks; ++j) {
           for (std::uint32_t h = 0; ok && h < kParts && j + 1 < blocks; ++h) {
-            ok = load_half(false, j + 1, h);
+            ok = load_half(false, block0 + j + 1, h);
           }
           for (std::uint32_t h = 0; ok && h < kParts; ++h) {
-            ok = load_half(true, j, h);
+            ok = load_half(true, block0 + j, h);
           }
         }
       }
@@ -762,6 +839,9 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
       }
+      if constexpr (Split) {
+        mbar_arrive(bar(kBarStoresDone)); // every write-back has read its slot: the ring may hold the partial tile
+      }
       tma_store_wait_all();
       // this grid never completes before the append kernel has: work queued behind it sees the cache rows
       wait_for_append();
@@ -772,7 +852,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     // lane and can live in uniform registers (where tcgen05.mma takes its operands from); one elected lane issues
     // the MMAs and the commits.  A wait that runs out flags the CTA, and from then on nothing waits: the warp runs
     // through its remaining tiles on stale operands rather than leave a loop early.
-    if (rank == 0) {
+    if (!Pair || rank == 0) {
       const bool leader = elect_one();
       constexpr int kUnitRows = Pair ? 2 * kTileRows : kTileRows;
       constexpr std::uint32_t kIdescQk = instr_desc(kUnitRows, kBlockKeys, false);
@@ -782,8 +862,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       const std::uint64_t k_desc = smem_desc(ring, 16, 1024); // K-major, 8-row groups 1 KiB apart
       // dim-major V: 64-dim boxes of 64 keys (8 KiB) in the single-CTA form, of 128 keys (16 KiB) in the pair form
       const std::uint64_t v_desc = smem_desc(ring, Pair ? kKeyBoxBytes : kSlotBoxBytes, 1024);
-      const std::uint32_t remote_bars = Pair ? map_to_rank(bars, 1) : 0U;
-      const std::uint32_t local_bars = Pair ? map_to_rank(bars, 0) : bars;
+      const std::uint32_t remote_bars = Pair ? map_to_rank(bars, lead_cta + 1) : 0U;
+      const std::uint32_t local_bars = Pair ? map_to_rank(bars, lead_cta) : bars;
       // completion of everything issued so far, signalled to this CTA and, in a pair, to the partner as well
       auto commit = [&](std::uint32_t index) {
         if (leader) {
@@ -809,7 +889,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       };
       std::uint32_t g0 = 0; // running key-block number of the tile's first block (S buffer = block & 1)
       for (TileWalk walk(p.tiles, Pair ? p.query_heads / 2 : p.query_heads, units, unit); !walk.done(); walk.next()) {
-        const std::uint32_t blocks = tile_blocks(walk.tile());
+        const std::uint32_t blocks = my_blocks(walk.tile());
         wait(kBarQFull, walk.iteration & 1U);
         // S[g & 1] = Q K_block^T.  Pair form: one slot, each CTA holding 64 of the block's 128 keys with all 256
         // dims in four 64-dim boxes.  Single form: two slots, each holding all 128 keys for half of the dims.
@@ -858,7 +938,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             RIB200_STAMP(j, 1); // QK issued
           }
         };
-        issue_qk(0);
+        if (blocks > 0) {
+          issue_qk(0);
+        }
         for (std::uint32_t j = 0; j < blocks; ++j) {
           const std::uint32_t g = g0 + j;
           if (j + 1 < blocks) {
@@ -934,7 +1016,8 @@ __global__ void __launch_bounds__(kThreads, 1)
       const std::uint32_t head = Pair ? walk.head() * 2 + rank : walk.head();
       const std::uint32_t row0 = walk.tile() * kTileRows;
       const std::uint32_t rows = tile_rows(walk.tile());
-      const std::uint32_t blocks = tile_blocks(walk.tile());
+      const std::uint32_t blocks = my_blocks(walk.tile());
+      const std::uint32_t block0 = first_block(walk.tile());
       const std::uint32_t q_pos = p.past + row0 + row; // position of this row's query (rows past the tile are idle)
 
       float m_used = -INFINITY; // maximum the exponentials are taken against (scaled, base 2); same in both groups
@@ -969,7 +1052,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           x[e] = __uint_as_float(xr[e >> 5][e & 31]);
         }
         // causal mask: key position j*128 + c is visible iff <= q_pos (also hides rows the context never held)
-        const std::uint32_t key0 = j * kBlockKeys;
+        const std::uint32_t key0 = (block0 + j) * kBlockKeys;
         if (key0 + kBlockKeys - 1 > p.past + row0) {
           const int visible = static_cast<int>(q_pos) - static_cast<int>(key0 + group * 64) + 1;
 #pragma unroll
@@ -993,7 +1076,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (threadIdx.x == 0 && walk.iteration == 0) {
           RIB200_STAMP(j, 11); // maxima exchanged
         }
-        const float mx = fmaxf(mine, theirs) * kScaleLog2e; // the scale is positive: it commutes with the maximum
+        // the scale is positive: it commutes with the maximum.  A row that sees no key of this block (possible only
+        // for the second half of a split item) gets a large negative finite maximum, so that its weights are zeros.
+        const float mx = fmaxf(fmaxf(mine, theirs) * kScaleLog2e, -1.0e30F);
         // move the reference maximum only when it fell far behind; block 0 always sets it
         const bool move = mx > m_used + kRescaleThreshold;
         if (__any_sync(0xFFFFFFFFU, move && j > 0)) {
@@ -1084,6 +1169,60 @@ __global__ void __launch_bounds__(kThreads, 1)
         break;
       }
       tcgen05_fence_after();
+      if (threadIdx.x == 0 && walk.iteration == 0) {
+        RIB200_STAMP(1, 14); // last PV landed
+      }
+      if constexpr (Split) {
+        if (half == 1) {
+          // Second half of a split item: the unnormalised O rows, the maximum they are scaled against and the
+          // row-sum shares go to this CTA's own ring (its MMAs have left it), and from there to the first CTA's
+          // ring in one bulk copy through distributed shared memory, once that CTA's MMAs have left theirs.
+          unsigned char *stage = smem + kRingOffset;
+          if (threadIdx.x == 0) {
+            RIB200_STAMP_CTA2(0); // last PV landed
+          }
+          ok = mbar_wait(bar(kBarStoresDone), walk.iteration & 1U, abort_flag); // the cache write-backs are out
+          ok = __all_sync(0xFFFFFFFFU, ok);
+          if (!ok) {
+            break;
+          }
+          if (threadIdx.x == 0) {
+            RIB200_STAMP_CTA2(1); // write-backs out
+          }
+#pragma unroll 1
+          for (int c = 0; c < 4; ++c) {
+            std::uint32_t v[32];
+            tmem_ld32(tmem_o + lane_base + group * 128 + c * 32, v);
+            tmem_wait_ld();
+            uint4 *dst = reinterpret_cast<uint4 *>(stage + row * kLandingPitch + (group * 128 + c * 32) * 4);
+#pragma unroll
+            for (int e = 0; e < 32; e += 4) {
+              dst[e / 4] = make_uint4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+            }
+          }
+          float *meta = reinterpret_cast<float *>(stage + kLandingMeta);
+          meta[group * kTileRows + row] = m_used;
+          meta[2 * kTileRows + group * kTileRows + row] = l_sum;
+          if (threadIdx.x == 0) {
+            RIB200_STAMP_CTA2(2); // staged
+          }
+          asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+          asm volatile("bar.sync 1, 256;\n" ::: "memory");
+          if (threadIdx.x == 0) {
+            ok = mbar_wait(bar(kBarPeerFree), walk.iteration & 1U, abort_flag);
+            RIB200_STAMP_CTA2(3); // partner's ring free
+            if (ok) {
+              bulk_copy_to_cluster(map_to_rank(ring, cta - half_stride), ring, kLandingBytes,
+                                   map_to_rank(bar(kBarPeerFull), cta - half_stride));
+            }
+          }
+          tcgen05_fence_before();
+          arrive_on_leader(kBarOFree);
+          continue;
+        }
+        // first half: every MMA of this CTA has completed, its ring is free for the partner's partial tile
+        mbar_arrive_cluster_release(map_to_rank(bar(kBarPeerFree), cta + half_stride));
+      }
       // The row sum is the two groups' shares.  They pass through the half of the exchange area that the next
       // block to run (the first of the next tile) does not use; the first barrier makes sure the partner has
       // finished reading this tile's last maximum from it.
@@ -1091,7 +1230,28 @@ __global__ void __launch_bounds__(kThreads, 1)
       asm volatile("bar.sync 1, 256;\n" ::: "memory");
       exchange[(sums + group) * kTileRows + row] = l_sum;
       asm volatile("bar.sync 1, 256;\n" ::: "memory");
-      const float inv = 1.0F / (l_sum + exchange[(sums + (group ^ 1)) * kTileRows + row]);
+      float inv = 1.0F / (l_sum + exchange[(sums + (group ^ 1)) * kTileRows + row]);
+      float own_weight = 1.0F;  // split form: factors that bring the two halves to a common maximum
+      float peer_weight = 0.0F;
+      const unsigned char *landed = smem + kRingOffset;
+      if constexpr (Split) {
+        ok = mbar_wait(bar(kBarPeerFull), walk.iteration & 1U, abort_flag);
+        ok = __all_sync(0xFFFFFFFFU, ok);
+        if (!ok) {
+          break;
+        }
+        fence_cluster();
+        if (threadIdx.x == 0 && walk.iteration == 0) {
+          RIB200_STAMP(1, 15); // partner's partial tile landed
+        }
+        const float *meta = reinterpret_cast<const float *>(landed + kLandingMeta);
+        const float peer_max = meta[group * kTileRows + row];
+        const float peer_sum = meta[2 * kTileRows + row] + meta[3 * kTileRows + row];
+        const float both = fmaxf(m_used, peer_max);
+        own_weight = exp2f(m_used - both);
+        peer_weight = exp2f(peer_max - both);
+        inv = 1.0F / (own_weight * (l_sum + exchange[(sums + (group ^ 1)) * kTileRows + row]) + peer_weight * peer_sum);
+      }
       // FP32 gates cannot all wait in registers as the BF16 ones do: they are fetched one 32-column piece ahead
       float4 gate_now[F32 ? 8 : 1];
       if constexpr (F32) {
@@ -1119,6 +1279,17 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
         tmem_wait_ld();
+        if constexpr (Split) {
+          const float4 *peer = reinterpret_cast<const float4 *>(landed + row * kLandingPitch + (group * 128 + c * 32) * 4);
+#pragma unroll
+          for (int e = 0; e < 32; e += 4) {
+            const float4 pv = peer[e / 4];
+            v[e] = __float_as_uint(__uint_as_float(v[e]) * own_weight + pv.x * peer_weight);
+            v[e + 1] = __float_as_uint(__uint_as_float(v[e + 1]) * own_weight + pv.y * peer_weight);
+            v[e + 2] = __float_as_uint(__uint_as_float(v[e + 2]) * own_weight + pv.z * peer_weight);
+            v[e + 3] = __float_as_uint(__uint_as_float(v[e + 3]) * own_weight + pv.w * peer_weight);
+          }
+        }
         if (c == 3) {
           // O has been read: the next tile's first PV may overwrite it
           tcgen05_fence_before();
@@ -1191,6 +1362,9 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
       }
+      if (threadIdx.x == 0 && walk.iteration == 0) {
+        RIB200_STAMP(0, 15); // tile written
+      }
 #ifdef RIB200_TRACE
       traced_blocks += blocks;
 #endif
@@ -1199,7 +1373,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   tcgen05_fence_before();
   __syncthreads();
-  if constexpr (Pair) {
+  if constexpr (kCluster) {
     cluster_sync_all(); // neither CTA leaves (or frees tensor memory) while the other may still use it
   }
   if (threadIdx.x == 0 && *abort_flag != 0) {
@@ -1260,13 +1434,14 @@ CUtensorMap make_map(void *base, int rank, const cuuint64_t *dims, const cuuint6
   return map;
 }
 
-template <bool F32, bool Pair> void configure_once() {
+template <bool F32, bool Pair, bool Split> void configure_once() {
   static std::once_flag flags[64];
   int device = 0;
   cuda_ok(cudaGetDevice(&device), "cudaGetDevice");
   require(device >= 0 && device < 64, "device ordinal out of range", RIB200_STATUS_INTERNAL);
   std::call_once(flags[device], [] {
-    cuda_ok(cudaFuncSetAttribute(prefill_attention_kernel<F32, Pair>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cuda_ok(cudaFuncSetAttribute(prefill_attention_kernel<F32, Pair, Split>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  kSmemBytes),
             "prefill attention shared-memory opt-in");
   });
@@ -1281,8 +1456,17 @@ bool pair_form_enabled() {
   return enabled;
 }
 
-template <bool F32, bool Pair> void launch(const PrefillArgs &a, cudaStream_t stream) {
-  configure_once<F32, Pair>();
+// RIB200_PREFILL_SPLIT=0 never splits an item over two CTAs (a tuning aid, not an interface).
+bool split_form_enabled() {
+  static const bool enabled = [] {
+    const char *env = std::getenv("RIB200_PREFILL_SPLIT");
+    return env == nullptr || env[0] != '0';
+  }();
+  return enabled;
+}
+
+template <bool F32, bool Pair, bool Split> void launch(const PrefillArgs &a, cudaStream_t stream) {
+  configure_once<F32, Pair, Split>();
   auto *cache = static_cast<__nv_bfloat16 *>(a.kv_cache);
   // The attention kernel itself writes the key blocks that lie wholly inside this chunk into the cache (BF16
   // inputs).  The append kernel covers the rest: every row for FP32 inputs, else the chunk's rows that share a key
@@ -1369,7 +1553,10 @@ template <bool F32, bool Pair> void launch(const PrefillArgs &a, cudaStream_t st
   cuda_ok(cudaGetDevice(&device), "cudaGetDevice");
   cuda_ok(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device), "SM count query");
   const std::uint32_t sms = static_cast<std::uint32_t>(sm_count);
-  if (Pair) {
+  if (Split) {
+    // one item (or pair of heads) per cluster
+    config.gridDim = dim3(Pair ? 4 * params.tiles * (a.query_heads / 2) : 2 * params.tiles * a.query_heads, 1, 1);
+  } else if (Pair) {
     const std::uint32_t pair_items = params.tiles * (a.query_heads / 2);
     config.gridDim = dim3(2 * std::min<std::uint32_t>(pair_items, sms / 2), 1, 1);
   } else {
@@ -1382,13 +1569,13 @@ template <bool F32, bool Pair> void launch(const PrefillArgs &a, cudaStream_t st
   attributes[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attributes[0].val.programmaticStreamSerializationAllowed = 1;
   attributes[1].id = cudaLaunchAttributeClusterDimension;
-  attributes[1].val.clusterDim.x = 2;
+  attributes[1].val.clusterDim.x = (Pair ? 2 : 1) * (Split ? 2 : 1);
   attributes[1].val.clusterDim.y = 1;
   attributes[1].val.clusterDim.z = 1;
   // attribute 0 (overlap with the append kernel) only when that kernel was launched
   config.attrs = append_rows > 0 ? attributes : attributes + 1;
-  config.numAttrs = (Pair ? 1 : 0) + (append_rows > 0 ? 1 : 0);
-  cuda_ok(cudaLaunchKernelEx(&config, prefill_attention_kernel<F32, Pair>, q_map, k_map, v_map, k_new_map, v_new_map, a.query,
+  config.numAttrs = (Pair || Split ? 1 : 0) + (append_rows > 0 ? 1 : 0);
+  cuda_ok(cudaLaunchKernelEx(&config, prefill_attention_kernel<F32, Pair, Split>, q_map, k_map, v_map, k_new_map, v_new_map, a.query,
                              params),
           "prefill attention launch");
 }
@@ -1406,12 +1593,34 @@ extern "C" int rib200_debug_read_cta_trace(long long *host, std::size_t count) {
 
 void launch_prefill_attention(const PrefillArgs &args, cudaStream_t stream) {
   require(args.tokens <= 65535U * kTileRows, "prefill attention: too many tokens for one launch");
-  // Two query heads of one KV head form a pair; an odd group size keeps the single-CTA form.
+  // Few items, each with many key blocks (a short chunk against a long past): two CTAs share an item's keys.
+  // Otherwise two query heads of one KV head form a pair; an odd group size keeps the single-CTA form.
+  int device = 0;
+  int sm_count = 0;
+  cuda_ok(cudaGetDevice(&device), "cudaGetDevice");
+  cuda_ok(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device), "SM count query");
+  const std::uint32_t tiles = (args.tokens + kTileRows - 1) / kTileRows;
+  const std::uint32_t first_tile_blocks =
+      (args.past_tokens + std::min<std::uint32_t>(args.tokens, kTileRows) - 1) / kBlockKeys + 1;
+  const bool split = split_form_enabled() && 2 * tiles * args.query_heads <= static_cast<std::uint32_t>(sm_count) &&
+                     first_tile_blocks >= 4;
   const bool pair = pair_form_enabled() && (args.query_heads / args.kv_heads) % 2 == 0;
+  auto dispatch = [&](auto f32) {
+    constexpr bool kF32 = decltype(f32)::value;
+    if (split && pair) {
+      launch<kF32, true, true>(args, stream);
+    } else if (split) {
+      launch<kF32, false, true>(args, stream);
+    } else if (pair) {
+      launch<kF32, true, false>(args, stream);
+    } else {
+      launch<kF32, false, false>(args, stream);
+    }
+  };
   if (args.activations_f32) {
-    pair ? launch<true, true>(args, stream) : launch<true, false>(args, stream);
+    dispatch(std::true_type{});
   } else {
-    pair ? launch<false, true>(args, stream) : launch<false, false>(args, stream);
+    dispatch(std::false_type{});
   }
 }
 

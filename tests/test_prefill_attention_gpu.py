@@ -56,7 +56,10 @@ def run_prefill(tokens, past, max_ctx, dtype, seed, q_scale=1.0, rows_to_check=N
 
 
 @pytest.mark.parametrize("tokens,past,max_ctx", [(2, 0, 4), (4, 0, 4), (17, 0, 64), (128, 0, 128), (129, 0, 300),
-                                                  (17, 111, 128), (64, 200, 512), (512, 0, 512), (300, 77, 1024)])
+                                                  (17, 111, 128), (64, 200, 512), (512, 0, 512), (300, 77, 1024),
+                                                  # few items with many key blocks: two CTAs split an item's keys
+                                                  (17, 511, 1024), (128, 1000, 2048), (300, 640, 1024),
+                                                  (512, 1536, 2048), (2, 700, 1024)])
 @pytest.mark.parametrize("dtype", [K.DTYPE_BF16, K.DTYPE_F32])
 def test_prefill_shapes(tokens, past, max_ctx, dtype):
     run_prefill(tokens, past, max_ctx, dtype, seed=0xB2004000 + tokens + past)
