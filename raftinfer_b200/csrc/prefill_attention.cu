@@ -828,8 +828,9 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
       }
-      // slots still waiting to be written back: the last fill of slot s was number m, m % kSlots == s
-      for (std::uint32_t back = 1; ok && back <= kSlots && back <= n; ++back) {
+      // slots still waiting to be written back, oldest first (its MMAs finish first): the last fill of slot s was
+      // number m, m % kSlots == s
+      for (std::uint32_t back = std::min<std::uint32_t>(kSlots, n); ok && back >= 1; --back) {
         const std::uint32_t m = n - back;
         const std::uint32_t slot = m % kSlots;
         if (pending[slot] != 0) {
