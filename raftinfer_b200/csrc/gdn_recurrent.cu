@@ -163,10 +163,20 @@ __global__ void __launch_bounds__(kBatchedThreads, 1)
   const std::uint32_t count = first < sequences ? (sequences - first + step - 1) / step : 0;
   const std::uint32_t ring_base = static_cast<std::uint32_t>(__cvta_generic_to_shared(ring));
 
+  // The state pointers of this CTA's first sequences are read once: a dependent pointer load in front of every copy
+  // and every write-back would sit on the critical path of each sequence.
+  constexpr std::uint32_t kKnownPointers = 64;
+  __shared__ float *known[kKnownPointers];
+  if (threadIdx.x < kKnownPointers && threadIdx.x < count) {
+    known[threadIdx.x] = p.states[first + threadIdx.x * step];
+  }
+  __syncthreads();
+  auto state_of = [&](std::uint32_t n) { return n < kKnownPointers ? known[n] : p.states[first + n * step]; };
+
   // copy the head's 128 x 128 state of this CTA's n-th sequence into stage n % kStages
   auto issue = [&](std::uint32_t n) {
     const std::uint32_t seq = first + n * step;
-    const float *src = p.states[seq] + static_cast<std::size_t>(head) * kDim * kDim;
+    const float *src = state_of(n) + static_cast<std::size_t>(head) * kDim * kDim;
     const std::uint32_t dst = ring_base + (n % kStages) * kStageBytes;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -296,7 +306,7 @@ __global__ void __launch_bounds__(kBatchedThreads, 1)
       *reinterpret_cast<float4 *>(dst + 4) = make_float4(o[4], o[5], o[6], o[7]);
     }
     __syncthreads(); // the whole updated state is in the stage
-    float *state = p.states[seq] + static_cast<std::size_t>(head) * kDim * kDim;
+    float *state = state_of(n) + static_cast<std::size_t>(head) * kDim * kDim;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int idx = threadIdx.x + i * kBatchedThreads;
