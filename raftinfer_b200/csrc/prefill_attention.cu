@@ -538,8 +538,7 @@ template <bool F32, bool Pair, bool Split>
 __global__ void __launch_bounds__(kThreads, 1)
     prefill_attention_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                              const __grid_constant__ CUtensorMap v_map, const __grid_constant__ CUtensorMap k_new_map,
-                             const __grid_constant__ CUtensorMap v_new_map, const void *query_f32,
-                             const PrefillParams p) {
+                             const __grid_constant__ CUtensorMap v_new_map, const PrefillParams p) {
   extern __shared__ __align__(1024) unsigned char smem[];
   const std::uint32_t base = smem_u32(smem); // the 128-byte swizzle needs 1 KiB alignment; checked below
   const std::uint32_t q_smem = base;
@@ -1576,8 +1575,7 @@ template <bool F32, bool Pair, bool Split> void launch(const PrefillArgs &a, cud
   // attribute 0 (overlap with the append kernel) only when that kernel was launched
   config.attrs = append_rows > 0 ? attributes : attributes + 1;
   config.numAttrs = (Pair || Split ? 1 : 0) + (append_rows > 0 ? 1 : 0);
-  cuda_ok(cudaLaunchKernelEx(&config, prefill_attention_kernel<F32, Pair, Split>, q_map, k_map, v_map, k_new_map, v_new_map, a.query,
-                             params),
+  cuda_ok(cudaLaunchKernelEx(&config, prefill_attention_kernel<F32, Pair, Split>, q_map, k_map, v_map, k_new_map, v_new_map, params),
           "prefill attention launch");
 }
 
