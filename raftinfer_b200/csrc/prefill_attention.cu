@@ -634,7 +634,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   auto tile_blocks = [&](std::uint32_t tile) {
     return (p.past + tile * kTileRows + tile_rows(tile) - 1) / kBlockKeys + 1; // newest visible key / 128 + 1
   };
-  // the key blocks this CTA walks: all of them, or its half in the split form
+  // the key blocks this CTA walks: all of them, or its half in the split form (the hand-over can only start when
+  // both halves are done, so equal halves are best)
   auto first_block = [&](std::uint32_t tile) { return Split && half == 1 ? (tile_blocks(tile) + 1) / 2 : 0U; };
   auto my_blocks = [&](std::uint32_t tile) {
     const std::uint32_t all = tile_blocks(tile);
