@@ -115,10 +115,19 @@ __device__ __forceinline__ long long global_ns() {
 #define RIB200_STAMP_CTA2(slot)                                                     \
   do {                                                                              \
     if (blockIdx.x == 2 && blockIdx.y == 0) {                                       \
-      g_trace[120 * 16 + (slot)] = clock64();                                       \
+      g_trace[120 * 16 + (slot)] = global_ns();                                     \
+    }                                                                               \
+  } while (0)
+#define RIB200_STAMP_NS(slot)                                                       \
+  do {                                                                              \
+    if (blockIdx.x == 0 && blockIdx.y == 0) {                                       \
+      g_trace[121 * 16 + (slot)] = global_ns();                                     \
     }                                                                               \
   } while (0)
 #else
+#define RIB200_STAMP_NS(slot)                                                       \
+  do {                                                                              \
+  } while (0)
 #define RIB200_STAMP(block, slot)                                                   \
   do {                                                                              \
   } while (0)
@@ -622,6 +631,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
   if (threadIdx.x == 0) {
     RIB200_STAMP(0, 14); // set-up done
+    RIB200_STAMP_NS(3);
+    RIB200_STAMP_CTA2(4);
   }
   const std::uint32_t tmem = *tmem_slot;
   const std::uint32_t tmem_o = tmem;         // columns [0, 256)
@@ -1172,6 +1183,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       tcgen05_fence_after();
       if (threadIdx.x == 0 && walk.iteration == 0) {
         RIB200_STAMP(1, 14); // last PV landed
+        RIB200_STAMP_NS(0);
       }
       if constexpr (Split) {
         if (half == 1) {
@@ -1244,6 +1256,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         fence_cluster();
         if (threadIdx.x == 0 && walk.iteration == 0) {
           RIB200_STAMP(1, 15); // partner's partial tile landed
+          RIB200_STAMP_NS(1);
         }
         const float *meta = reinterpret_cast<const float *>(landed + kLandingMeta);
         const float peer_max = meta[group * kTileRows + row];
@@ -1365,6 +1378,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       if (threadIdx.x == 0 && walk.iteration == 0) {
         RIB200_STAMP(0, 15); // tile written
+        RIB200_STAMP_NS(2);
       }
 #ifdef RIB200_TRACE
       traced_blocks += blocks;
