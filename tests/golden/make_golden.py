@@ -1,6 +1,6 @@
 """Regenerates the golden fixtures under tests/golden/ from the RAFTInfer reference checkout.
 
-Run where the reference checkout exists (REF, default /root/reference) after `make -C oracle`:
+Run where the reference checkout exists (its location is the REF environment variable) after `make -C oracle`:
 
     python tests/golden/make_golden.py
 
