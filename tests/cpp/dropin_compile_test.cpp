@@ -3,6 +3,7 @@
 // reference's contract tests (cpp/tests/qwen35_cuda_attention_test.cu:263-440).  No GPU is touched: every call
 // below either is pure host arithmetic or is refused before a launch.
 #include <raftinfer_b200/kernels.hpp>
+#include <raftinfer_b200/primitives.hpp>
 
 #include <cstdio>
 #include <cstdlib>
@@ -77,6 +78,21 @@ int main() {
   auto bad = delta;
   bad.value_heads = 33;
   EXPECT(throws<rk::Qwen35DeltaError>([&] { (void)rk::qwen35_gated_delta_workspace_bytes(bad); }));
+  // the two pre-attention primitives, called the way cpp/execution/qwen35_executor.cu:1989-2015 calls them
+  EXPECT(throws<rk::Qwen35PrimitiveError>([&] {
+    rk::qwen35_split_full_query_gate(fake, fake, fake, 4, 16, 256, RAFTINFER_DTYPE_F32, nullptr);
+  }));
+  EXPECT(throws<rk::Qwen35PrimitiveError>([&] {
+    rk::qwen35_qk_norm_rope(fake, fake, fake,
+                            rk::QkNormRopeShape{.tokens = 4, .heads = 16, .head_dim = 256, .rotary_dim = 258,
+                                                .position_offset = 0, .rope_base = 1.0e7F},
+                            1.0e-6F, RAFTINFER_DTYPE_F32, RAFTINFER_DTYPE_F32, reinterpret_cast<cudaStream_t>(fake));
+  }));
+  EXPECT(throws<rk::Qwen35PrimitiveError>([&] {
+    rk::qwen35_attention_prologue(fake, fake, fake, fake, fake, fake, fake, fake, fake, {4, 16, 4, 256, 8, 0}, 64,
+                                  1.0e7F, 1.0e-6F, RAFTINFER_DTYPE_F32, RAFTINFER_DTYPE_F32, RAFTINFER_DTYPE_BF16,
+                                  nullptr);
+  }));
   std::puts("dropin ok");
   return 0;
 }
