@@ -138,8 +138,9 @@ def run_reference_arm(args):
         "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup,
         "ms_per_step": algorithmic_bytes(CONTEXT) / gbs / 1e6, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f64 dot / f32 accumulate (CPU)", "data": "synthetic",
-        "config": {"workload": f"decode attention, batch 1, context {CONTEXT}, 16q/4kv heads, head_dim 256, "
-                               "BF16 head-major KV, CPU reference arithmetic"},
+        "config": {"workload": f"split-k decode attention, batch 1 per GPU, context {CONTEXT}, 16q/4kv heads, "
+                               "head_dim 256, BF16 head-major KV, partition 256",
+                   "arithmetic": "CPU reference arithmetic (one pass over the context, no split) on the host cores"},
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "wall_seconds": total,
