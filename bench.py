@@ -254,10 +254,10 @@ def main():
     e2e_steps = min(steps, 200)
 
     def e2e_step(i):
-        dev_packed.copy_(host_packed, non_blocking=True)
-        step(i, dev_in[0], dev_in[1], dev_in[2], dev_in[3])
-        host_out.copy_(out, non_blocking=True)
-        stream.synchronize()
+        # the library's host-buffer entry point: copy in, the decode step, copy out, synchronise
+        K.online_attention_decode_from_host(host_packed, host_out, dev_packed, out, caches[i % ROTATION], cache_bytes,
+                                            ws, layout.bytes, shape, K.DTYPE_BF16, K.KV_BF16, K.HEAD_MAJOR, plan, None,
+                                            stream)
 
     for i in range(3):
         e2e_step(i)

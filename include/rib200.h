@@ -333,6 +333,19 @@ Rib200Status rib200_shared_open(const uint8_t handle[64], void **pointer);
 Rib200Status rib200_shared_close(void *pointer);
 Rib200Status rib200_shared_free(void *pointer);
 
+/* One decode step driven from host memory (no counterpart in the reference, whose callers hold device
+ * buffers): copies the token's rows q | k | v | gate ([16+4+4+16][256] in the activation dtype, back to back,
+ * ideally pinned) into device_token (same size), runs rib200_online_attention_decode with them, copies the
+ * [16][256] output from device_output to host_output and returns once it is there (it synchronises `stream`).
+ * The other arguments are those of rib200_online_attention_decode. */
+Rib200Status rib200_online_attention_decode_from_host(const void *host_token, void *host_output, void *device_token,
+                                                      void *device_output, void *kv_cache, size_t kv_cache_bytes,
+                                                      void *workspace, size_t workspace_bytes,
+                                                      const Rib200AttentionShape *shape, int32_t activation_dtype,
+                                                      uint8_t cache_dtype, uint8_t cache_layout,
+                                                      const Rib200OnlineDecodePlan *plan,
+                                                      const uint32_t *device_position, void *stream);
+
 /* Reads and clears the status word the kernels of this library set on the current device.  It
  * synchronises `stream` first, so it is not for use inside a graph capture. */
 Rib200Status rib200_device_status(void *stream, uint32_t *bits);

@@ -85,6 +85,8 @@ PROTOTYPES = {
                                         C.c_uint8, C.c_uint8, vp],
     "rib200_online_attention_decode": [vp, vp, vp, vp, vp, vp, sz, vp, sz, C.POINTER(AttentionShape), C.c_int32,
                                        C.c_uint8, C.c_uint8, C.POINTER(OnlineDecodePlan), vp, vp],
+    "rib200_online_attention_decode_from_host": [vp, vp, vp, vp, vp, sz, vp, sz, C.POINTER(AttentionShape), C.c_int32,
+                                                 C.c_uint8, C.c_uint8, C.POINTER(OnlineDecodePlan), vp, vp],
     "rib200_online_attention_prefill_scatter": [vp, vp, vp, vp, C.POINTER(vp), sz, sz, sz, sz, vp, sz,
                                                 C.POINTER(AttentionShape), C.c_int32, C.c_uint8, C.c_uint8, vp],
     "rib200_peer_rendezvous": [C.POINTER(vp), sz, sz, C.c_uint32, vp],

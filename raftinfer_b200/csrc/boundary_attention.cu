@@ -452,6 +452,41 @@ Rib200Status rib200_online_attention_decode(const void *query, const void *key, 
   });
 }
 
+// One decode step driven from host memory: the token's rows go up, the step runs, the output comes back, and
+// the call returns when it is there.
+Rib200Status rib200_online_attention_decode_from_host(const void *host_token, void *host_output, void *device_token,
+                                                      void *device_output, void *kv_cache, size_t kv_cache_bytes,
+                                                      void *workspace, size_t workspace_bytes,
+                                                      const Rib200AttentionShape *shape, int32_t activation_dtype,
+                                                      uint8_t cache_dtype, uint8_t cache_layout,
+                                                      const Rib200OnlineDecodePlan *plan,
+                                                      const uint32_t *device_position, void *stream) {
+  return guarded([&] {
+    require(plan != nullptr, "online decode: plan pointer is null");
+    require(host_token != nullptr && host_output != nullptr, "online decode from host: a host pointer is null");
+    require(device_token != nullptr && device_output != nullptr, "online decode from host: a staging pointer is null");
+    require(stream != nullptr, "online decode: CUDA stream is null");
+    const Rib200AttentionShape &s = deref(shape);
+    require(decode_signature_ok(s, activation_dtype, cache_dtype, cache_layout),
+            "online decode: unsupported decode signature");
+    const std::size_t element = activation_dtype == RIB200_DTYPE_F32 ? 4 : 2;
+    const std::size_t q_bytes = s.query_heads * s.head_dim * element;
+    const std::size_t kv_bytes = s.kv_heads * s.head_dim * element;
+    require_aligned16(device_token, "online decode from host: staging is not 16-byte aligned");
+    auto *staged = static_cast<unsigned char *>(device_token);
+    cudaStream_t cuda_stream = static_cast<cudaStream_t>(stream);
+    // rows in the order q | k | v | gate
+    cuda_ok(cudaMemcpyAsync(staged, host_token, 2 * q_bytes + 2 * kv_bytes, cudaMemcpyHostToDevice, cuda_stream),
+            "online decode from host: copy in");
+    online_decode(staged, staged + q_bytes, staged + q_bytes + kv_bytes, staged + q_bytes + 2 * kv_bytes,
+                  device_output, kv_cache, kv_cache_bytes, workspace, workspace_bytes, s, activation_dtype,
+                  cache_dtype, cache_layout, *plan, device_position, cuda_stream);
+    cuda_ok(cudaMemcpyAsync(host_output, device_output, q_bytes, cudaMemcpyDeviceToHost, cuda_stream),
+            "online decode from host: copy out");
+    cuda_ok(cudaStreamSynchronize(cuda_stream), "online decode from host: synchronise");
+  });
+}
+
 // Dispatcher, cpp/kernels/qwen35_attention.cu:565-613.
 Rib200Status rib200_causal_attention(const void *query, const void *key, const void *value, const void *gate,
                                      void *output, void *kv_cache, size_t kv_cache_bytes, void *workspace,

@@ -242,6 +242,20 @@ def attention_prologue(query_gate, key, value, query_norm_weight, key_norm_weigh
                                          weight_dtype, output_dtype, _ptr(device_position), _stream(stream)))
 
 
+def online_attention_decode_from_host(host_token, host_output, device_token, device_output, kv_cache, kv_cache_bytes,
+                                      workspace, workspace_bytes, shape, activation_dtype, cache_dtype, cache_layout,
+                                      plan, device_position, stream):
+    """One decode step driven from (pinned) host memory: rows q | k | v | gate go up, the [16][256] output comes
+    back, and the call returns when it is there.  No counterpart in the reference."""
+    s = shape.c()
+    p = plan.c()
+    _check(lib.rib200_online_attention_decode_from_host(_ptr(host_token), _ptr(host_output), _ptr(device_token),
+                                                        _ptr(device_output), _ptr(kv_cache), kv_cache_bytes,
+                                                        _ptr(workspace), workspace_bytes, C.byref(s),
+                                                        activation_dtype, cache_dtype, cache_layout, C.byref(p),
+                                                        _ptr(device_position), _stream(stream)))
+
+
 def online_attention_prefill_scatter(query, key, value, gate, outputs, rank, total_query_heads, head_offset, kv_cache,
                                      kv_cache_bytes, shape, activation_dtype, cache_dtype, cache_layout, stream):
     """Head-sharded prefill: `outputs` lists every rank's full-width output buffer (pointers or tensors valid on

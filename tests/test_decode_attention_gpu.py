@@ -13,8 +13,8 @@ from oracle import bindings as ob
 from raftinfer_b200 import kernels as K
 from raftinfer_b200 import synth
 
-from gpu_util import (D, HKV, HQ, NAN_BITS, act_tensor, cache_bits_of, cache_to_device, compare, decode_operands,
-                      dev, gate_bf16_outputs, make_cache, to_numpy_f32)
+from gpu_util import (D, HKV, HQ, NAN_BITS, act_tensor, bf16_tensor, cache_bits_of, cache_to_device, compare,
+                      decode_operands, dev, gate_bf16_outputs, make_cache, to_numpy_f32)
 
 pytestmark = pytest.mark.gpu
 SENTINEL = -12345.0
@@ -260,6 +260,39 @@ def test_back_to_back_steps_keep_stream_order():
     assert K.device_status(stream) == 0
     assert torch.equal(loose, strict)
     assert torch.equal(loose_cache, strict_cache)
+
+
+def test_decode_from_host_buffers():
+    """The host-buffer entry point (copy in, step, copy out, synchronise) gives what the device-buffer call gives."""
+    ctx, max_ctx = 1500, 2048
+    pos = ctx - 1
+    q, gate, k, v = decode_operands(0xB2000A00, ctx)
+    shape = K.Qwen35AttentionShape(1, HQ, HKV, D, max_ctx, pos)
+    plan = K.qwen35_online_decode_plan(shape, K.SPLIT_K_256, ctx)
+    layout = K.qwen35_online_decode_workspace_layout(shape, plan.resolved_mode)
+    stream = torch.cuda.current_stream()
+    token = np.concatenate([q, k[pos], v[pos], gate], axis=0)  # rows q | k | v | gate
+    host_token = bf16_tensor(token).cpu().pin_memory()
+    host_out = torch.zeros(HQ, D, dtype=torch.bfloat16).pin_memory()
+    dev_token = torch.zeros(2 * HQ + 2 * HKV, D, device=dev(), dtype=torch.bfloat16)
+    dev_out = torch.zeros(HQ, D, device=dev(), dtype=torch.bfloat16)
+    ws = torch.zeros(layout.bytes // 4, device=dev())
+    cache = cache_to_device(make_cache(k, v, max_ctx, pos))
+    K.online_attention_decode_from_host(host_token, host_out, dev_token, dev_out, cache, cache.numel() * 2, ws,
+                                        layout.bytes, shape, K.DTYPE_BF16, K.KV_BF16, K.HEAD_MAJOR, plan, None, stream)
+    # no synchronisation here: the call has returned, so the host buffer holds the result
+    got = host_out.clone()
+    ref_out = torch.zeros(HQ, D, device=dev(), dtype=torch.bfloat16)
+    cache2 = cache_to_device(make_cache(k, v, max_ctx, pos))
+    K.qwen35_online_attention_decode(bf16_tensor(q), bf16_tensor(k[pos]), bf16_tensor(v[pos]), bf16_tensor(gate),
+                                     ref_out, cache2, cache2.numel() * 2, ws, layout.bytes, shape, K.DTYPE_BF16,
+                                     K.KV_BF16, K.HEAD_MAJOR, plan, None, stream)
+    torch.cuda.synchronize()
+    assert torch.equal(got, ref_out.cpu()) and torch.equal(cache, cache2)
+    with pytest.raises(K.Qwen35PrimitiveError):
+        K.online_attention_decode_from_host(None, host_out, dev_token, dev_out, cache, cache.numel() * 2, ws,
+                                            layout.bytes, shape, K.DTYPE_BF16, K.KV_BF16, K.HEAD_MAJOR, plan, None,
+                                            stream)
 
 
 def test_batched_ragged_decode():
