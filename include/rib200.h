@@ -346,6 +346,19 @@ Rib200Status rib200_online_attention_decode_from_host(const void *host_token, vo
                                                       const Rib200OnlineDecodePlan *plan,
                                                       const uint32_t *device_position, void *stream);
 
+/* Opt-in for rib200_online_attention_decode with a host position (no counterpart in the reference).  A decode
+ * step reads cache rows [0, past_tokens) that earlier calls wrote and four token rows the kernel in front of it
+ * produced.  With the option on, the partition kernel starts fetching the cache rows as soon as it is resident --
+ * under programmatic dependent launch that can be while the kernels in front of it are still running -- and waits
+ * for them only before it touches the token's rows and before it writes anything.  The caller promises in return
+ * that whatever wrote rows [0, past_tokens) of that KV cache has completed, or is separated from the step by at
+ * least one ordinary kernel launch on the stream (a kernel that does not release its dependents early; the two
+ * kernels of a decode step of this library do release them early).  True for the reference's executor, where the
+ * previous writer of a layer's cache is the previous token's step, a whole model pass earlier; false for two
+ * steps enqueued directly one after the other on the same cache with advancing positions.  Off by default;
+ * process-wide; calls with a device position or a batch ignore it.  enabled: 0 or 1. */
+Rib200Status rib200_set_decode_early_kv_fetch(int32_t enabled);
+
 /* Reads and clears the status word the kernels of this library set on the current device.  It
  * synchronises `stream` first, so it is not for use inside a graph capture. */
 Rib200Status rib200_device_status(void *stream, uint32_t *bits);

@@ -107,6 +107,7 @@ PROTOTYPES = {
     "rib200_batched_gdn_decode": [vp, vp, vp, vp, vp, vp, vp, sz, sz, sz, vp],
     "rib200_online_attention_decode_static_scratch": [vp, vp, vp, vp, vp, vp, sz, C.POINTER(AttentionShape), C.c_int32,
                                                       vp, vp],
+    "rib200_set_decode_early_kv_fetch": [C.c_int32],
     "rib200_device_status": [vp, C.POINTER(C.c_uint32)],
 }
 

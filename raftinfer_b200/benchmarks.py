@@ -53,8 +53,12 @@ def _bf16(gen, dev, *shape):
     return torch.randn(*shape, device=dev, generator=gen, dtype=torch.float32).to(torch.bfloat16)
 
 
-def decode_contexts(dev, stream, hbm_peak, contexts=(4096, 131072)):
+def decode_contexts(dev, stream, hbm_peak, contexts=(4096, 131072), early_kv_fetch_contexts=(32768,)):
+    """Single-sequence decode steps on caches visited round-robin.  For `early_kv_fetch_contexts` the same loop is
+    also timed with rib200_set_decode_early_kv_fetch on: no step of the loop writes a cache row another one reads,
+    which is what that option asks of the caller."""
     out = {}
+    contexts = tuple(contexts) + tuple(c for c in early_kv_fetch_contexts if c not in contexts)
     gen = torch.Generator(device=dev).manual_seed(11)
     for ctx in contexts:
         rotation = max(2, min(16, -(-600_000_000 // (4096 * ctx))))
@@ -76,6 +80,14 @@ def decode_contexts(dev, stream, hbm_peak, contexts=(4096, 131072)):
         nbytes = 4096 * ctx + 24576
         out[f"decode_ctx{ctx}"] = {"ms": ms, "cv": cv, "bytes": nbytes, "GB/s": nbytes / ms / 1e6,
                                    "frac_of_measured_hbm": nbytes / ms / 1e6 / hbm_peak, "caches_rotated": rotation}
+        if ctx in early_kv_fetch_contexts:
+            K.set_decode_early_kv_fetch(True)
+            try:
+                ms, cv = _median_ms(fn, stream, warmup=5, reps=10, calls=8)
+            finally:
+                K.set_decode_early_kv_fetch(False)
+            out[f"decode_ctx{ctx}_early_kv_fetch"] = {"ms": ms, "cv": cv, "bytes": nbytes, "GB/s": nbytes / ms / 1e6,
+                                                      "frac_of_measured_hbm": nbytes / ms / 1e6 / hbm_peak}
         del caches
     return out
 

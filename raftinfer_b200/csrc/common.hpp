@@ -88,6 +88,7 @@ struct DecodeArgs {
   bool activations_f32;
 };
 void launch_decode_attention(const DecodeArgs &args, cudaStream_t stream);
+void set_decode_early_kv_fetch(bool enabled);
 
 // One decode step for a batch of ragged sequences (BF16 activations).
 struct BatchedDecodeArgs {

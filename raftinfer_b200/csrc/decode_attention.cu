@@ -31,6 +31,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdint>
 #include <cstdlib>
 #include <mutex>
@@ -115,6 +116,7 @@ struct DecodeParams {
   float *partial_value;
   std::size_t partial_stride; // floats between sequences in partial_max / partial_sum (batched)
   unsigned int *status;
+  std::uint32_t early_kv; // single sequence, host position: the first ring slots are fetched before the wait below
 };
 
 __device__ __forceinline__ std::uint32_t smem_address(const void *p) {
@@ -242,9 +244,12 @@ __global__ void __launch_bounds__(T::kWarps * 32, T::kCtasPerSm) decode_partitio
   constexpr int kRingBytes = T::kRingBytes;
   extern __shared__ __align__(128) unsigned char smem[];
   // Both kernels of a decode step are launched with programmatic stream serialisation.  This grid may have been
-  // made resident early by the kernel before it (the combine kernel of a preceding step does that); nothing is read
-  // or written before that kernel has completed, so the ordering is that of a plain launch, minus the launch latency.
-  asm volatile("griddepcontrol.wait;\n" ::: "memory");
+  // made resident early by the kernel before it (the combine kernel of a preceding step does that).  Unless the
+  // caller has opted into the early cache fetch, nothing is read or written before that kernel has completed, so
+  // the ordering is that of a plain launch, minus the launch latency.
+  if (Batched || p.early_kv == 0) {
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
+  }
   // Let the combine kernel become resident now; it blocks in griddepcontrol.wait until this whole grid has
   // finished and flushed.
   asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
@@ -376,6 +381,13 @@ __global__ void __launch_bounds__(T::kWarps * 32, T::kCtasPerSm) decode_partitio
     if (static_cast<std::uint32_t>(n) < my_slots) {
       issue(n);
     }
+  }
+  if (!Batched && p.early_kv != 0) {
+    // Early cache fetch: the copies above read cache rows only, with every address taken from kernel
+    // parameters, and the caller has promised that no kernel in flight writes those rows.  Everything the
+    // kernel in front may have produced (query, key, value, gate) and everything this grid writes comes
+    // after this wait.
+    asm volatile("griddepcontrol.wait;\n" ::: "memory");
   }
 
   // Query fragments (the B operand of the score product): lane (g, t) holds, for k-step ks, dims
@@ -824,6 +836,11 @@ extern "C" int rib200_debug_read_decode_trace(long long *partition, long long *c
 }
 #endif
 
+// Process-wide opt-in set through rib200_set_decode_early_kv_fetch.
+std::atomic<int> g_early_kv_fetch{0};
+
+void set_decode_early_kv_fetch(bool enabled) { g_early_kv_fetch.store(enabled ? 1 : 0, std::memory_order_relaxed); }
+
 void launch_decode_attention(const DecodeArgs &a, cudaStream_t stream) {
   DecodeParams params{};
   params.query = a.query;
@@ -844,6 +861,7 @@ void launch_decode_attention(const DecodeArgs &a, cudaStream_t stream) {
   params.partial_value = a.partial_value;
   params.partial_stride = 0;
   params.status = device_status_word();
+  params.early_kv = (a.device_position == nullptr && g_early_kv_fetch.load(std::memory_order_relaxed) != 0) ? 1U : 0U;
   const bool split = a.partition_tokens != 0;
   const dim3 partition_grid(split ? a.partition_capacity : 1, kKvHeads, 1);
   const dim3 combine_grid(kQueryHeads, 4, 1);

@@ -275,14 +275,6 @@ __device__ __forceinline__ void mbar_arrive_cluster_release(std::uint32_t cluste
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_bar) : "memory");
 }
 __device__ __forceinline__ void fence_cluster() { asm volatile("fence.acq_rel.cluster;\n" ::: "memory"); }
-__device__ __forceinline__ void st_cluster_v4(std::uint32_t cluster_addr, float a, float b, float c, float d) {
-  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"r"(cluster_addr), "f"(a), "f"(b), "f"(c),
-               "f"(d)
-               : "memory");
-}
-__device__ __forceinline__ void st_cluster_f32(std::uint32_t cluster_addr, float a) {
-  asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(cluster_addr), "f"(a) : "memory");
-}
 
 // bulk copy from this CTA's shared memory into another CTA of the cluster; the bytes count on a barrier there
 __device__ __forceinline__ void bulk_copy_to_cluster(std::uint32_t cluster_dst, std::uint32_t cta_src,

@@ -395,6 +395,12 @@ def batched_gdn_decode(q, k, v, beta, log_decay, states, out, batch, key_heads, 
            Qwen35DeltaError)
 
 
+def set_decode_early_kv_fetch(enabled):
+    """Opt-in described at rib200_set_decode_early_kv_fetch: the caller promises that no work in flight writes the
+    cache rows a decode step reads, and the step starts fetching them before the kernel in front has finished."""
+    _check(lib.rib200_set_decode_early_kv_fetch(1 if enabled else 0))
+
+
 def device_status(stream):
     bits = C.c_uint32()
     _check(lib.rib200_device_status(_stream(stream), C.byref(bits)))
