@@ -58,7 +58,8 @@ enum { RIB200_DELTA_SCHEDULE_CURRENT = 0, RIB200_DELTA_SCHEDULE_PREFILL_SM120 = 
 enum {
   RIB200_DEVICE_DECODE_CAPACITY_EXCEEDED = 1u << 0, /* live context needs more partitions than the plan holds */
   RIB200_DEVICE_POSITION_OUT_OF_RANGE = 1u << 1,    /* *device_position >= max_context_tokens */
-  RIB200_DEVICE_WAIT_TIMED_OUT = 1u << 2            /* a bounded on-device wait gave up */
+  RIB200_DEVICE_WAIT_TIMED_OUT = 1u << 2,           /* a bounded on-device wait gave up */
+  RIB200_DEVICE_PAGE_OUT_OF_RANGE = 1u << 3         /* a block table names a page the pool does not hold */
 };
 
 /* cpp/kernels/qwen35_attention.cuh:14-21 */
@@ -247,6 +248,19 @@ Rib200Status rib200_batched_decode_attention(const void *query, const void *key,
                                              const uint32_t *max_context_tokens, const uint32_t *positions,
                                              size_t batch, size_t largest_max_context_tokens, void *workspace,
                                              size_t workspace_bytes, void *stream);
+/* Paged form of the batched decode step (no counterpart in the reference, which holds one contiguous cache per
+ * sequence).  The KV rows live in a pool of pages of 256 tokens; a page is laid out like a head-major cache of 256
+ * rows, [2][4][256][256] BF16 = 1 MiB, and block_tables[i][b] (device memory, rows of max_blocks_per_sequence
+ * entries) names the page that holds rows [256 b, 256 b + 256) of sequence i.  positions[i] is the row the new
+ * token is appended at; its page must be in the table already.  Entries past a sequence's live context are not
+ * read.  An entry >= pool_pages sets RIB200_DEVICE_PAGE_OUT_OF_RANGE and leaves that sequence's output undefined;
+ * positions[i] >= 256 * max_blocks_per_sequence sets RIB200_DEVICE_POSITION_OUT_OF_RANGE.  The workspace is that of
+ * rib200_batched_decode_workspace_bytes(batch, 256 * max_blocks_per_sequence). */
+Rib200Status rib200_paged_decode_attention(const void *query, const void *key, const void *value, const void *gate,
+                                           void *output, void *page_pool, size_t pool_pages,
+                                           const uint32_t *block_tables, size_t max_blocks_per_sequence,
+                                           const uint32_t *positions, size_t batch, void *workspace,
+                                           size_t workspace_bytes, void *stream);
 /* Recurrent gated-delta decode step for a batch of sequences: states[i] FP32 [value_heads][128][128]
  * (array of device pointers, itself in device memory); q,k BF16 [batch][key_heads][128], v BF16
  * [batch][value_heads][128], beta/log_decay FP32 [batch][value_heads], out FP32 [batch][value_heads][128]. */

@@ -108,6 +108,7 @@ PROTOTYPES = {
     "rib200_online_attention_decode_static_scratch": [vp, vp, vp, vp, vp, vp, sz, C.POINTER(AttentionShape), C.c_int32,
                                                       vp, vp],
     "rib200_set_decode_early_kv_fetch": [C.c_int32],
+    "rib200_paged_decode_attention": [vp, vp, vp, vp, vp, vp, sz, vp, sz, vp, sz, vp, sz, vp],
     "rib200_device_status": [vp, C.POINTER(C.c_uint32)],
 }
 

@@ -128,11 +128,26 @@ def batched_serving_decode(dev, stream, hbm_peak, batch=64, lo=1024, hi=32768, s
         attn(i)
         gdn(i)
 
+    # the same contexts served from a pool of 256-token pages handed out in shuffled order
+    blocks = [c // K.PAGE_TOKENS for c in caps]
+    pool_pages = sum(blocks)
+    pool = _bf16(gen, dev, pool_pages, 2, HKV, K.PAGE_TOKENS, D)
+    order = torch.randperm(pool_pages, generator=cpu_gen).tolist()
+    table_rows, handed = [], 0
+    for n in blocks:
+        table_rows.append(order[handed:handed + n] + [0] * (max(blocks) - n))
+        handed += n
+    tables = torch.tensor(table_rows, device=dev, dtype=torch.int32)
+
+    def paged(i):
+        K.paged_decode_attention(q, k, v, gate, o, pool, pool_pages, tables, max(blocks), dpos, batch, ws, ws_bytes,
+                                 stream)
+
     attn_bytes = sum(4096 * n + 24576 for n in lengths)
     gdn_bytes = batch * 2 * HV * DK * DK * 4
     res = {"sequences": batch, "total_context_tokens": sum(lengths)}
-    for name, fn, nbytes in (("attention", attn, attn_bytes), ("gdn_decode", gdn, gdn_bytes),
-                             ("attention+gdn_decode", both, attn_bytes + gdn_bytes)):
+    for name, fn, nbytes in (("attention", attn, attn_bytes), ("attention_paged", paged, attn_bytes),
+                             ("gdn_decode", gdn, gdn_bytes), ("attention+gdn_decode", both, attn_bytes + gdn_bytes)):
         ms, cv = _median_ms(fn, stream, warmup=3, reps=10, calls=4)
         res[name] = {"ms": ms, "cv": cv, "bytes": nbytes, "GB/s": nbytes / ms / 1e6,
                      "frac_of_measured_hbm": nbytes / ms / 1e6 / hbm_peak}

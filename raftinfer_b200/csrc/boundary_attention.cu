@@ -585,4 +585,49 @@ Rib200Status rib200_batched_decode_attention(const void *query, const void *key,
   });
 }
 
+Rib200Status rib200_paged_decode_attention(const void *query, const void *key, const void *value, const void *gate,
+                                           void *output, void *page_pool, size_t pool_pages,
+                                           const uint32_t *block_tables, size_t max_blocks_per_sequence,
+                                           const uint32_t *positions, size_t batch, void *workspace,
+                                           size_t workspace_bytes, void *stream) {
+  return guarded([&] {
+    require(query != nullptr && key != nullptr && value != nullptr && gate != nullptr && output != nullptr,
+            "paged decode: an activation pointer is null");
+    require(page_pool != nullptr && block_tables != nullptr && positions != nullptr,
+            "paged decode: the page pool, the block tables or the positions pointer is null");
+    require(workspace != nullptr, "paged decode: workspace is null");
+    require(stream != nullptr, "paged decode: CUDA stream is null");
+    require(batch > 0 && batch <= 65535, "paged decode: batch must be in 1..65535");
+    require(pool_pages > 0 && pool_pages <= 0x7FFFFFFFU, "paged decode: pool_pages out of range");
+    require(max_blocks_per_sequence > 0 && max_blocks_per_sequence <= (0x7FFFFFFFU / 256),
+            "paged decode: max_blocks_per_sequence out of range");
+    const std::size_t partials = mul(mul(batch, kModelQueryHeads, "paged decode overflow"), max_blocks_per_sequence,
+                                     "paged decode overflow");
+    const std::size_t need =
+        mul(mul(partials, kModelHeadDim + 2, "paged decode overflow"), sizeof(float), "paged decode overflow");
+    require(workspace_bytes >= need, "paged decode: workspace is too small");
+    require_aligned16(query, "paged decode: query is not 16-byte aligned");
+    require_aligned16(key, "paged decode: key is not 16-byte aligned");
+    require_aligned16(value, "paged decode: value is not 16-byte aligned");
+    require_aligned16(gate, "paged decode: gate is not 16-byte aligned");
+    require_aligned16(output, "paged decode: output is not 16-byte aligned");
+    require_aligned16(page_pool, "paged decode: page pool is not 16-byte aligned");
+    require_aligned16(workspace, "paged decode: workspace is not 16-byte aligned");
+    BatchedDecodeArgs args{};
+    args.query = query;
+    args.key = key;
+    args.value = value;
+    args.gate = gate;
+    args.output = output;
+    args.positions = positions;
+    args.batch = static_cast<std::uint32_t>(batch);
+    args.partition_capacity = static_cast<std::uint32_t>(max_blocks_per_sequence);
+    args.workspace = static_cast<float *>(workspace);
+    args.page_pool = page_pool;
+    args.block_tables = block_tables;
+    args.pool_pages = static_cast<std::uint32_t>(pool_pages);
+    launch_batched_decode_attention(args, static_cast<cudaStream_t>(stream));
+  });
+}
+
 } // extern "C"

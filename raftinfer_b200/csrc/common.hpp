@@ -100,6 +100,10 @@ struct BatchedDecodeArgs {
   std::uint32_t batch;
   std::uint32_t partition_capacity; // partitions of the largest cache
   float *workspace;                 // max[batch][16*cap], then sum[batch][16*cap], then value[batch][16*cap][256]
+  // paged form: kv_caches and max_context_tokens are null, partition_capacity is the width of a table row
+  void *page_pool;                    // [pool_pages][2][4][256][256] BF16
+  const std::uint32_t *block_tables;  // [batch][partition_capacity] page indices
+  std::uint32_t pool_pages;
 };
 void launch_batched_decode_attention(const BatchedDecodeArgs &args, cudaStream_t stream);
 

@@ -117,7 +117,15 @@ struct DecodeParams {
   std::size_t partial_stride; // floats between sequences in partial_max / partial_sum (batched)
   unsigned int *status;
   std::uint32_t early_kv; // single sequence, host position: the first ring slots are fetched before the wait below
+  // Paged form of the batched kernel: `cache` is the page pool, a page holds one partition (256 tokens) in the
+  // head-major layout of a 256-token cache, and block_tables[sequence][partition] names the page.
+  const std::uint32_t *block_tables;
+  std::uint32_t max_blocks;
+  std::uint32_t pool_pages;
 };
+
+constexpr std::uint32_t kPageTokens = 256;
+constexpr std::size_t kPageElems = static_cast<std::size_t>(2) * 4 * kPageTokens * 256;
 
 __device__ __forceinline__ std::uint32_t smem_address(const void *p) {
   return static_cast<std::uint32_t>(__cvta_generic_to_shared(p));
@@ -257,7 +265,8 @@ __global__ void __launch_bounds__(T::kWarps * 32, T::kCtasPerSm) decode_partitio
   RIB200_DECODE_STAMP(g_decode_trace, trace_cta, 0);
 
   const int seq = Batched ? static_cast<int>(blockIdx.z) : 0;
-  const std::uint32_t max_ctx = Batched ? p.max_ctx_array[seq] : p.max_ctx;
+  const bool paged = Batched && p.block_tables != nullptr;
+  const std::uint32_t max_ctx = (Batched && !paged) ? p.max_ctx_array[seq] : p.max_ctx;
   const std::uint32_t pos = p.pos_array != nullptr ? p.pos_array[seq] : p.host_pos;
   if (pos >= max_ctx) {
     if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) {
@@ -286,9 +295,29 @@ __global__ void __launch_bounds__(T::kWarps * 32, T::kCtasPerSm) decode_partitio
   const int g = lane >> 2;
   const int t = lane & 3;
   const int kvh = blockIdx.y;
-  __nv_bfloat16 *cache = Batched ? static_cast<__nv_bfloat16 *>(p.caches[seq]) : p.cache;
-  __nv_bfloat16 *k_plane = cache + static_cast<std::size_t>(kvh) * max_ctx * kHeadDim;
-  __nv_bfloat16 *v_plane = k_plane + static_cast<std::size_t>(kKvHeads) * max_ctx * kHeadDim;
+  // Token `tok` of a head's plane sits at row tok - origin: a contiguous cache holds the whole context, a page
+  // only this CTA's partition.
+  __nv_bfloat16 *cache = p.cache;
+  std::uint32_t plane_tokens = max_ctx;
+  std::uint32_t origin = 0;
+  if constexpr (Batched) {
+    if (paged) {
+      const std::uint32_t page = p.block_tables[static_cast<std::size_t>(seq) * p.max_blocks + blockIdx.x];
+      if (page >= p.pool_pages) {
+        if (threadIdx.x == 0) {
+          atomicOr(p.status, static_cast<unsigned int>(RIB200_DEVICE_PAGE_OUT_OF_RANGE));
+        }
+        return;
+      }
+      cache = p.cache + static_cast<std::size_t>(page) * kPageElems;
+      plane_tokens = kPageTokens;
+      origin = begin;
+    } else {
+      cache = static_cast<__nv_bfloat16 *>(p.caches[seq]);
+    }
+  }
+  __nv_bfloat16 *k_plane = cache + static_cast<std::size_t>(kvh) * plane_tokens * kHeadDim;
+  __nv_bfloat16 *v_plane = k_plane + static_cast<std::size_t>(kKvHeads) * plane_tokens * kHeadDim;
   const std::size_t act_seq = static_cast<std::size_t>(seq);
   const std::size_t kv_in_base = (act_seq * kKvHeads + kvh) * kHeadDim;
 
@@ -318,7 +347,8 @@ __global__ void __launch_bounds__(T::kWarps * 32, T::kCtasPerSm) decode_partitio
     const std::uint32_t rows = min(static_cast<std::uint32_t>(kStepTokens), end - tok0);
     const std::uint32_t slot = ring + (n % kRingSlots) * kSlotBytes;
     const std::uint32_t bar = bars + (n % kRingSlots) * 8;
-    const __nv_bfloat16 *src = ((n & 1U) == 0 ? k_plane : v_plane) + static_cast<std::size_t>(tok0) * kHeadDim;
+    const __nv_bfloat16 *src =
+        ((n & 1U) == 0 ? k_plane : v_plane) + static_cast<std::size_t>(tok0 - origin) * kHeadDim;
     fence_proxy_async(); // earlier reads of this ring position are ordered before the TMA write
     mbarrier_expect_tx(bar, rows * kRowBytes);
 #pragma unroll
@@ -361,7 +391,7 @@ __global__ void __launch_bounds__(T::kWarps * 32, T::kCtasPerSm) decode_partitio
       const uint4 raw = load8_as_bf16<F32>(is_value ? p.value : p.key, kv_in_base + 8 * lane);
       sts128(slot + row_offset(pos - tok0) + lane * 16, raw);
       __nv_bfloat16 *plane = is_value ? v_plane : k_plane;
-      *reinterpret_cast<uint4 *>(plane + static_cast<std::size_t>(pos) * kHeadDim + 8 * lane) = raw;
+      *reinterpret_cast<uint4 *>(plane + static_cast<std::size_t>(pos - origin) * kHeadDim + 8 * lane) = raw;
       touched = true;
     }
     if (tok0 + kStepTokens > end) {
@@ -641,7 +671,7 @@ __global__ void __launch_bounds__(256) decode_combine_kernel(const DecodeParams 
   RIB200_DECODE_STAMP(g_combine_trace, trace_cta, 1);
 
   const int seq = Batched ? static_cast<int>(blockIdx.z) : 0;
-  const std::uint32_t max_ctx = Batched ? p.max_ctx_array[seq] : p.max_ctx;
+  const std::uint32_t max_ctx = (Batched && p.block_tables == nullptr) ? p.max_ctx_array[seq] : p.max_ctx;
   const std::uint32_t pos = p.pos_array != nullptr ? p.pos_array[seq] : p.host_pos;
   if (pos >= max_ctx) {
     return;
@@ -881,6 +911,13 @@ void launch_batched_decode_attention(const BatchedDecodeArgs &a, cudaStream_t st
   params.output = a.output;
   params.caches = a.kv_caches;
   params.max_ctx_array = a.max_context_tokens;
+  if (a.block_tables != nullptr) {
+    params.cache = static_cast<__nv_bfloat16 *>(a.page_pool);
+    params.block_tables = a.block_tables;
+    params.max_blocks = a.partition_capacity;
+    params.pool_pages = a.pool_pages;
+    params.max_ctx = a.partition_capacity * kPageTokens;
+  }
   params.pos_array = a.positions;
   params.partition_tokens = 256;
   params.threshold_tokens = 256;

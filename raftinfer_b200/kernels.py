@@ -25,6 +25,7 @@ TOKEN_MAJOR, HEAD_MAJOR = 0, 1
 OK, INVALID_ARGUMENT, UNAVAILABLE, CUDA_ERROR, INTERNAL, UNSUPPORTED, RESOURCE_EXHAUSTED = range(7)
 # device status bits
 DEVICE_DECODE_CAPACITY_EXCEEDED, DEVICE_POSITION_OUT_OF_RANGE, DEVICE_WAIT_TIMED_OUT = 1, 2, 4
+DEVICE_PAGE_OUT_OF_RANGE = 8
 
 
 class Qwen35PrimitiveError(RuntimeError):
@@ -339,6 +340,19 @@ def batched_decode_attention(query, key, value, gate, output, kv_caches, max_con
                                                _ptr(kv_caches), _ptr(max_context_tokens), _ptr(positions), batch,
                                                largest_max_context_tokens, _ptr(workspace), workspace_bytes,
                                                _stream(stream)))
+
+
+PAGE_TOKENS = 256
+
+
+def paged_decode_attention(query, key, value, gate, output, page_pool, pool_pages, block_tables, max_blocks_per_sequence,
+                           positions, batch, workspace, workspace_bytes, stream):
+    """Batched decode step over a pool of 256-token pages ([2][4][256][256] BF16 each) named by per-sequence block
+    tables (uint32, device memory)."""
+    _check(lib.rib200_paged_decode_attention(_ptr(query), _ptr(key), _ptr(value), _ptr(gate), _ptr(output),
+                                             _ptr(page_pool), pool_pages, _ptr(block_tables), max_blocks_per_sequence,
+                                             _ptr(positions), batch, _ptr(workspace), workspace_bytes,
+                                             _stream(stream)))
 
 
 # ---- gated delta ---------------------------------------------------------------------------------

@@ -382,3 +382,95 @@ def test_batched_ragged_decode():
         assert np.array_equal(cache_bits_of(caches[i]).reshape(fulls[i].shape), fulls[i])
         want = ob.attention_core_cache(qs[i][None], gs[i][None], fulls[i], caps[i], ctx - 1)[0]
         gate_bf16_outputs(compare(got[i], want))
+
+
+def paged_setup(contexts, seed, spare_pages=3, shuffle_seed=5):
+    """Contiguous per-sequence caches and the same rows scattered over a page pool in a shuffled page order."""
+    batch = len(contexts)
+    caps = [-(-c // K.PAGE_TOKENS) * K.PAGE_TOKENS for c in contexts]
+    max_blocks = max(caps) // K.PAGE_TOKENS
+    qs, gs, ks, vs, before, after = [], [], [], [], [], []
+    for i, ctx in enumerate(contexts):
+        q, gate, k, v = decode_operands(seed + i, ctx)
+        qs.append(q), gs.append(gate), ks.append(k[ctx - 1]), vs.append(v[ctx - 1])
+        before.append(make_cache(k, v, caps[i], ctx - 1))
+        after.append(make_cache(k, v, caps[i], ctx))
+    pool_pages = sum(c // K.PAGE_TOKENS for c in caps) + spare_pages
+    order = np.random.default_rng(shuffle_seed).permutation(pool_pages)
+    pool = np.full((pool_pages, 2, HKV, K.PAGE_TOKENS, D), NAN_BITS, dtype=np.uint16)
+    want_pool = pool.copy()
+    tables = np.full((batch, max_blocks), 0xFFFFFFFF, dtype=np.uint32)  # entries past the live context: never read
+    nxt = 0
+    for i, cap in enumerate(caps):
+        for b in range(cap // K.PAGE_TOKENS):
+            page = int(order[nxt])
+            nxt += 1
+            tables[i, b] = page
+            rows = slice(b * K.PAGE_TOKENS, (b + 1) * K.PAGE_TOKENS)
+            pool[page] = before[i][:, :, rows]
+            want_pool[page] = after[i][:, :, rows]
+    return dict(batch=batch, caps=caps, max_blocks=max_blocks, qs=qs, gs=gs, ks=ks, vs=vs, before=before, after=after,
+                pool=pool, want_pool=want_pool, tables=tables, pool_pages=pool_pages)
+
+
+def test_paged_decode_matches_the_contiguous_batched_step():
+    """The paged form reads the same rows through a block table: outputs are bit-identical to the batched step over
+    contiguous caches, the appended rows land in the right pages, and every other page byte is untouched (unused
+    pages and table entries past the live context hold NaNs / an invalid page number)."""
+    contexts = [1, 200, 256, 257, 1000, 2049, 4096]
+    s = paged_setup(contexts, 0xB2000C00)
+    batch, largest = s["batch"], max(s["caps"])
+    dq, dg = act_tensor(np.stack(s["qs"]), K.DTYPE_BF16), act_tensor(np.stack(s["gs"]), K.DTYPE_BF16)
+    dk, dv = act_tensor(np.stack(s["ks"]), K.DTYPE_BF16), act_tensor(np.stack(s["vs"]), K.DTYPE_BF16)
+    dpos = torch.tensor([c - 1 for c in contexts], device=dev(), dtype=torch.int32)
+    ws_bytes = K.batched_decode_workspace_bytes(batch, largest)
+    stream = torch.cuda.current_stream()
+
+    caches = [cache_to_device(c) for c in s["before"]]
+    ptrs = torch.tensor([c.data_ptr() for c in caches], device=dev(), dtype=torch.int64)
+    dcaps = torch.tensor(s["caps"], device=dev(), dtype=torch.int32)
+    out_flat = torch.zeros(batch, HQ, D, device=dev(), dtype=torch.bfloat16)
+    ws = torch.zeros(ws_bytes // 4, device=dev())
+    K.batched_decode_attention(dq, dk, dv, dg, out_flat, ptrs, dcaps, dpos, batch, largest, ws, ws_bytes, stream)
+
+    pool = cache_to_device(s["pool"])
+    tables = torch.from_numpy(s["tables"].view(np.int32)).to(dev())
+    out_paged = torch.zeros(batch, HQ, D, device=dev(), dtype=torch.bfloat16)
+    ws2 = torch.zeros(ws_bytes // 4, device=dev())
+    K.paged_decode_attention(dq, dk, dv, dg, out_paged, pool, s["pool_pages"], tables, s["max_blocks"], dpos, batch,
+                             ws2, ws_bytes, stream)
+    torch.cuda.synchronize()
+    assert K.device_status(stream) == 0
+    assert torch.equal(out_paged, out_flat)
+    assert np.array_equal(cache_bits_of(pool).reshape(s["want_pool"].shape), s["want_pool"])
+    got = to_numpy_f32(out_paged)
+    for i, ctx in enumerate(contexts):
+        want = ob.attention_core_cache(s["qs"][i][None], s["gs"][i][None], s["after"][i], s["caps"][i], ctx - 1)[0]
+        gate_bf16_outputs(compare(got[i], want))
+
+
+def test_paged_decode_flags_a_page_outside_the_pool():
+    """A live table entry that names a page the pool does not hold is reported through the status word; the kernel
+    does not touch memory for it, and the other sequences of the batch are served as usual."""
+    contexts = [300, 700]
+    s = paged_setup(contexts, 0xB2000D00)
+    s["tables"][0, 1] = s["pool_pages"] + 7
+    batch, largest = s["batch"], max(s["caps"])
+    dq, dg = act_tensor(np.stack(s["qs"]), K.DTYPE_BF16), act_tensor(np.stack(s["gs"]), K.DTYPE_BF16)
+    dk, dv = act_tensor(np.stack(s["ks"]), K.DTYPE_BF16), act_tensor(np.stack(s["vs"]), K.DTYPE_BF16)
+    dpos = torch.tensor([c - 1 for c in contexts], device=dev(), dtype=torch.int32)
+    ws_bytes = K.batched_decode_workspace_bytes(batch, largest)
+    ws = torch.zeros(ws_bytes // 4, device=dev())
+    pool = cache_to_device(s["pool"])
+    tables = torch.from_numpy(s["tables"].view(np.int32)).to(dev())
+    out = torch.zeros(batch, HQ, D, device=dev(), dtype=torch.bfloat16)
+    stream = torch.cuda.current_stream()
+    K.paged_decode_attention(dq, dk, dv, dg, out, pool, s["pool_pages"], tables, s["max_blocks"], dpos, batch, ws,
+                             ws_bytes, stream)
+    torch.cuda.synchronize()
+    assert K.device_status(stream) == K.DEVICE_PAGE_OUT_OF_RANGE
+    want = ob.attention_core_cache(s["qs"][1][None], s["gs"][1][None], s["after"][1], s["caps"][1], contexts[1] - 1)[0]
+    gate_bf16_outputs(compare(to_numpy_f32(out)[1], want))
+    with pytest.raises(K.Qwen35PrimitiveError):
+        K.paged_decode_attention(dq, dk, dv, dg, out, pool, s["pool_pages"], tables, s["max_blocks"], dpos, batch, ws,
+                                 ws_bytes // 2, stream)
