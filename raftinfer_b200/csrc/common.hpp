@@ -87,6 +87,15 @@ struct DecodeArgs {
   std::uint32_t max_partitions;     // stride of the partial arrays
   bool activations_f32;
 };
+// 128-byte opaque image of a driver tensor map (TMA descriptor); 64-byte aligned as the driver's type is.
+struct alignas(64) TensorMapBytes {
+  unsigned char bytes[128];
+};
+// Tiled map over a row-major FP32 matrix [rows][row_floats], box [box_rows][box_floats], 128-byte swizzle
+// (box_floats * 4 must be 128).  Defined next to the other tensor-map code in prefill_attention.cu.
+void encode_f32_rows_map(void *map_out, void *base, std::uint64_t row_floats, std::uint64_t rows,
+                         std::uint32_t box_floats, std::uint32_t box_rows);
+
 void launch_decode_attention(const DecodeArgs &args, cudaStream_t stream);
 void set_decode_early_kv_fetch(bool enabled);
 

@@ -13,11 +13,13 @@
 // (beta = 0, log decay = 0, k = q = v = 0), which leave the state untouched.
 //
 // Two kernels.  `prepare` is parallel over (chunk, value head): T by forward substitution in FP32, the four
-// dense products on mma.sync TF32 tensor-core tiles, results (W, U, P, G) to the workspace.  `apply` walks the
-// chunks in order for one (value head, 32-column slice of the state): the slice lives in shared memory, and
-// W S0, Q S0, P Delta and K^T Delta are TF32 tensor-core products.  State columns are independent, so the
-// four slices of a head never talk to each other.  TF32 (10-bit mantissa, FP32 accumulate) rather than BF16
-// keeps the FP32 state within 1e-3 relative L2 of the sequential recurrence over 64 chunks.
+// dense products on mma.sync TF32 tensor-core tiles; it leaves every operand the apply kernel multiplies with as a
+// ready shared-memory image (K-major, 128-byte swizzle) in the workspace.  `apply` walks the chunks in order for one
+// (value head, 32-column slice of the state): the slice lives in registers (FP32) and, rounded to TF32, in shared
+// memory as the B operand; [Q; W] S0, P Delta and K^T diag(e) Delta are tcgen05.mma.kind::tf32 products with
+// accumulators in tensor memory.  State columns are independent, so the four slices of a head never talk to each
+// other.  TF32 (10-bit mantissa, FP32 accumulate) rather than BF16 keeps the FP32 state within 1e-3 relative L2 of
+// the sequential recurrence over 64 chunks.
 //
 // Dense flops per launch: chunks * value_heads * [2 C^2 (3 dk + 2 dv) + 6 C dk dv].
 
@@ -38,20 +40,29 @@ constexpr int kSlice = 32;          // state columns per apply CTA
 constexpr int kPitchRow = 132;      // [row][k] operands read along k by lane%4: pitch = 4 mod 32
 constexpr int kPitchCol = 136;      // [k][n] operands read along n by lane/4: pitch = 8 mod 32
 constexpr int kPitchSq = 68;        // 64-wide [row][k] operands
-constexpr int kPitchSlice = 40;     // 32-wide [k][n] operands
-// Workspace record of one (chunk, value head), in floats.  Every block is stored at the padded pitch the apply
-// kernel reads it at, so that one bulk copy brings a block into shared memory ready for conflict-free fragment reads.
-constexpr std::size_t kRecW = 0;                                   // [64][132], rounded to TF32
-constexpr std::size_t kRecGamma = kRecW + kChunk * kPitchRow;      // [64] exp(G_i)
-constexpr std::size_t kRecE = kRecGamma + kChunk;                  // [64] exp(G_C - G_i)
-constexpr std::size_t kRecP = kRecE + kChunk;                      // [64][68], rounded to TF32
-constexpr std::size_t kRecU = kRecP + kChunk * kPitchSq;           // [4 slices][64][40]
-constexpr std::size_t kRecFloats = kRecU + (kDim / kSlice) * kChunk * kPitchSlice;
-// FP32 (TF32-rounded) copy of one (chunk, key head)'s q and k rows, zero rows past the last token
-constexpr std::size_t kCopyQ = 0;                                  // [64][132]
-constexpr std::size_t kCopyK = kCopyQ + kChunk * kPitchRow;        // [64][136]
-constexpr std::size_t kCopyFloats = kCopyK + kChunk * kPitchCol;
-static_assert(kRecFloats % 4 == 0 && kCopyFloats % 4 == 0 && kRecP % 4 == 0 && kRecU % 4 == 0, "16-byte blocks");
+// Workspace record of one (chunk, value head), in bytes.  A1, A2 and A3 are images of tcgen05 shared-memory
+// operands: K-major, 32 TF32 elements (128 bytes) per row and k-block, [k-block][row][128 bytes], the 16-byte chunk
+// index of a row XORed with row % 8 (SWIZZLE_128B).
+constexpr std::uint32_t kRowBytes = 128;
+constexpr std::uint32_t kA1Block = 128 * kRowBytes;               // rows 0..63 Q, rows 64..127 W; 4 k-blocks
+constexpr std::uint32_t kA1Bytes = 4 * kA1Block;
+constexpr std::uint32_t kA2Block = kChunk * kRowBytes;            // P, 64 rows; 2 k-blocks
+constexpr std::uint32_t kA2Bytes = 2 * kA2Block;
+constexpr std::uint32_t kA3Block = kDim * kRowBytes;              // (K diag(e))^T, 128 rows; 2 k-blocks
+constexpr std::uint32_t kA3Bytes = 2 * kA3Block;
+constexpr int kPitchU = 36;                                        // U slice [64][36] FP32, then gamma [64]
+constexpr std::uint32_t kUBytes = (kChunk * kPitchU + kChunk) * 4;
+constexpr std::uint32_t kRecA1 = 0;
+constexpr std::uint32_t kRecA2 = kRecA1 + kA1Bytes;
+constexpr std::uint32_t kRecA3 = kRecA2 + kA2Bytes;
+constexpr std::uint32_t kRecU = kRecA3 + kA3Bytes;                // [4 slices] of kUBytes
+constexpr std::uint32_t kRecBytes = kRecU + (kDim / kSlice) * kUBytes;
+static_assert(kRecBytes % 16 == 0 && kUBytes % 16 == 0, "16-byte blocks");
+
+// Byte offset of element (row, k) inside an operand image whose k-blocks are block_bytes apart.
+__host__ __device__ constexpr std::uint32_t image_offset(std::uint32_t row, std::uint32_t k, std::uint32_t block_bytes) {
+  return (k >> 5) * block_bytes + row * kRowBytes + ((((k & 31U) >> 2) ^ (row & 7U)) << 4) + ((k & 3U) << 2);
+}
 
 struct ChunkParams {
   const void *q, *k, *v;
@@ -60,8 +71,7 @@ struct ChunkParams {
   const float *log_decay;
   float *state;
   float *out;
-  float *workspace;
-  float *qk_copy; // [chunk][key_head] copy records, after the chunk records
+  unsigned char *workspace;
   unsigned int *status;
   std::uint32_t tokens;
   std::uint32_t chunks;
@@ -144,17 +154,6 @@ template <bool F32> __device__ __forceinline__ void store_rows(float *dst, int p
   }
 }
 
-// Copies a dense [rows][cols] FP32 block from global memory into dst[rows][pitch].  256 threads.
-__device__ __forceinline__ void load_block(float *dst, int pitch, const float *src, int rows, int cols,
-                                           int src_pitch) {
-  const int vec_per_row = cols / 4;
-  for (int i = threadIdx.x; i < rows * vec_per_row; i += 256) {
-    const int r = i / vec_per_row;
-    const int c = (i % vec_per_row) * 4;
-    *reinterpret_cast<float4 *>(dst + r * pitch + c) = *reinterpret_cast<const float4 *>(src + r * src_pitch + c);
-  }
-}
-
 // Optional timeline probe (compile with -DRIB200_TRACE): thread 0 of the first CTA stamps clock64() at eight points
 // per chunk, the producer's lane 0 at four more; the first prepare CTA stamps row 127.
 #ifdef RIB200_TRACE
@@ -172,7 +171,7 @@ __device__ long long g_gdn_trace[128 * 16];
 #endif
 
 // ---- prepare: per (chunk, value head) ---------------------------------------------------------------
-constexpr int kPrepSmemFloats = kChunk * kPitchRow + kChunk * kPitchCol + 2 * kChunk * kPitchSq + 3 * kChunk;
+constexpr int kPrepSmemFloats = kChunk * kPitchRow + kChunk * kPitchCol + 2 * kChunk * kPitchSq + 4 * kChunk;
 
 template <bool F32>
 __global__ void __launch_bounds__(256, 2) gdn_chunk_prepare_kernel(const ChunkParams p) {
@@ -184,12 +183,13 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_prepare_kernel(const ChunkPa
   float *sG = sT + kChunk * kPitchSq;         // [64] inclusive running log decay
   float *sBeta = sG + kChunk;                 // [64]
   float *sBg = sBeta + kChunk;                // [64] beta * exp(G)
+  float *sE = sBg + kChunk;                   // [64] exp(G_C - G)
 
   const std::uint32_t chunk = blockIdx.x;
   const std::uint32_t head = blockIdx.y;
   const std::uint32_t key_head = head % p.key_heads;
   const std::uint32_t tok0 = chunk * kChunk;
-  float *rec = p.workspace + (static_cast<std::size_t>(chunk) * p.value_heads + head) * kRecFloats;
+  unsigned char *rec = p.workspace + (static_cast<std::size_t>(chunk) * p.value_heads + head) * kRecBytes;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int g = lane >> 2;
@@ -230,26 +230,23 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_prepare_kernel(const ChunkPa
   if (threadIdx.x == 0 && blockIdx.x == 0) {
     RIB200_GDN_STAMP(127, 1);
   }
-  if (head < p.key_heads) { // the first value head of each key head leaves the q and k rows for the apply kernel
-    float *copy = p.qk_copy + (static_cast<std::size_t>(chunk) * p.key_heads + head) * kCopyFloats;
-    for (int i = threadIdx.x; i < kChunk * (kDim / 4); i += 256) {
-      const int r = i / (kDim / 4);
-      const int c = (i % (kDim / 4)) * 4;
-      const float4 kv = *reinterpret_cast<const float4 *>(sK + r * kPitchRow + c);
-      const float4 qv = *reinterpret_cast<const float4 *>(sX + r * kPitchRow + c);
-      *reinterpret_cast<float4 *>(copy + kCopyK + r * kPitchCol + c) =
-          make_float4(__uint_as_float(tf32(kv.x)), __uint_as_float(tf32(kv.y)), __uint_as_float(tf32(kv.z)),
-                      __uint_as_float(tf32(kv.w)));
-      *reinterpret_cast<float4 *>(copy + kCopyQ + r * kPitchRow + c) =
-          make_float4(__uint_as_float(tf32(qv.x)), __uint_as_float(tf32(qv.y)), __uint_as_float(tf32(qv.z)),
-                      __uint_as_float(tf32(qv.w)));
-    }
+  // Q rows of the [Q; W] operand image, rounded to TF32 (zero rows past the last token)
+  for (int i = threadIdx.x; i < kChunk * (kDim / 4); i += 256) {
+    const int r = i / (kDim / 4);
+    const int c = (i % (kDim / 4)) * 4;
+    const float4 qv = *reinterpret_cast<const float4 *>(sX + r * kPitchRow + c);
+    *reinterpret_cast<float4 *>(rec + kRecA1 + image_offset(r, c, kA1Block)) =
+        make_float4(__uint_as_float(tf32(qv.x)), __uint_as_float(tf32(qv.y)), __uint_as_float(tf32(qv.z)),
+                    __uint_as_float(tf32(qv.w)));
   }
   if (threadIdx.x < kChunk) {
     const float gamma = expf(sG[threadIdx.x]);
     sBg[threadIdx.x] = sBeta[threadIdx.x] * gamma;
-    rec[kRecGamma + threadIdx.x] = gamma;
-    rec[kRecE + threadIdx.x] = expf(sG[kChunk - 1] - sG[threadIdx.x]);
+    sE[threadIdx.x] = expf(sG[kChunk - 1] - sG[threadIdx.x]);
+#pragma unroll
+    for (int slice = 0; slice < kDim / kSlice; ++slice) {
+      reinterpret_cast<float *>(rec + kRecU + slice * kUBytes)[kChunk * kPitchU + threadIdx.x] = gamma;
+    }
   }
 
   if (threadIdx.x == 0 && blockIdx.x == 0) {
@@ -286,12 +283,18 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_prepare_kernel(const ChunkPa
 #pragma unroll
     for (int n = 0; n < 4; ++n) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int i = 16 * mt + g + (e >> 1) * 8;
-        const int j = 8 * (nt0 + n) + 2 * t + (e & 1);
-        const float decay = j <= i ? expf(sG[i] - sG[j]) : 0.0F;
-        sA[i * kPitchSq + j] = j < i ? sBeta[i] * decay * acc_k[n][e] : 0.0F;
-        rec[kRecP + i * kPitchSq + j] = __uint_as_float(tf32(decay * acc_q[n][e]));
+      for (int half = 0; half < 2; ++half) {
+        const int i = 16 * mt + g + half * 8;
+        const int j0 = 8 * (nt0 + n) + 2 * t;
+        float pv[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int j = j0 + e;
+          const float decay = j <= i ? expf(sG[i] - sG[j]) : 0.0F;
+          sA[i * kPitchSq + j] = j < i ? sBeta[i] * decay * acc_k[n][2 * half + e] : 0.0F;
+          pv[e] = __uint_as_float(tf32(decay * acc_q[n][2 * half + e]));
+        }
+        *reinterpret_cast<float2 *>(rec + kRecA2 + image_offset(i, j0, kA2Block)) = make_float2(pv[0], pv[1]);
       }
     }
   }
@@ -378,14 +381,26 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_prepare_kernel(const ChunkPa
       const int d = n0 + 8 * n + 2 * t;
       const int i = 16 * mt + g;
       // W only ever feeds TF32 products: round it here, once
-      *reinterpret_cast<float2 *>(rec + kRecW + i * kPitchRow + d) =
+      *reinterpret_cast<float2 *>(rec + kRecA1 + image_offset(kChunk + i, d, kA1Block)) =
           make_float2(__uint_as_float(tf32(acc_w[n][0])), __uint_as_float(tf32(acc_w[n][1])));
-      *reinterpret_cast<float2 *>(rec + kRecW + (i + 8) * kPitchRow + d) =
+      *reinterpret_cast<float2 *>(rec + kRecA1 + image_offset(kChunk + i + 8, d, kA1Block)) =
           make_float2(__uint_as_float(tf32(acc_w[n][2])), __uint_as_float(tf32(acc_w[n][3])));
-      float *u = rec + kRecU + (d / kSlice) * (kChunk * kPitchSlice) + d % kSlice;
-      *reinterpret_cast<float2 *>(u + i * kPitchSlice) = make_float2(acc_u[n][0], acc_u[n][1]);
-      *reinterpret_cast<float2 *>(u + (i + 8) * kPitchSlice) = make_float2(acc_u[n][2], acc_u[n][3]);
+      float *u = reinterpret_cast<float *>(rec + kRecU + (d / kSlice) * kUBytes) + d % kSlice;
+      *reinterpret_cast<float2 *>(u + i * kPitchU) = make_float2(acc_u[n][0], acc_u[n][1]);
+      *reinterpret_cast<float2 *>(u + (i + 8) * kPitchU) = make_float2(acc_u[n][2], acc_u[n][3]);
     }
+  }
+  // (K diag(e))^T operand image: row = key dim, k = token.  A thread gathers four tokens of one dim from sK.  Last,
+  // because nothing in this kernel waits for it.
+  for (int i = threadIdx.x; i < kDim * (kChunk / 4); i += 256) {
+    const int d = i / (kChunk / 4);
+    const int j = (i % (kChunk / 4)) * 4;
+    const float4 e4 = *reinterpret_cast<const float4 *>(sE + j);
+    *reinterpret_cast<float4 *>(rec + kRecA3 + image_offset(d, j, kA3Block)) =
+        make_float4(__uint_as_float(tf32(sK[j * kPitchRow + d] * e4.x)),
+                    __uint_as_float(tf32(sK[(j + 1) * kPitchRow + d] * e4.y)),
+                    __uint_as_float(tf32(sK[(j + 2) * kPitchRow + d] * e4.z)),
+                    __uint_as_float(tf32(sK[(j + 3) * kPitchRow + d] * e4.w)));
   }
   if (threadIdx.x == 0 && blockIdx.x == 0) {
     RIB200_GDN_STAMP(127, 6);
@@ -393,29 +408,51 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_prepare_kernel(const ChunkPa
 }
 
 // ---- apply: per (state slice, value head), chunks in order ---------------------------------------------
-// Eight consumer warps and one producer warp.  The producer streams each chunk's operands into shared memory with
-// TMA bulk row copies (cp.async.bulk, bytes counted on an mbarrier), one chunk ahead of the consumers: W, K, the U
-// slice and G sit in a two-stage ring, Q and P in single buffers that are refilled as soon as their last reader is
-// done.  Rows land at padded pitches so that every tensor-core fragment read is free of bank conflicts.
+// 192 threads.  Warps 0-3 own the 128 lanes of tensor memory (thread = row of every product), warp 4 issues the
+// tcgen05 products (whole warp in step, one elected lane issuing), lane 0 of warp 5 streams the operand images of
+// each chunk into shared memory with bulk copies counted on mbarriers.  Per chunk:
+//   X  = [Q; W] S0            M 128 (rows 0..63 Q S0, rows 64..127 W S0), N 32, K 128
+//   warps 2-3: Delta = U - X[64..]  ->  B operand (TF32);   warps 0-1: keep gamma_i (Q S0)_i
+//   SD = (K diag(e))^T Delta  M 128, N 32, K 64
+//   O2 = P Delta              M 128 (rows 64..127 are don't-care), N 32, K 64
+//   all: S = gamma_C S + SD (FP32 registers) -> B operand (TF32): the next chunk's first product waits for this
+//   warps 0-1: O = gamma_i (Q S0)_i + O2, each row through shared memory and out with a bulk copy
 // Every mbarrier wait is bounded; when one runs out the CTA records RIB200_DEVICE_WAIT_TIMED_OUT, stops waiting
 // and copying, and runs to its end (its results are then meaningless, as the status word says).
-constexpr int kApplyConsumers = 256;
-constexpr int kApplyThreads = kApplyConsumers + 32;
-constexpr int kStageW = 0;                                   // W, gamma, e: one block of the record
-constexpr int kStageGamma = kStageW + kChunk * kPitchRow;
-constexpr int kStageE = kStageGamma + kChunk;
-constexpr int kStageK = kStageE + kChunk;
-constexpr int kStageD = kStageK + kChunk * kPitchCol;
-constexpr int kStageFloats = kStageD + kChunk * kPitchSlice;
-constexpr int kApplyS = 0;
-constexpr int kApplyStage = kApplyS + kDim * kPitchSlice;
-constexpr int kApplyQ = kApplyStage + 2 * kStageFloats;
-constexpr int kApplyP = kApplyQ + kChunk * kPitchRow;
-constexpr int kApplyFloats = kApplyP + kChunk * kPitchSq;
-constexpr int kApplyBars = 8; // full[2], empty[2], q_full, q_empty, p_full, p_empty
-constexpr int kApplySmemBytes = kApplyFloats * 4 + kApplyBars * 8 + 16;
+constexpr int kApplyThreads = 192;
+constexpr std::uint32_t kSmA1 = 0;                         // two stages of the [Q; W] image
+constexpr std::uint32_t kSmA23 = kSmA1 + 2 * kA1Bytes;     // P image, then the (K diag(e))^T image
+constexpr std::uint32_t kSmB1 = kSmA23 + kA2Bytes + kA3Bytes; // S^T, [4 k-blocks][32 rows][128 bytes]
+constexpr std::uint32_t kB1Block = kSlice * kRowBytes;
+constexpr std::uint32_t kSmBD = kSmB1 + 4 * kB1Block;      // Delta^T, [2 k-blocks][32 rows][128 bytes]
+constexpr std::uint32_t kSmU = kSmBD + 2 * kB1Block;       // two stages of U slice + gamma
+constexpr std::uint32_t kUStage = 10240;                   // stage stride: the output tile that reuses a stage wants 1 KiB alignment
+constexpr std::uint32_t kSmBars = kSmU + 2 * kUStage;
+enum : std::uint32_t {
+  kBarA1Full = 0,   // [2] bytes of a [Q; W] image
+  kBarA1Empty = 2,  // [2] the product that read it has completed
+  kBarA23Full = 4,
+  kBarA23Empty = 5,
+  kBarUFull = 6,    // [2]
+  kBarUEmpty = 8,   // [2] 128 readers
+  kBarXDone = 10,   // X is in tensor memory
+  kBarDReady = 11,  // Delta^T is in shared memory (64 writers)
+  kBarSdDone = 12,  // SD is in tensor memory
+  kBarSReady = 13,  // S^T is in shared memory, X and SD have been read (128 threads)
+  kBarO2Done = 14,  // O2 is in tensor memory
+  kBarO2Free = 15,  // O2 has been read (64 threads)
+  kBarCount = 16
+};
+constexpr std::uint32_t kSmTmemSlot = kSmBars + kBarCount * 8;
+constexpr std::uint32_t kSmAbort = kSmTmemSlot + 4;
+constexpr std::uint32_t kApplySmemBytes = kSmAbort + 4 + 1024; // + room to align the base to 1 KiB
+static_assert(kUStage >= kUBytes && kSmA23 % 1024 == 0 && kSmB1 % 1024 == 0 && kSmBD % 1024 == 0 && kSmU % 1024 == 0 &&
+                  kSmBars % 8 == 0,
+              "operand images sit on 1 KiB boundaries");
 static_assert(kApplySmemBytes <= 232448, "apply kernel exceeds the shared memory of an SM");
 constexpr long long kWaitLimitCycles = 1LL << 28;
+constexpr std::uint32_t kTmemColumns = 128; // X at 0, O2 at 32, SD at 64
+constexpr std::uint32_t kCopyPiece = 16384;  // the operand images come in as several bulk copies in flight at once
 
 __device__ __forceinline__ std::uint32_t smem_address(const void *p) {
   return static_cast<std::uint32_t>(__cvta_generic_to_shared(p));
@@ -448,51 +485,151 @@ __device__ __forceinline__ void bulk_copy_g2s(std::uint32_t dst, const void *src
                : "memory");
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 256;\n" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ bool elect_one() {
+  std::uint32_t chosen;
+  asm volatile("{\n"
+               ".reg .pred p;\n"
+               "elect.sync _|p, 0xFFFFFFFF;\n"
+               "selp.u32 %0, 1, 0, p;\n"
+               "}\n"
+               : "=r"(chosen));
+  return chosen != 0;
+}
+// Shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1 KiB apart, descriptor version 1.
+__device__ __forceinline__ std::uint64_t smem_desc(std::uint32_t addr) {
+  std::uint64_t d = 0;
+  d |= static_cast<std::uint64_t>((addr & 0x3FFFFU) >> 4);
+  d |= static_cast<std::uint64_t>(1) << 16;            // leading-dimension offset: unused by this layout
+  d |= static_cast<std::uint64_t>(1024 >> 4) << 32;    // stride between 8-row groups
+  d |= static_cast<std::uint64_t>(1) << 46;            // version
+  d |= static_cast<std::uint64_t>(2) << 61;            // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor: TF32 x TF32 -> FP32, both operands K-major, M 128, N 32.
+constexpr std::uint32_t kIdesc = (1U << 4) | (2U << 7) | (2U << 10) | (static_cast<std::uint32_t>(kSlice >> 3) << 17) |
+                                 (static_cast<std::uint32_t>(128 >> 4) << 24);
+__device__ __forceinline__ void umma_tf32(std::uint32_t d_tmem, std::uint64_t a_desc, std::uint64_t b_desc,
+                                          std::uint32_t accumulate) {
+  asm volatile("{\n"
+               ".reg .pred p;\n"
+               "setp.ne.b32 p, %4, 0;\n"
+               "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n"
+               "}\n" ::"r"(d_tmem),
+               "l"(a_desc), "l"(b_desc), "r"(kIdesc), "r"(accumulate)
+               : "memory");
+}
+__device__ __forceinline__ void umma_commit(std::uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(std::uint32_t taddr, float (&v)[32]) {
+  std::uint32_t r[32];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+               "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+               "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+                 "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+                 "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+                 "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+               : "r"(taddr)
+               : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    v[i] = __uint_as_float(r[i]);
+  }
+}
+__device__ __forceinline__ void sts32(std::uint32_t addr, std::uint32_t value) {
+  asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(addr), "r"(value) : "memory");
+}
+// Shared-memory loads by 32-bit shared address: unlike loads through a generic pointer they are known not to
+// alias global stores, so a run of them is issued back to back.
+__device__ __forceinline__ void sts128(std::uint32_t addr, float a, float b, float c, float d) {
+  asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ float lds32(std::uint32_t addr) {
+  float value;
+  asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(value) : "r"(addr));
+  return value;
+}
+__device__ __forceinline__ float4 lds128(std::uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
 
-__global__ void __launch_bounds__(kApplyThreads, 1) gdn_chunk_apply_kernel(const ChunkParams p) {
-  extern __shared__ __align__(16) float apply_smem[];
-  float *sS = apply_smem + kApplyS;  // [128][40] state slice
-  float *sQ = apply_smem + kApplyQ;  // [64][132]
-  float *sP = apply_smem + kApplyP;  // [64][68]
-  const std::uint32_t bars = smem_address(apply_smem + kApplyFloats);
-  volatile std::uint32_t *abort_flag = reinterpret_cast<volatile std::uint32_t *>(apply_smem + kApplyFloats) +
-                                       2 * kApplyBars;
-  const std::uint32_t bar_full0 = bars, bar_empty0 = bars + 16, bar_q_full = bars + 32, bar_q_empty = bars + 40,
-                      bar_p_full = bars + 48, bar_p_empty = bars + 56;
+__global__ void __launch_bounds__(kApplyThreads, 1)
+    gdn_chunk_apply_kernel(const ChunkParams p, const __grid_constant__ TensorMapBytes out_map) {
+  extern __shared__ unsigned char apply_smem_raw[];
+  const std::uint32_t base = (smem_address(apply_smem_raw) + 1023U) & ~1023U;
+  unsigned char *smem = apply_smem_raw + (base - smem_address(apply_smem_raw));
+  const std::uint32_t bars = base + kSmBars;
+  auto bar = [&](std::uint32_t index) { return bars + index * 8; };
+  volatile std::uint32_t *tmem_slot = reinterpret_cast<volatile std::uint32_t *>(smem + kSmTmemSlot);
+  volatile std::uint32_t *abort_flag = reinterpret_cast<volatile std::uint32_t *>(smem + kSmAbort);
 
   const std::uint32_t slice = blockIdx.x;
   const std::uint32_t head = blockIdx.y;
-  const std::uint32_t key_head = head % p.key_heads;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   float *state = p.state + static_cast<std::size_t>(head) * kDim * kDim + slice * kSlice;
 
   if (threadIdx.x == 0) {
-    mbarrier_init(bar_full0, 1);
-    mbarrier_init(bar_full0 + 8, 1);
-    mbarrier_init(bar_empty0, 8);
-    mbarrier_init(bar_empty0 + 8, 8);
-    mbarrier_init(bar_q_full, 1);
-    mbarrier_init(bar_q_empty, 8);
-    mbarrier_init(bar_p_full, 1);
-    mbarrier_init(bar_p_empty, 8);
+    for (std::uint32_t i = 0; i < kBarCount; ++i) {
+      std::uint32_t count = 1;
+      if (i == kBarSReady) {
+        count = 128;
+      } else if (i == kBarUEmpty || i == kBarUEmpty + 1) {
+        count = 65; // the 64 readers of U rows, and thread 0 once the output tile has left the stage
+      } else if (i == kBarDReady || i == kBarO2Free) {
+        count = 64;
+      }
+      mbarrier_init(bar(i), count);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  if (threadIdx.x < kApplyConsumers) {
-    load_block(sS, kPitchSlice, state, kDim, kSlice, kDim);
+  if (warp == 4) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(base + kSmTmemSlot),
+                 "r"(kTmemColumns)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
   }
-  fence_proxy_async();
+
+  // State slice: row `key` of S in this thread's registers (FP32), S^T rounded to TF32 as the B operand.
+  float s_reg[kSlice];
+  const std::uint32_t key = threadIdx.x; // warps 0-3
+  // element (n, k) of a B operand image with 32-row k-blocks
+  auto b_offset = [](std::uint32_t n, std::uint32_t k) { return image_offset(n, k, kB1Block); };
+  if (warp < 4) {
+#pragma unroll
+    for (int c = 0; c < kSlice; c += 4) {
+      const float4 v = *reinterpret_cast<const float4 *>(state + static_cast<std::size_t>(key) * kDim + c);
+      s_reg[c] = v.x;
+      s_reg[c + 1] = v.y;
+      s_reg[c + 2] = v.z;
+      s_reg[c + 3] = v.w;
+    }
+#pragma unroll
+    for (int n = 0; n < kSlice; ++n) {
+      sts32(base + kSmB1 + b_offset(n, key), tf32(s_reg[n]));
+    }
+    fence_proxy_async();
+  }
+  tcgen05_fence_before();
   __syncthreads();
+  tcgen05_fence_after();
+  const std::uint32_t tmem = *tmem_slot;
 
   // bounded wait; once the CTA has given up nobody waits any more
-  auto wait = [&](std::uint32_t bar, std::uint32_t parity) {
-    if (*abort_flag != 0 || mbarrier_try_wait(bar, parity)) {
+  auto wait = [&](std::uint32_t b, std::uint32_t parity) {
+    if (*abort_flag != 0 || mbarrier_try_wait(b, parity)) {
       return;
     }
     const long long started = clock64();
-    while (!mbarrier_try_wait(bar, parity)) {
+    while (!mbarrier_try_wait(b, parity)) {
       if (*abort_flag != 0) {
         return;
       }
@@ -504,255 +641,275 @@ __global__ void __launch_bounds__(kApplyThreads, 1) gdn_chunk_apply_kernel(const
     }
   };
 
-  if (warp == kApplyConsumers / 32) {
-    // ---- producer ----
-    // One lane issues five bulk copies per chunk; every block of the records is stored ready-padded.
-    std::uint32_t issued[4] = {0, 0, 0, 0}; // fills of stage 0, stage 1, Q, P
+  if (warp == 5) {
+    // ---- producer: three bulk copies per chunk ----
     if (lane == 0) {
+      std::uint32_t issued[5] = {0, 0, 0, 0, 0}; // A1 stage 0/1, A23, U stage 0/1
       for (std::uint32_t chunk = 0; chunk < p.chunks; ++chunk) {
-        const float *rec = p.workspace + (static_cast<std::size_t>(chunk) * p.value_heads + head) * kRecFloats;
-        const float *copy = p.qk_copy + (static_cast<std::size_t>(chunk) * p.key_heads + key_head) * kCopyFloats;
+        const unsigned char *rec =
+            p.workspace + (static_cast<std::size_t>(chunk) * p.value_heads + head) * kRecBytes;
         const std::uint32_t s = chunk & 1U;
-        float *stage = apply_smem + kApplyStage + s * kStageFloats;
-        // stage: W with gamma and e, K, U slice
         if (chunk >= 2) {
-          wait(bar_empty0 + 8 * s, ((chunk >> 1) - 1) & 1U);
+          wait(bar(kBarA1Empty + s), ((chunk >> 1) - 1) & 1U);
         }
         if (*abort_flag != 0) {
           break;
         }
-        RIB200_GDN_STAMP(chunk, 8);
-        fence_proxy_async();
-        constexpr std::uint32_t kWBytes = (kChunk * kPitchRow + 2 * kChunk) * 4;
-        constexpr std::uint32_t kKBytes = kChunk * kPitchCol * 4;
-        constexpr std::uint32_t kUBytes = kChunk * kPitchSlice * 4;
-        mbarrier_expect_tx(bar_full0 + 8 * s, kWBytes + kKBytes + kUBytes);
-        bulk_copy_g2s(smem_address(stage + kStageW), rec + kRecW, kWBytes, bar_full0 + 8 * s);
-        bulk_copy_g2s(smem_address(stage + kStageD), rec + kRecU + slice * (kChunk * kPitchSlice), kUBytes,
-                      bar_full0 + 8 * s);
-        bulk_copy_g2s(smem_address(stage + kStageK), copy + kCopyK, kKBytes, bar_full0 + 8 * s);
+        mbarrier_expect_tx(bar(kBarA1Full + s), kA1Bytes);
+#pragma unroll
+        for (std::uint32_t part = 0; part < kA1Bytes; part += kCopyPiece) {
+          bulk_copy_g2s(base + kSmA1 + s * kA1Bytes + part, rec + kRecA1 + part, kCopyPiece, bar(kBarA1Full + s));
+        }
         ++issued[s];
-        RIB200_GDN_STAMP(chunk, 9);
-        // Q
-        if (chunk >= 1) {
-          wait(bar_q_empty, (chunk - 1) & 1U);
+        if (chunk >= 2) {
+          wait(bar(kBarUEmpty + s), ((chunk >> 1) - 1) & 1U);
         }
         if (*abort_flag != 0) {
           break;
         }
-        fence_proxy_async();
-        mbarrier_expect_tx(bar_q_full, kChunk * kPitchRow * 4);
-        bulk_copy_g2s(smem_address(sQ), copy + kCopyQ, kChunk * kPitchRow * 4, bar_q_full);
+        fence_proxy_async(); // the readers of this stage used ordinary loads
+        mbarrier_expect_tx(bar(kBarUFull + s), kUBytes);
+        bulk_copy_g2s(base + kSmU + s * kUStage, rec + kRecU + slice * kUBytes, kUBytes, bar(kBarUFull + s));
+        ++issued[3 + s];
+        if (chunk >= 1) {
+          wait(bar(kBarA23Empty), (chunk - 1) & 1U);
+        }
+        if (*abort_flag != 0) {
+          break;
+        }
+        mbarrier_expect_tx(bar(kBarA23Full), kA2Bytes + kA3Bytes);
+#pragma unroll
+        for (std::uint32_t part = 0; part < kA2Bytes + kA3Bytes; part += kCopyPiece) {
+          bulk_copy_g2s(base + kSmA23 + part, rec + kRecA2 + part, kCopyPiece, bar(kBarA23Full));
+        }
         ++issued[2];
-        RIB200_GDN_STAMP(chunk, 10);
-        // P
-        if (chunk >= 1) {
-          wait(bar_p_empty, (chunk - 1) & 1U);
-        }
-        if (*abort_flag != 0) {
-          break;
-        }
-        fence_proxy_async();
-        mbarrier_expect_tx(bar_p_full, kChunk * kPitchSq * 4);
-        bulk_copy_g2s(smem_address(sP), rec + kRecP, kChunk * kPitchSq * 4, bar_p_full);
-        ++issued[3];
-        RIB200_GDN_STAMP(chunk, 11);
       }
-    }
-    // after giving up: let the copies already issued land before the CTA's shared memory goes away
-    if (lane == 0 && *abort_flag != 0) {
-      const std::uint32_t full_bars[4] = {bar_full0, bar_full0 + 8, bar_q_full, bar_p_full};
-      for (int b = 0; b < 4; ++b) {
-        if (issued[b] > 0) {
-          const std::uint32_t parity = (issued[b] - 1) & 1U;
-          const long long started = clock64();
-          while (!mbarrier_try_wait(full_bars[b], parity) && clock64() - started < kWaitLimitCycles) {
+      // after giving up: let the copies already issued land before the CTA's shared memory goes away
+      if (*abort_flag != 0) {
+        const std::uint32_t full_bars[5] = {bar(kBarA1Full), bar(kBarA1Full + 1), bar(kBarA23Full), bar(kBarUFull),
+                                            bar(kBarUFull + 1)};
+        for (int b = 0; b < 5; ++b) {
+          if (issued[b] > 0) {
+            const std::uint32_t parity = (issued[b] - 1) & 1U;
+            const long long started = clock64();
+            while (!mbarrier_try_wait(full_bars[b], parity) && clock64() - started < kWaitLimitCycles) {
+            }
           }
         }
       }
     }
-    return;
+  } else if (warp == 4) {
+    // ---- tensor-core issue: the whole warp walks the chunks, one elected lane issues ----
+    const bool issuer = elect_one();
+    const std::uint64_t b1_desc = smem_desc(base + kSmB1);
+    const std::uint64_t bd_desc = smem_desc(base + kSmBD);
+    const std::uint64_t a2_desc = smem_desc(base + kSmA23);
+    const std::uint64_t a3_desc = smem_desc(base + kSmA23 + kA2Bytes);
+    // descriptor address field counts 16-byte units: a k-step inside a k-block is 32 bytes = 2 units
+    auto step = [](std::uint32_t ks, std::uint32_t block_bytes) {
+      return static_cast<std::uint64_t>(((ks >> 2) * block_bytes + (ks & 3U) * 32U) >> 4);
+    };
+    for (std::uint32_t chunk = 0; chunk < p.chunks; ++chunk) {
+      const std::uint32_t s = chunk & 1U;
+      wait(bar(kBarA1Full + s), (chunk >> 1) & 1U);
+      if (chunk >= 1) {
+        wait(bar(kBarSReady), (chunk - 1) & 1U);
+      }
+      tcgen05_fence_after();
+      if (issuer) {
+        RIB200_GDN_STAMP(chunk, 5);
+      }
+      if (issuer && *abort_flag == 0) {
+        const std::uint64_t a1_desc = smem_desc(base + kSmA1 + s * kA1Bytes);
+#pragma unroll
+        for (std::uint32_t ks = 0; ks < 16; ++ks) {
+          umma_tf32(tmem, a1_desc + step(ks, kA1Block), b1_desc + step(ks, kB1Block), ks);
+        }
+        umma_commit(bar(kBarXDone));
+        umma_commit(bar(kBarA1Empty + s));
+      }
+      __syncwarp();
+      wait(bar(kBarDReady), chunk & 1U);
+      if (issuer) {
+        RIB200_GDN_STAMP(chunk, 6);
+      }
+      wait(bar(kBarA23Full), chunk & 1U);
+      if (issuer) {
+        RIB200_GDN_STAMP(chunk, 7);
+      }
+      tcgen05_fence_after();
+      if (issuer && *abort_flag == 0) {
+#pragma unroll
+        for (std::uint32_t ks = 0; ks < 8; ++ks) {
+          umma_tf32(tmem + 64, a3_desc + step(ks, kA3Block), bd_desc + step(ks, kB1Block), ks);
+        }
+        umma_commit(bar(kBarSdDone));
+      }
+      __syncwarp();
+      if (chunk >= 1) {
+        wait(bar(kBarO2Free), (chunk - 1) & 1U);
+      }
+      tcgen05_fence_after();
+      if (issuer && *abort_flag == 0) {
+#pragma unroll
+        for (std::uint32_t ks = 0; ks < 8; ++ks) {
+          umma_tf32(tmem + 32, a2_desc + step(ks, kA2Block), bd_desc + step(ks, kB1Block), ks);
+        }
+        umma_commit(bar(kBarO2Done));
+        umma_commit(bar(kBarA23Empty));
+      }
+      __syncwarp();
+      if (*abort_flag != 0) {
+        break;
+      }
+    }
+  } else {
+    // ---- warps 0-3: thread = lane of tensor memory ----
+    const std::uint32_t lane_base = static_cast<std::uint32_t>(warp * 32) << 16;
+    const bool upper = warp >= 2;                  // rows 64..127 of X: W S0 of token threadIdx.x - 64
+    const std::uint32_t token = threadIdx.x & 63U; // the token this thread serves in X and O2
+    for (std::uint32_t chunk = 0; chunk < p.chunks; ++chunk) {
+      const std::uint32_t s = chunk & 1U;
+      const std::uint32_t u_stage = base + kSmU + s * kUStage; // U slice [64][36] FP32, then gamma [64]
+      if (threadIdx.x == 0) {
+        RIB200_GDN_STAMP(chunk, 0);
+      }
+      wait(bar(kBarUFull + s), (chunk >> 1) & 1U);
+      wait(bar(kBarXDone), chunk & 1U);
+      tcgen05_fence_after();
+      if (threadIdx.x == 0) {
+        RIB200_GDN_STAMP(chunk, 1);
+      }
+      if (threadIdx.x == 64) {
+        RIB200_GDN_STAMP(chunk, 12);
+      }
+      float x[kSlice];
+      tmem_ld32(tmem + lane_base, x);
+      if (threadIdx.x == 64) {
+        RIB200_GDN_STAMP(chunk, 14);
+      }
+      const float gamma_c = lds32(u_stage + (kChunk * kPitchU + kChunk - 1) * 4);
+      if (upper) {
+        // Delta = U - W S0, written as the B operand of the two products that follow.  All loads first, then the
+        // arithmetic, then the stores: the store helper is a compiler barrier for memory accesses.
+        float4 u[kSlice / 4];
+#pragma unroll
+        for (int c = 0; c < kSlice / 4; ++c) {
+          u[c] = lds128(u_stage + (token * kPitchU + 4 * c) * 4);
+        }
+        std::uint32_t d[kSlice];
+#pragma unroll
+        for (int c = 0; c < kSlice / 4; ++c) {
+          d[4 * c] = tf32(u[c].x - x[4 * c]);
+          d[4 * c + 1] = tf32(u[c].y - x[4 * c + 1]);
+          d[4 * c + 2] = tf32(u[c].z - x[4 * c + 2]);
+          d[4 * c + 3] = tf32(u[c].w - x[4 * c + 3]);
+        }
+#pragma unroll
+        for (int n = 0; n < kSlice; ++n) {
+          sts32(base + kSmBD + b_offset(n, token), d[n]);
+        }
+        if (threadIdx.x == 64) {
+          RIB200_GDN_STAMP(chunk, 15);
+        }
+        fence_proxy_async();
+        tcgen05_fence_before();
+        mbarrier_arrive(bar(kBarDReady));
+        if (threadIdx.x == 64) {
+          RIB200_GDN_STAMP(chunk, 13);
+        }
+        mbarrier_arrive(bar(kBarUEmpty + s)); // the lower half hands the stage back after using it for the output
+      } else {
+        const float gamma = lds32(u_stage + (kChunk * kPitchU + token) * 4);
+#pragma unroll
+        for (int c = 0; c < kSlice; ++c) {
+          x[c] *= gamma;
+        }
+      }
+      if (threadIdx.x == 0) {
+        RIB200_GDN_STAMP(chunk, 2);
+      }
+
+      wait(bar(kBarSdDone), chunk & 1U);
+      tcgen05_fence_after();
+      if (threadIdx.x == 0) {
+        RIB200_GDN_STAMP(chunk, 3);
+      }
+      {
+        float sd[kSlice];
+        tmem_ld32(tmem + lane_base + 64, sd);
+        std::uint32_t rounded[kSlice];
+#pragma unroll
+        for (int n = 0; n < kSlice; ++n) {
+          s_reg[n] = s_reg[n] * gamma_c + sd[n];
+          rounded[n] = tf32(s_reg[n]);
+        }
+#pragma unroll
+        for (int n = 0; n < kSlice; ++n) {
+          sts32(base + kSmB1 + b_offset(n, key), rounded[n]);
+        }
+      }
+      fence_proxy_async();
+      tcgen05_fence_before();
+      mbarrier_arrive(bar(kBarSReady));
+      if (threadIdx.x == 0) {
+        RIB200_GDN_STAMP(chunk, 4);
+      }
+      if (!upper) {
+        // O = gamma_i (Q S0)_i + (P Delta)_i; the thread owns a row.
+        wait(bar(kBarO2Done), chunk & 1U);
+        tcgen05_fence_after();
+        if (threadIdx.x == 0) {
+          RIB200_GDN_STAMP(chunk, 8);
+        }
+        float o2[kSlice];
+        tmem_ld32(tmem + lane_base + 32, o2);
+        tcgen05_fence_before();
+        mbarrier_arrive(bar(kBarO2Free));
+        // The 64 x 32 tile goes through the U stage (dead since the Delta step) in the 128-byte-swizzled layout of
+        // the output's tensor map, and out with one tiled bulk store; rows past the last token are clipped by it.
+#pragma unroll
+        for (std::uint32_t c = 0; c < kSlice / 4; ++c) {
+          sts128(u_stage + token * kRowBytes + ((c ^ (token & 7U)) << 4), x[4 * c] + o2[4 * c],
+                 x[4 * c + 1] + o2[4 * c + 1], x[4 * c + 2] + o2[4 * c + 2], x[4 * c + 3] + o2[4 * c + 3]);
+        }
+        fence_proxy_async();
+        asm volatile("bar.sync 1, 64;\n" ::: "memory");
+        if (threadIdx.x == 0) {
+          if (*abort_flag == 0) {
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];\n" ::"l"(
+                             reinterpret_cast<std::uint64_t>(&out_map)),
+                         "r"(static_cast<int>(head * kDim + slice * kSlice)), "r"(static_cast<int>(chunk * kChunk)),
+                         "r"(u_stage)
+                         : "memory");
+          }
+          asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+          RIB200_GDN_STAMP(chunk, 9);
+          asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory"); // the tile has been read
+          mbarrier_arrive(bar(kBarUEmpty + s));
+        }
+      }
+      if (threadIdx.x == 0) {
+        RIB200_GDN_STAMP(chunk, 11);
+      }
+      if (*abort_flag != 0) {
+        break;
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < kSlice; c += 4) {
+      *reinterpret_cast<float4 *>(state + static_cast<std::size_t>(key) * kDim + c) =
+          make_float4(s_reg[c], s_reg[c + 1], s_reg[c + 2], s_reg[c + 3]);
+    }
   }
 
-  // ---- consumers ----
-  const int g = lane >> 2;
-  const int t = lane & 3;
-  const int mt = warp & 3;
-  const int nc0 = (warp >> 2) * 16;
-  for (std::uint32_t chunk = 0; chunk < p.chunks; ++chunk) {
-    const std::uint32_t tok0 = chunk * kChunk;
-    const std::uint32_t s = chunk & 1U;
-    float *stage = apply_smem + kApplyStage + s * kStageFloats;
-    const float *sW = stage + kStageW;
-    const float *sK = stage + kStageK;
-    float *sD = stage + kStageD;
-    const float *sGamma = stage + kStageGamma;
-    const float *sE = stage + kStageE;
-
-    if (threadIdx.x == 0) {
-      RIB200_GDN_STAMP(chunk, 0);
-    }
-    wait(bar_full0 + 8 * s, (chunk >> 1) & 1U);
-    wait(bar_q_full, chunk & 1U);
-    if (threadIdx.x == 0) {
-      RIB200_GDN_STAMP(chunk, 1);
-    }
-    consumer_sync(); // the previous chunk's state update is complete
-    if (threadIdx.x == 0) {
-      RIB200_GDN_STAMP(chunk, 2);
-    }
-
-    // W S0 and Q S0: 64 x 32, contraction over 128.  Warp: rows 16*(warp&3).., columns 16*(warp>>2)..
-    // W and Q arrive already rounded to TF32.
-    float acc_w[2][4] = {};
-    float acc_o[2][4] = {};
-#pragma unroll
-    for (int ks = 0; ks < 16; ++ks) {
-      std::uint32_t aw[4];
-      std::uint32_t aq[4];
-      const int col = ks * 8 + t;
-      aw[0] = __float_as_uint(sW[(16 * mt + g) * kPitchRow + col]);
-      aw[1] = __float_as_uint(sW[(16 * mt + g + 8) * kPitchRow + col]);
-      aw[2] = __float_as_uint(sW[(16 * mt + g) * kPitchRow + col + 4]);
-      aw[3] = __float_as_uint(sW[(16 * mt + g + 8) * kPitchRow + col + 4]);
-      aq[0] = __float_as_uint(sQ[(16 * mt + g) * kPitchRow + col]);
-      aq[1] = __float_as_uint(sQ[(16 * mt + g + 8) * kPitchRow + col]);
-      aq[2] = __float_as_uint(sQ[(16 * mt + g) * kPitchRow + col + 4]);
-      aq[3] = __float_as_uint(sQ[(16 * mt + g + 8) * kPitchRow + col + 4]);
-#pragma unroll
-      for (int n = 0; n < 2; ++n) {
-        const std::uint32_t b0 = tf32(sS[col * kPitchSlice + nc0 + 8 * n + g]);
-        const std::uint32_t b1 = tf32(sS[(col + 4) * kPitchSlice + nc0 + 8 * n + g]);
-        mma_tf32(acc_w[n], aw, b0, b1);
-        mma_tf32(acc_o[n], aq, b0, b1);
-      }
-    }
-    __syncwarp();
-    if (threadIdx.x == 0) {
-      RIB200_GDN_STAMP(chunk, 3);
-    }
-    if (lane == 0) {
-      mbarrier_arrive(bar_q_empty);
-    }
-    // Delta = U - W S0 (in place over the U slice); the output starts as exp(G_i) * (Q S0)_i
-    {
-      const int i0 = 16 * mt + g;
-      const float gamma0 = sGamma[i0];
-      const float gamma1 = sGamma[i0 + 8];
-#pragma unroll
-      for (int n = 0; n < 2; ++n) {
-        const int c = nc0 + 8 * n + 2 * t;
-        float2 lo = *reinterpret_cast<float2 *>(sD + i0 * kPitchSlice + c);
-        float2 hi = *reinterpret_cast<float2 *>(sD + (i0 + 8) * kPitchSlice + c);
-        lo.x -= acc_w[n][0];
-        lo.y -= acc_w[n][1];
-        hi.x -= acc_w[n][2];
-        hi.y -= acc_w[n][3];
-        *reinterpret_cast<float2 *>(sD + i0 * kPitchSlice + c) = lo;
-        *reinterpret_cast<float2 *>(sD + (i0 + 8) * kPitchSlice + c) = hi;
-        acc_o[n][0] *= gamma0;
-        acc_o[n][1] *= gamma0;
-        acc_o[n][2] *= gamma1;
-        acc_o[n][3] *= gamma1;
-      }
-    }
-    consumer_sync(); // Delta is complete
-    if (threadIdx.x == 0) {
-      RIB200_GDN_STAMP(chunk, 4);
-    }
-
-    // S = exp(G_C) S + K^T (diag(exp(G_C - G)) Delta): 128 x 32, contraction over the 64 tokens.
-    // Warp: state rows 16*warp.., all 32 columns.  This is the step the next chunk waits for, so it runs first.
-    {
-      const float gamma_c = sGamma[kChunk - 1];
-      float acc[4][4];
-      const int r0 = 16 * warp + g;
-#pragma unroll
-      for (int n = 0; n < 4; ++n) {
-        const int c = 8 * n + 2 * t;
-        const float2 lo = *reinterpret_cast<const float2 *>(sS + r0 * kPitchSlice + c);
-        const float2 hi = *reinterpret_cast<const float2 *>(sS + (r0 + 8) * kPitchSlice + c);
-        acc[n][0] = lo.x * gamma_c;
-        acc[n][1] = lo.y * gamma_c;
-        acc[n][2] = hi.x * gamma_c;
-        acc[n][3] = hi.y * gamma_c;
-      }
-#pragma unroll
-      for (int ks = 0; ks < 8; ++ks) {
-        std::uint32_t a[4];
-        const int tok = ks * 8 + t;
-        a[0] = __float_as_uint(sK[tok * kPitchCol + 16 * warp + g]);
-        a[1] = __float_as_uint(sK[tok * kPitchCol + 16 * warp + g + 8]);
-        a[2] = __float_as_uint(sK[(tok + 4) * kPitchCol + 16 * warp + g]);
-        a[3] = __float_as_uint(sK[(tok + 4) * kPitchCol + 16 * warp + g + 8]);
-        const float e0 = sE[tok];
-        const float e1 = sE[tok + 4];
-#pragma unroll
-        for (int n = 0; n < 4; ++n) {
-          const std::uint32_t b0 = tf32(sD[tok * kPitchSlice + 8 * n + g] * e0);
-          const std::uint32_t b1 = tf32(sD[(tok + 4) * kPitchSlice + 8 * n + g] * e1);
-          mma_tf32(acc[n], a, b0, b1);
-        }
-      }
-#pragma unroll
-      for (int n = 0; n < 4; ++n) {
-        const int c = 8 * n + 2 * t;
-        *reinterpret_cast<float2 *>(sS + r0 * kPitchSlice + c) = make_float2(acc[n][0], acc[n][1]);
-        *reinterpret_cast<float2 *>(sS + (r0 + 8) * kPitchSlice + c) = make_float2(acc[n][2], acc[n][3]);
-      }
-    }
-
-    // O += P Delta: 64 x 32, contraction over the 64 tokens (P is lower triangular: stop at the diagonal tile;
-    // P arrives already rounded to TF32)
-    if (threadIdx.x == 0) {
-      RIB200_GDN_STAMP(chunk, 5);
-    }
-    wait(bar_p_full, chunk & 1U);
-    if (threadIdx.x == 0) {
-      RIB200_GDN_STAMP(chunk, 6);
-    }
-    for (int ks = 0; ks < 2 * mt + 2; ++ks) {
-      std::uint32_t a[4];
-      const int col = ks * 8 + t;
-      a[0] = __float_as_uint(sP[(16 * mt + g) * kPitchSq + col]);
-      a[1] = __float_as_uint(sP[(16 * mt + g + 8) * kPitchSq + col]);
-      a[2] = __float_as_uint(sP[(16 * mt + g) * kPitchSq + col + 4]);
-      a[3] = __float_as_uint(sP[(16 * mt + g + 8) * kPitchSq + col + 4]);
-#pragma unroll
-      for (int n = 0; n < 2; ++n) {
-        const std::uint32_t b0 = tf32(sD[col * kPitchSlice + nc0 + 8 * n + g]);
-        const std::uint32_t b1 = tf32(sD[(col + 4) * kPitchSlice + nc0 + 8 * n + g]);
-        mma_tf32(acc_o[n], a, b0, b1);
-      }
-    }
-    __syncwarp();
-    if (threadIdx.x == 0) {
-      RIB200_GDN_STAMP(chunk, 7);
-    }
-    if (lane == 0) {
-      mbarrier_arrive(bar_p_empty);
-      mbarrier_arrive(bar_empty0 + 8 * s);
-    }
-    {
-      const std::uint32_t r0 = tok0 + 16 * mt + g;
-#pragma unroll
-      for (int n = 0; n < 2; ++n) {
-        const std::size_t c = static_cast<std::size_t>(head) * kDim + slice * kSlice + nc0 + 8 * n + 2 * t;
-        const std::size_t row_pitch = static_cast<std::size_t>(p.value_heads) * kDim;
-        if (r0 < p.tokens) {
-          *reinterpret_cast<float2 *>(p.out + r0 * row_pitch + c) = make_float2(acc_o[n][0], acc_o[n][1]);
-        }
-        if (r0 + 8 < p.tokens) {
-          *reinterpret_cast<float2 *>(p.out + (r0 + 8) * row_pitch + c) = make_float2(acc_o[n][2], acc_o[n][3]);
-        }
-      }
-    }
-  }
-  consumer_sync();
-  for (int i = threadIdx.x; i < kDim * (kSlice / 4); i += kApplyConsumers) {
-    const int r = i / (kSlice / 4);
-    const int c = (i % (kSlice / 4)) * 4;
-    *reinterpret_cast<float4 *>(state + r * kDim + c) = *reinterpret_cast<const float4 *>(sS + r * kPitchSlice + c);
+  // every role comes here; the products issued so far have completed or the CTA has given up waiting for them
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    // warps 0-3 waited for the last commit, so nothing is still writing tensor memory
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(kTmemColumns) : "memory");
   }
 }
 
@@ -776,7 +933,11 @@ template <bool F32> void launch(const ChunkParams &params, cudaStream_t stream) 
   gdn_chunk_prepare_kernel<F32>
       <<<dim3(params.chunks, params.value_heads), 256, kPrepSmemFloats * 4, stream>>>(params);
   cuda_ok(cudaGetLastError(), "gated-delta prepare launch");
-  gdn_chunk_apply_kernel<<<dim3(kDim / kSlice, params.value_heads), kApplyThreads, kApplySmemBytes, stream>>>(params);
+  TensorMapBytes out_map;
+  encode_f32_rows_map(&out_map, params.out, static_cast<std::uint64_t>(params.value_heads) * kDim, params.tokens,
+                      kSlice, kChunk);
+  gdn_chunk_apply_kernel<<<dim3(kDim / kSlice, params.value_heads), kApplyThreads, kApplySmemBytes, stream>>>(
+      params, out_map);
   cuda_ok(cudaGetLastError(), "gated-delta apply launch");
 }
 
@@ -789,17 +950,17 @@ extern "C" int rib200_debug_read_gdn_trace(long long *host, std::size_t count) {
 #endif
 
 std::size_t gdn_chunk_workspace_bytes(std::size_t tokens, std::size_t key_heads, std::size_t value_heads) {
+  (void)key_heads;
   const std::size_t chunks = ceil_div(tokens, kChunk, "gated-delta chunk count overflows");
-  const std::size_t records = mul(mul(chunks, value_heads, "gated-delta chunk workspace overflows"),
-                                  kRecFloats * sizeof(float), "gated-delta chunk workspace overflows");
-  const std::size_t copies = mul(mul(chunks, key_heads, "gated-delta chunk workspace overflows"),
-                                 kCopyFloats * sizeof(float), "gated-delta chunk workspace overflows");
-  return add(records, copies, "gated-delta chunk workspace overflows");
+  return mul(mul(chunks, value_heads, "gated-delta chunk workspace overflows"), kRecBytes,
+             "gated-delta chunk workspace overflows");
 }
 
 void launch_gdn_chunked(const GdnCoreArgs &a, void *workspace, cudaStream_t stream) {
   require(workspace != nullptr, "gated-delta chunked prefill needs its workspace");
   require(reinterpret_cast<std::uintptr_t>(workspace) % 16 == 0, "gated-delta chunk workspace is not 16-byte aligned");
+  require(reinterpret_cast<std::uintptr_t>(a.out) % 16 == 0 && reinterpret_cast<std::uintptr_t>(a.state) % 16 == 0,
+          "gated-delta chunked prefill: output and state must be 16-byte aligned");
   ChunkParams p{};
   p.q = a.q;
   p.k = a.k;
@@ -811,13 +972,12 @@ void launch_gdn_chunked(const GdnCoreArgs &a, void *workspace, cudaStream_t stre
   p.log_decay = a.log_decay;
   p.state = a.state;
   p.out = a.out;
-  p.workspace = static_cast<float *>(workspace);
+  p.workspace = static_cast<unsigned char *>(workspace);
   p.tokens = a.tokens;
   p.chunks = (a.tokens + kChunk - 1) / kChunk;
   p.key_heads = a.key_heads;
   p.value_heads = a.value_heads;
   p.status = device_status_word();
-  p.qk_copy = p.workspace + static_cast<std::size_t>(p.chunks) * a.value_heads * kRecFloats;
   if (a.qkv_f32) {
     launch<true>(p, stream);
   } else {

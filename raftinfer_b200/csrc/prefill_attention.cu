@@ -1588,6 +1588,20 @@ template <bool F32, bool Pair, bool Split> void launch(const PrefillArgs &a, cud
 
 } // namespace
 
+void encode_f32_rows_map(void *map_out, void *base, std::uint64_t row_floats, std::uint64_t rows,
+                         std::uint32_t box_floats, std::uint32_t box_rows) {
+  static_assert(sizeof(CUtensorMap) == 128, "the opaque tensor-map type of common.hpp has the driver's size");
+  const cuuint64_t dims[2] = {row_floats, rows};
+  const cuuint64_t strides[1] = {row_floats * sizeof(float)};
+  const cuuint32_t box[2] = {box_floats, box_rows};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  const CUresult rc = encode_tiled_entry()(static_cast<CUtensorMap *>(map_out), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base,
+                                           dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  require(rc == CUDA_SUCCESS, "tensor map encoding failed", RIB200_STATUS_CUDA_ERROR);
+}
+
 #ifdef RIB200_TRACE
 extern "C" int rib200_debug_read_trace(long long *host, std::size_t count) {
   return static_cast<int>(cudaMemcpyFromSymbol(host, g_trace, count * sizeof(long long)));
