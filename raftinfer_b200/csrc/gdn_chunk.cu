@@ -95,7 +95,9 @@ __device__ __forceinline__ void mma_tf32(float (&c)[4], const std::uint32_t (&a)
 
 // Rows [tok0, tok0 + 64) of a [token][heads][128] operand (head `head`) go to dst[64][pitch] as FP32 in two halves,
 // so that other work can run while the loads are in flight: fetch_rows reads this thread's 32 elements of its row
-// into registers (zeros at or past `tokens`), store_rows converts and writes them.  256 threads.
+// into registers (zeros at or past `tokens`), store_rows converts and writes them.  256 threads, four per row.
+// The four threads of a row take 8-element pieces in turn (piece 4 a + part for a = 0..3), so that the 16-byte
+// stores of a quarter-warp (two rows) fall into 32 different banks at a pitch of 4 mod 32 words.
 template <bool F32> struct RowRegs {
   uint4 v[F32 ? 8 : 4];
 };
@@ -105,7 +107,7 @@ __device__ __forceinline__ RowRegs<F32> fetch_rows(const void *src, std::size_t 
                                                    std::uint32_t tok0, std::uint32_t tokens) {
   RowRegs<F32> regs;
   const int row = threadIdx.x >> 2;
-  const int part = threadIdx.x & 3; // 32 elements each
+  const int part = threadIdx.x & 3;
   const std::uint32_t tok = tok0 + row;
   constexpr int kVectors = F32 ? 8 : 4;
   if (tok >= tokens) {
@@ -115,12 +117,16 @@ __device__ __forceinline__ RowRegs<F32> fetch_rows(const void *src, std::size_t 
     }
     return regs;
   }
-  const std::size_t base = static_cast<std::size_t>(tok) * stride + head * kDim + part * 32;
-  const uint4 *s = F32 ? reinterpret_cast<const uint4 *>(static_cast<const float *>(src) + base)
-                       : reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(src) + base);
+  const std::size_t base = static_cast<std::size_t>(tok) * stride + head * kDim + part * 8;
 #pragma unroll
-  for (int i = 0; i < kVectors; ++i) {
-    regs.v[i] = s[i];
+  for (int a = 0; a < 4; ++a) {
+    if constexpr (F32) {
+      const uint4 *s = reinterpret_cast<const uint4 *>(static_cast<const float *>(src) + base + 32 * a);
+      regs.v[2 * a] = s[0];
+      regs.v[2 * a + 1] = s[1];
+    } else {
+      regs.v[a] = *reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(src) + base + 32 * a);
+    }
   }
   return regs;
 }
@@ -128,16 +134,14 @@ __device__ __forceinline__ RowRegs<F32> fetch_rows(const void *src, std::size_t 
 template <bool F32> __device__ __forceinline__ void store_rows(float *dst, int pitch, const RowRegs<F32> &regs) {
   const int row = threadIdx.x >> 2;
   const int part = threadIdx.x & 3;
-  float *d = dst + row * pitch + part * 32;
-  if constexpr (F32) {
+  float *d = dst + row * pitch + part * 8;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      *reinterpret_cast<uint4 *>(d + 4 * i) = regs.v[i];
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const std::uint32_t w[4] = {regs.v[i].x, regs.v[i].y, regs.v[i].z, regs.v[i].w};
+  for (int a = 0; a < 4; ++a) {
+    if constexpr (F32) {
+      *reinterpret_cast<uint4 *>(d + 32 * a) = regs.v[2 * a];
+      *reinterpret_cast<uint4 *>(d + 32 * a + 4) = regs.v[2 * a + 1];
+    } else {
+      const std::uint32_t w[4] = {regs.v[a].x, regs.v[a].y, regs.v[a].z, regs.v[a].w};
       float4 lo;
       float4 hi;
       lo.x = __uint_as_float(w[0] << 16);
@@ -148,8 +152,8 @@ template <bool F32> __device__ __forceinline__ void store_rows(float *dst, int p
       hi.y = __uint_as_float(w[2] & 0xFFFF0000U);
       hi.z = __uint_as_float(w[3] << 16);
       hi.w = __uint_as_float(w[3] & 0xFFFF0000U);
-      *reinterpret_cast<float4 *>(d + 8 * i) = lo;
-      *reinterpret_cast<float4 *>(d + 8 * i + 4) = hi;
+      *reinterpret_cast<float4 *>(d + 32 * a) = lo;
+      *reinterpret_cast<float4 *>(d + 32 * a + 4) = hi;
     }
   }
 }
@@ -390,11 +394,13 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_prepare_kernel(const ChunkPa
       *reinterpret_cast<float2 *>(u + (i + 8) * kPitchU) = make_float2(acc_u[n][2], acc_u[n][3]);
     }
   }
-  // (K diag(e))^T operand image: row = key dim, k = token.  A thread gathers four tokens of one dim from sK.  Last,
+  // (K diag(e))^T operand image: row = key dim, k = token.  A thread gathers four tokens of one dim from sK; a
+  // warp covers 16 dims x 2 token quads, which reads 32 different banks and writes whole 32-byte sectors.  Last,
   // because nothing in this kernel waits for it.
-  for (int i = threadIdx.x; i < kDim * (kChunk / 4); i += 256) {
-    const int d = i / (kChunk / 4);
-    const int j = (i % (kChunk / 4)) * 4;
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int d = 16 * warp + (lane & 15);
+    const int j = 4 * (2 * it + (lane >> 4));
     const float4 e4 = *reinterpret_cast<const float4 *>(sE + j);
     *reinterpret_cast<float4 *>(rec + kRecA3 + image_offset(d, j, kA3Block)) =
         make_float4(__uint_as_float(tf32(sK[j * kPitchRow + d] * e4.x)),
