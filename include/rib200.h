@@ -349,9 +349,10 @@ Rib200Status rib200_shared_free(void *pointer);
 
 /* One decode step driven from host memory (no counterpart in the reference, whose callers hold device
  * buffers): copies the token's rows q | k | v | gate ([16+4+4+16][256] in the activation dtype, back to back,
- * ideally pinned) into device_token (same size), runs rib200_online_attention_decode with them, copies the
- * [16][256] output from device_output to host_output and returns once it is there (it synchronises `stream`).
- * The other arguments are those of rib200_online_attention_decode. */
+ * ideally pinned) into device_token (same size), runs rib200_online_attention_decode with them and returns once
+ * the [16][256] output is in host_output (it synchronises `stream`).  When host_output is page-locked memory the
+ * device can address, the kernel writes it there itself and device_output is left untouched; otherwise the output
+ * goes to device_output and is copied.  The other arguments are those of rib200_online_attention_decode. */
 Rib200Status rib200_online_attention_decode_from_host(const void *host_token, void *host_output, void *device_token,
                                                       void *device_output, void *kv_cache, size_t kv_cache_bytes,
                                                       void *workspace, size_t workspace_bytes,

@@ -478,11 +478,25 @@ Rib200Status rib200_online_attention_decode_from_host(const void *host_token, vo
     // rows in the order q | k | v | gate
     cuda_ok(cudaMemcpyAsync(staged, host_token, 2 * q_bytes + 2 * kv_bytes, cudaMemcpyHostToDevice, cuda_stream),
             "online decode from host: copy in");
+    // Page-locked host memory that the device can address takes the result straight from the kernel (16 heads x 256
+    // values, written once); anything else gets it through device_output and a copy.
+    void *direct = nullptr;
+    cudaPointerAttributes attributes{};
+    if (cudaPointerGetAttributes(&attributes, host_output) == cudaSuccess) {
+      if (attributes.type == cudaMemoryTypeHost && attributes.devicePointer != nullptr &&
+          reinterpret_cast<std::uintptr_t>(attributes.devicePointer) % 16 == 0) {
+        direct = attributes.devicePointer;
+      }
+    } else {
+      (void)cudaGetLastError(); // an unregistered pointer is not an error here
+    }
     online_decode(staged, staged + q_bytes, staged + q_bytes + kv_bytes, staged + q_bytes + 2 * kv_bytes,
-                  device_output, kv_cache, kv_cache_bytes, workspace, workspace_bytes, s, activation_dtype,
-                  cache_dtype, cache_layout, *plan, device_position, cuda_stream);
-    cuda_ok(cudaMemcpyAsync(host_output, device_output, q_bytes, cudaMemcpyDeviceToHost, cuda_stream),
-            "online decode from host: copy out");
+                  direct != nullptr ? direct : device_output, kv_cache, kv_cache_bytes, workspace, workspace_bytes, s,
+                  activation_dtype, cache_dtype, cache_layout, *plan, device_position, cuda_stream);
+    if (direct == nullptr) {
+      cuda_ok(cudaMemcpyAsync(host_output, device_output, q_bytes, cudaMemcpyDeviceToHost, cuda_stream),
+              "online decode from host: copy out");
+    }
     cuda_ok(cudaStreamSynchronize(cuda_stream), "online decode from host: synchronise");
   });
 }

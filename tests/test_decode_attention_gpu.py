@@ -346,6 +346,13 @@ def test_decode_from_host_buffers():
                                      K.KV_BF16, K.HEAD_MAJOR, plan, None, stream)
     torch.cuda.synchronize()
     assert torch.equal(got, ref_out.cpu()) and torch.equal(cache, cache2)
+    # pageable host buffers: the result comes back through device_output and a copy
+    cache3 = cache_to_device(make_cache(k, v, max_ctx, pos))
+    pageable_out = torch.zeros(HQ, D, dtype=torch.bfloat16)
+    K.online_attention_decode_from_host(bf16_tensor(token).cpu(), pageable_out, dev_token, dev_out, cache3,
+                                        cache3.numel() * 2, ws, layout.bytes, shape, K.DTYPE_BF16, K.KV_BF16,
+                                        K.HEAD_MAJOR, plan, None, stream)
+    assert torch.equal(pageable_out, ref_out.cpu()) and torch.equal(dev_out, ref_out) and torch.equal(cache3, cache2)
     with pytest.raises(K.Qwen35PrimitiveError):
         K.online_attention_decode_from_host(None, host_out, dev_token, dev_out, cache, cache.numel() * 2, ws,
                                             layout.bytes, shape, K.DTYPE_BF16, K.KV_BF16, K.HEAD_MAJOR, plan, None,
