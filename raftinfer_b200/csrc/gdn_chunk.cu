@@ -458,6 +458,7 @@ static_assert(kUStage >= kUBytes && kSmA23 % 1024 == 0 && kSmB1 % 1024 == 0 && k
 static_assert(kApplySmemBytes <= 232448, "apply kernel exceeds the shared memory of an SM");
 constexpr long long kWaitLimitCycles = 1LL << 28;
 constexpr std::uint32_t kTmemColumns = 128; // X at 0, O2 at 32, SD at 64
+constexpr std::uint32_t kPrefetchAhead = 3;   // chunks between an L2 prefetch and the copy that uses it
 constexpr std::uint32_t kCopyPiece = 16384;  // the operand images come in as several bulk copies in flight at once
 
 __device__ __forceinline__ std::uint32_t smem_address(const void *p) {
@@ -655,6 +656,14 @@ __global__ void __launch_bounds__(kApplyThreads, 1)
         const unsigned char *rec =
             p.workspace + (static_cast<std::size_t>(chunk) * p.value_heads + head) * kRecBytes;
         const std::uint32_t s = chunk & 1U;
+        if (slice == (chunk & 3U) && chunk + kPrefetchAhead < p.chunks) {
+          // Pull a later chunk's images into L2 (the four slices of a head take turns): the copies below then hit L2.
+          const unsigned char *ahead = rec + static_cast<std::size_t>(kPrefetchAhead) * p.value_heads * kRecBytes;
+#pragma unroll
+          for (std::uint32_t part = 0; part < kRecU; part += kCopyPiece) {
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(ahead + part), "r"(kCopyPiece) : "memory");
+          }
+        }
         if (chunk >= 2) {
           wait(bar(kBarA1Empty + s), ((chunk >> 1) - 1) & 1U);
         }
