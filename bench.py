@@ -296,7 +296,7 @@ def main():
     if ctx == CONTEXT:
         # dram__bytes_read.sum + dram__bytes_write.sum of one partition-kernel launch at this context
         # (ncu capture summarised in profiles/decode_partition_ctx32768.md)
-        line["roofline"]["traffic"] = 138.3e6
+        line["roofline"]["traffic"] = 137.9e6
 
     if rank == 0 and world == 1:
         threads = max(1, len(os.sched_getaffinity(0)))
