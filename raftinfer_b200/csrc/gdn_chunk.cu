@@ -307,45 +307,39 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_prepare_kernel(const ChunkPa
     RIB200_GDN_STAMP(127, 3);
   }
 
-  // V replaces Q; T = (I + A)^-1 by forward substitution in FP32.  Column c belongs to four neighbouring lanes
-  // that split the sum over j in groups of four (lane `part` holds T[16 q + 4 part + r][c] in mine[4 q + r], and
-  // reads its four A_ij with one 16-byte load) and add their parts with two shuffles.
+  // V replaces Q; T = (I + A)^-1 by forward substitution in FP32.
   const RowRegs<F32> v_regs = fetch_rows<F32>(p.v, p.v_stride, head, tok0, p.tokens); // lands during the substitution
   if (threadIdx.x == 0 && blockIdx.x == 0) {
     RIB200_GDN_STAMP(127, 4);
   }
-  {
-    const int c = threadIdx.x >> 2;
-    const int part = threadIdx.x & 3;
-    float mine[kChunk / 4];
+  if (threadIdx.x < kChunk) {
+    // Two warps, a column of T per thread, all of it in registers: row i costs i multiply-adds in four
+    // independent chains and no exchange between lanes; only the term with T[i-1] waits for the row before.
+    const int c = threadIdx.x;
+    float tcol[kChunk];
 #pragma unroll
-    for (int m = 0; m < kChunk / 4; ++m) {
-      mine[m] = 0.0F;
+    for (int i = 0; i < kChunk; ++i) {
+      tcol[i] = 0.0F;
     }
 #pragma unroll
     for (int i = 0; i < kChunk; ++i) {
       float acc0 = 0.0F;
       float acc1 = 0.0F;
+      float acc2 = 0.0F;
+      float acc3 = 0.0F;
 #pragma unroll
-      for (int q = 0; 16 * q < i; ++q) { // A is zero on and above the diagonal, entries not yet known are zero
-        const float4 a = *reinterpret_cast<const float4 *>(sA + i * kPitchSq + 16 * q + 4 * part);
-        acc0 -= a.x * mine[4 * q];
-        acc1 -= a.y * mine[4 * q + 1];
-        acc0 -= a.z * mine[4 * q + 2];
-        acc1 -= a.w * mine[4 * q + 3];
+      for (int j = 0; j < i; j += 4) { // A is zero on and above the diagonal, entries not yet known are zero
+        const float4 a = *reinterpret_cast<const float4 *>(sA + i * kPitchSq + j);
+        acc0 -= a.x * tcol[j];
+        acc1 -= a.y * tcol[j + 1];
+        acc2 -= a.z * tcol[j + 2];
+        acc3 -= a.w * tcol[j + 3];
       }
-      float acc = acc0 + acc1;
-      acc += __shfl_xor_sync(0xFFFFFFFFU, acc, 1);
-      acc += __shfl_xor_sync(0xFFFFFFFFU, acc, 2);
-      const float value = (i == c ? 1.0F : 0.0F) + acc;
-      if (part == ((i >> 2) & 3)) {
-        mine[4 * (i >> 4) + (i & 3)] = value;
-      }
+      tcol[i] = (i == c ? 1.0F : 0.0F) + ((acc0 + acc1) + (acc2 + acc3));
     }
-    // stores after the loop: none of the loads above has to wait for one
 #pragma unroll
-    for (int m = 0; m < kChunk / 4; ++m) {
-      sT[(16 * (m >> 2) + 4 * part + (m & 3)) * kPitchSq + c] = mine[m];
+    for (int i = 0; i < kChunk; ++i) {
+      sT[i * kPitchSq + c] = tcol[i];
     }
   }
   store_rows<F32>(sX, kPitchCol, v_regs);
