@@ -341,8 +341,25 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_prepare_kernel(const ChunkPa
     for (int i = 0; i < kChunk; ++i) {
       sT[i * kPitchSq + c] = tcol[i];
     }
+  } else {
+    // The other six warps meanwhile: their share of V, and the (K diag(e))^T operand image (row = key dim,
+    // k = token).  A thread gathers four tokens of one dim from sK; a warp covers 16 dims x 2 token quads per item,
+    // which reads 32 different banks and writes whole 32-byte sectors.
+    store_rows<F32>(sX, kPitchCol, v_regs);
+    for (int item = warp - 2; item < 64; item += 6) {
+      const int d = 16 * (item & 7) + (lane & 15);
+      const int j = 4 * (2 * (item >> 3) + (lane >> 4));
+      const float4 e4 = *reinterpret_cast<const float4 *>(sE + j);
+      *reinterpret_cast<float4 *>(rec + kRecA3 + image_offset(d, j, kA3Block)) =
+          make_float4(__uint_as_float(tf32(sK[j * kPitchRow + d] * e4.x)),
+                      __uint_as_float(tf32(sK[(j + 1) * kPitchRow + d] * e4.y)),
+                      __uint_as_float(tf32(sK[(j + 2) * kPitchRow + d] * e4.z)),
+                      __uint_as_float(tf32(sK[(j + 3) * kPitchRow + d] * e4.w)));
+    }
   }
-  store_rows<F32>(sX, kPitchCol, v_regs);
+  if (threadIdx.x < kChunk) {
+    store_rows<F32>(sX, kPitchCol, v_regs);
+  }
   __syncthreads();
   if (threadIdx.x == 0 && blockIdx.x == 0) {
     RIB200_GDN_STAMP(127, 5);
@@ -387,20 +404,6 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_prepare_kernel(const ChunkPa
       *reinterpret_cast<float2 *>(u + i * kPitchU) = make_float2(acc_u[n][0], acc_u[n][1]);
       *reinterpret_cast<float2 *>(u + (i + 8) * kPitchU) = make_float2(acc_u[n][2], acc_u[n][3]);
     }
-  }
-  // (K diag(e))^T operand image: row = key dim, k = token.  A thread gathers four tokens of one dim from sK; a
-  // warp covers 16 dims x 2 token quads, which reads 32 different banks and writes whole 32-byte sectors.  Last,
-  // because nothing in this kernel waits for it.
-#pragma unroll
-  for (int it = 0; it < 8; ++it) {
-    const int d = 16 * warp + (lane & 15);
-    const int j = 4 * (2 * it + (lane >> 4));
-    const float4 e4 = *reinterpret_cast<const float4 *>(sE + j);
-    *reinterpret_cast<float4 *>(rec + kRecA3 + image_offset(d, j, kA3Block)) =
-        make_float4(__uint_as_float(tf32(sK[j * kPitchRow + d] * e4.x)),
-                    __uint_as_float(tf32(sK[(j + 1) * kPitchRow + d] * e4.y)),
-                    __uint_as_float(tf32(sK[(j + 2) * kPitchRow + d] * e4.z)),
-                    __uint_as_float(tf32(sK[(j + 3) * kPitchRow + d] * e4.w)));
   }
   if (threadIdx.x == 0 && blockIdx.x == 0) {
     RIB200_GDN_STAMP(127, 6);
