@@ -294,7 +294,7 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_prepare_kernel(const ChunkPa
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const int j = j0 + e;
-          const float decay = j <= i ? expf(sG[i] - sG[j]) : 0.0F;
+          const float decay = j <= i ? __expf(sG[i] - sG[j]) : 0.0F;
           sA[i * kPitchSq + j] = j < i ? sBeta[i] * decay * acc_k[n][2 * half + e] : 0.0F;
           pv[e] = __uint_as_float(tf32(decay * acc_q[n][2 * half + e]));
         }
@@ -341,6 +341,9 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_prepare_kernel(const ChunkPa
     for (int i = 0; i < kChunk; ++i) {
       sT[i * kPitchSq + c] = tcol[i];
     }
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+      RIB200_GDN_STAMP(127, 7);
+    }
   } else {
     // The other six warps meanwhile: their share of V, and the (K diag(e))^T operand image (row = key dim,
     // k = token).  A thread gathers four tokens of one dim from sK; a warp covers 16 dims x 2 token quads per item,
@@ -355,6 +358,9 @@ __global__ void __launch_bounds__(256, 2) gdn_chunk_prepare_kernel(const ChunkPa
                       __uint_as_float(tf32(sK[(j + 1) * kPitchRow + d] * e4.y)),
                       __uint_as_float(tf32(sK[(j + 2) * kPitchRow + d] * e4.z)),
                       __uint_as_float(tf32(sK[(j + 3) * kPitchRow + d] * e4.w)));
+    }
+    if (threadIdx.x == 64 && blockIdx.x == 0) {
+      RIB200_GDN_STAMP(127, 8);
     }
   }
   if (threadIdx.x < kChunk) {
