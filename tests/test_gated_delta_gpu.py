@@ -68,6 +68,41 @@ def test_chunked_core_matches_the_sequential_recurrence(tokens, dtype):
     assert m_state["nonfinite"] == 0 and m_state["rel_l2"] <= 1.0e-3, m_state
 
 
+@pytest.mark.parametrize("hk,hv", [(16, 32), (4, 8)])
+def test_chunked_core_long_run_equals_the_same_run_in_pieces(hk, hv):
+    """A run of 9 297 tokens (146 chunks, ragged tail) in one call and the same tokens in three calls that split on
+    chunk boundaries walk the same chunks with the same arithmetic: outputs and final state are bit-identical.  It
+    also takes the barrier phases and the staging rings of the chunk kernels well past their first wrap-arounds."""
+    tokens, cuts = 9297, (0, 4096, 4096 + 64, 9297)
+    gen = torch.Generator(device=dev()).manual_seed(0xB2001500 + hv)
+    unit = lambda x: x / x.norm(dim=-1, keepdim=True)
+    q = (unit(torch.randn(tokens, hk, DK, device=dev(), generator=gen)) / DK ** 0.5).to(torch.bfloat16)
+    k = unit(torch.randn(tokens, hk, DK, device=dev(), generator=gen)).to(torch.bfloat16)
+    v = torch.randn(tokens, hv, DK, device=dev(), generator=gen).to(torch.bfloat16)
+    beta = torch.sigmoid(torch.randn(tokens, hv, device=dev(), generator=gen))
+    g = -torch.nn.functional.softplus(torch.randn(tokens, hv, device=dev(), generator=gen))
+    state0 = 0.05 * torch.randn(hv, DK, DK, device=dev(), generator=gen)
+    stream = torch.cuda.current_stream()
+
+    def run(pieces):
+        state = state0.clone()
+        out = torch.zeros(tokens, hv, DK, device=dev())
+        for lo, hi in pieces:
+            n = hi - lo
+            ws_bytes = K.gdn_core_workspace_bytes(n, hk, hv, DK, DK)
+            ws = torch.zeros(max(ws_bytes // 4, 4), device=dev())
+            K.gdn_core(q[lo:hi], k[lo:hi], v[lo:hi], beta[lo:hi], g[lo:hi], state, out[lo:hi], ws, ws_bytes, n, hk, hv,
+                       DK, DK, K.DTYPE_BF16, stream)
+        torch.cuda.synchronize()
+        return out, state
+
+    whole_out, whole_state = run([(0, tokens)])
+    parts_out, parts_state = run(list(zip(cuts[:-1], cuts[1:])))
+    assert K.device_status(stream) == 0
+    assert torch.isfinite(whole_out).all() and torch.isfinite(whole_state).all()
+    assert torch.equal(whole_out, parts_out) and torch.equal(whole_state, parts_state)
+
+
 def test_chunked_prefill_4096_then_128_decode_steps():
     """The benchmark's gated-delta configuration: zero state, 4096-token chunked prefill, then 128 recurrent steps."""
     tokens, steps, seed = 4096, 128, 0xB2001400
