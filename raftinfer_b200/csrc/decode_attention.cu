@@ -152,12 +152,22 @@ __device__ __forceinline__ bool mbarrier_try_wait(std::uint32_t bar, std::uint32
   return done != 0;
 }
 
+// L2 policy for the cache rows: a step reads each of them once, so they are the first to go.  What the step
+// writes and reads again (the split-k partials) then stays in L2 between the two kernels.
+__device__ __forceinline__ std::uint64_t evict_first_policy() {
+  std::uint64_t policy;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;\n" : "=l"(policy));
+  return policy;
+}
+
 // TMA bulk copy global -> shared, completion bytes counted on `bar`
 __device__ __forceinline__ void bulk_copy_g2s(std::uint32_t dst, const void *src, std::uint32_t bytes,
-                                              std::uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
-               "l"(src), "r"(bytes), "r"(bar)
-               : "memory");
+                                              std::uint32_t bar, std::uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;\n" ::"r"(
+          dst),
+      "l"(src), "r"(bytes), "r"(bar), "l"(policy)
+      : "memory");
 }
 
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
@@ -337,6 +347,7 @@ __global__ void __launch_bounds__(T::kWarps * 32, T::kCtasPerSm) decode_partitio
   }
   __syncwarp();
 
+  const std::uint64_t stream_policy = evict_first_policy();
   // Producer (lane 0): slot n goes to ring position n % kRingSlots.  Only the live rows of the step are
   // copied; the consumer zero-fills the rest and patches in the row that is being appended.
   auto issue = [&](std::uint32_t n) {
@@ -355,7 +366,7 @@ __global__ void __launch_bounds__(T::kWarps * 32, T::kCtasPerSm) decode_partitio
     for (int pair = 0; pair < kStepTokens / 2; ++pair) {
       if (static_cast<std::uint32_t>(2 * pair) < rows) {
         const std::uint32_t live = min(2U, rows - 2 * pair);
-        bulk_copy_g2s(slot + pair * kPairPitch, src + 2 * pair * kHeadDim, live * kRowBytes, bar);
+        bulk_copy_g2s(slot + pair * kPairPitch, src + 2 * pair * kHeadDim, live * kRowBytes, bar, stream_policy);
       }
     }
   };
