@@ -714,22 +714,40 @@ __global__ void __launch_bounds__(256) decode_combine_kernel(const DecodeParams 
   float run_max = -INFINITY;
   float run_sum = 0.0F;
   float4 acc = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
-#pragma unroll 8
-  for (std::uint32_t i = group; i < parts; i += 16) {
-    const float part_max = pmax[i];
-    const float part_sum = psum[i];
-    const float4 v =
-        *reinterpret_cast<const float4 *>(pval + static_cast<std::size_t>(i) * kHeadDim + quarter * 64 + sub * 4);
-    const float new_max = fmaxf(run_max, part_max);
-    const float keep = exp2f((run_max - new_max) * kLog2e);
-    const float take = exp2f((part_max - new_max) * kLog2e);
-    run_sum = run_sum * keep + part_sum * take;
-    acc.x = acc.x * keep + v.x * take;
-    acc.y = acc.y * keep + v.y * take;
-    acc.z = acc.z * keep + v.z * take;
-    acc.w = acc.w * keep + v.w * take;
-    run_max = new_max;
+  // Eight partials at a time: first all their loads (so that they are in flight together, one round trip to L2 for
+  // a 32K context), then the folding.
+  constexpr int kBatch = 8;
+  for (std::uint32_t first = group; first < parts; first += 16 * kBatch) {
+    float part_max[kBatch];
+    float part_sum[kBatch];
+    float4 part_value[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const std::uint32_t i = first + 16 * j;
+      if (i < parts) {
+        part_max[j] = pmax[i];
+        part_sum[j] = psum[i];
+        part_value[j] =
+            *reinterpret_cast<const float4 *>(pval + static_cast<std::size_t>(i) * kHeadDim + quarter * 64 + sub * 4);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      if (first + 16 * j < parts) {
+        const float4 v = part_value[j];
+        const float new_max = fmaxf(run_max, part_max[j]);
+        const float keep = exp2f((run_max - new_max) * kLog2e);
+        const float take = exp2f((part_max[j] - new_max) * kLog2e);
+        run_sum = run_sum * keep + part_sum[j] * take;
+        acc.x = acc.x * keep + v.x * take;
+        acc.y = acc.y * keep + v.y * take;
+        acc.z = acc.z * keep + v.z * take;
+        acc.w = acc.w * keep + v.w * take;
+        run_max = new_max;
+      }
+    }
   }
+  RIB200_DECODE_STAMP(g_combine_trace, trace_cta, 3);
   if (sub == 0) {
     group_max[group] = run_max;
     group_sum[group] = run_sum;
