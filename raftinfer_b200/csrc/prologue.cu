@@ -72,6 +72,20 @@ template <> struct Elements<float> {
 };
 template <> struct Elements<__nv_bfloat16> {
   template <int N> static __device__ __forceinline__ void load(const void *base, std::size_t index, float (&x)[N]) {
+    if constexpr (N % 8 == 0) { // eight elements per 16-byte access
+      const uint4 *src = reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(base) + index);
+#pragma unroll
+      for (int i = 0; i < N / 8; ++i) {
+        const uint4 v = src[i];
+        const std::uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+          x[8 * i + 2 * h] = __uint_as_float(w[h] << 16);
+          x[8 * i + 2 * h + 1] = __uint_as_float(w[h] & 0xFFFF0000U);
+        }
+      }
+      return;
+    }
     const uint2 *src = reinterpret_cast<const uint2 *>(static_cast<const __nv_bfloat16 *>(base) + index);
 #pragma unroll
     for (int i = 0; i < N / 4; ++i) {
@@ -83,6 +97,20 @@ template <> struct Elements<__nv_bfloat16> {
     }
   }
   template <int N> static __device__ __forceinline__ void store(void *base, std::size_t index, const float (&x)[N]) {
+    if constexpr (N % 8 == 0) {
+      uint4 *wide = reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(base) + index);
+#pragma unroll
+      for (int i = 0; i < N / 8; ++i) {
+        std::uint32_t w[4];
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+          const __nv_bfloat162 pair = __floats2bfloat162_rn(x[8 * i + 2 * h], x[8 * i + 2 * h + 1]);
+          w[h] = *reinterpret_cast<const std::uint32_t *>(&pair);
+        }
+        wide[i] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+      return;
+    }
     uint2 *dst = reinterpret_cast<uint2 *>(static_cast<__nv_bfloat16 *>(base) + index);
 #pragma unroll
     for (int i = 0; i < N / 4; ++i) {
