@@ -349,6 +349,12 @@ __device__ __forceinline__ void umma_commit_pair(std::uint32_t cluster_bar) {
                : "memory");
 }
 
+// 32-byte global load (sm_100) into two 16-byte halves
+__device__ __forceinline__ void ld_global_v8(const void *src, uint4 &lo, uint4 &hi) {
+  asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];\n"
+               : "=r"(lo.x), "=r"(lo.y), "=r"(lo.z), "=r"(lo.w), "=r"(hi.x), "=r"(hi.y), "=r"(hi.z), "=r"(hi.w)
+               : "l"(src));
+}
 // 32-byte global store (sm_100): one instruction per sector instead of two
 __device__ __forceinline__ void st_global_v8(void *dst, const std::uint32_t (&w)[8]) {
   asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};\n" ::"l"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]),
@@ -1168,8 +1174,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (live) {
           const uint4 *gp = reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.gate) + out_base);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            gate_raw[i] = gp[i];
+          for (int i = 0; i < 16; i += 2) {
+            ld_global_v8(gp + i, gate_raw[i], gate_raw[i + 1]);
           }
         }
       }
@@ -1270,8 +1276,8 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (live) {
           const float4 *gsrc = reinterpret_cast<const float4 *>(static_cast<const float *>(p.gate) + out_base);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            gate_now[i] = gsrc[i];
+          for (int i = 0; i < 8; i += 2) {
+            ld_global_v8(gsrc + i, *reinterpret_cast<uint4 *>(&gate_now[i]), *reinterpret_cast<uint4 *>(&gate_now[i + 1]));
           }
         }
       }
@@ -1285,8 +1291,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             const float4 *gsrc =
                 reinterpret_cast<const float4 *>(static_cast<const float *>(p.gate) + out_base + (c + 1) * 32);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              gate_next[i] = gsrc[i];
+            for (int i = 0; i < 8; i += 2) {
+              ld_global_v8(gsrc + i, *reinterpret_cast<uint4 *>(&gate_next[i]),
+                           *reinterpret_cast<uint4 *>(&gate_next[i + 1]));
             }
           }
         }
