@@ -99,6 +99,25 @@ class ClockSampler:
                 "sm_max_mhz": max(maxima) if maxima else None, "reasons": sorted(reasons), "samples": len(clocks)}
 
 
+def workload_config(context: int, cache_bytes: int):
+    """The `config` object of the JSON line: the same for the GPU arm and for the CPU reference arm."""
+    return {"workload": f"split-k decode attention, batch 1 per GPU, context {context}, 16q/4kv heads, head_dim 256, "
+                        "BF16 head-major KV, partition 256",
+            "l2": f"{ROTATION} KV caches of {cache_bytes / 1e6:.0f} MB visited round-robin (working set > L2)",
+            "sharding": "one sequence per GPU, no collective"}
+
+
+def profiled_traffic(context: int):
+    """DRAM bytes (read + written) of one decode launch at `context`, from the ncu capture recorded beside its
+    summary; None when no capture of that context is on record."""
+    path = os.path.join(ROOT, "profiles", f"decode_partition_ctx{context}.json")
+    try:
+        record = json.load(open(path))
+        return float(record["dram_bytes_read"]) + float(record["dram_bytes_write"])
+    except (OSError, KeyError, ValueError):
+        return None
+
+
 def cpu_decode_baseline(context: int, repeats: int, threads: int):
     """Times the oracle's attention core (decode row over a BF16 head-major cache) on the host cores."""
     import numpy as np
@@ -138,9 +157,9 @@ def run_reference_arm(args):
         "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup,
         "ms_per_step": algorithmic_bytes(CONTEXT) / gbs / 1e6, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f64 dot / f32 accumulate (CPU)", "data": "synthetic",
-        "config": {"workload": f"split-k decode attention, batch 1 per GPU, context {CONTEXT}, 16q/4kv heads, "
-                               "head_dim 256, BF16 head-major KV, partition 256",
-                   "arithmetic": "CPU reference arithmetic (one pass over the context, no split) on the host cores"},
+        "config": workload_config(CONTEXT, 2 * HKV * CONTEXT * D * 2),
+        "arithmetic": "CPU reference arithmetic (one pass over the context, no split) on the host cores; the cache "
+                      "rotation and the sharding named in config describe the GPU arm's run of the same workload",
         "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "wall_seconds": total,
@@ -230,6 +249,17 @@ def main():
     stop.record(stream)
     barrier()
     device_ms = max_over_ranks(start.elapsed_time(stop))
+    # the same K steps five more times: the spread of the figure from block to block
+    block_ms = []
+    for _ in range(5):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for i in range(steps):
+            step(i)
+        b.record(stream)
+        torch.cuda.synchronize()
+        block_ms.append(a.elapsed_time(b) / steps)
+    block_cv = statistics.pstdev(block_ms) / statistics.mean(block_ms)
     # keep the GPU under the same load a little longer so the clock sampler sees it
     t_end = time.time() + 0.6
     i = 0
@@ -279,10 +309,8 @@ def main():
         "metric": "split-k decode attention HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps,
         "warmup": warmup, "ms_per_step": device_ms / steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16 operands, f32 softmax/accumulate", "data": "synthetic",
-        "config": {"workload": f"split-k decode attention, batch 1 per GPU, context {ctx}, 16q/4kv heads, head_dim 256, "
-                               "BF16 head-major KV, partition 256",
-                   "l2": f"{ROTATION} KV caches of {cache_bytes / 1e6:.0f} MB visited round-robin (working set > L2)",
-                   "sharding": "one sequence per GPU, no collective"},
+        "config": workload_config(ctx, cache_bytes),
+        "cv": block_cv, "block_ms_per_step": [round(ms, 6) for ms in block_ms],
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": sum(t.numel() * 2 for t in host_in),
                 "d2h_bytes_per_step": host_out.numel() * 2, "ms_per_step": e2e_ms / e2e_steps},
         "gpu_launches": 2 * steps,
@@ -293,17 +321,20 @@ def main():
                              "programmatic dependent launch); the partition kernel moves all the algorithmic bytes"},
         "clocks": clocks,
     }
-    if ctx == CONTEXT:
-        # dram__bytes_read.sum + dram__bytes_write.sum of one partition-kernel launch at this context
-        # (ncu capture summarised in profiles/decode_partition_ctx32768.md)
-        line["roofline"]["traffic"] = 137.9e6
+    line["roofline"]["traffic"] = profiled_traffic(ctx)
 
     if rank == 0 and world == 1:
         threads = max(1, len(os.sched_getaffinity(0)))
         gbs, seconds = cpu_decode_baseline(ctx, 3, threads)
+        gbs1, seconds1 = cpu_decode_baseline(ctx, 3, 1)
         line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
                                 "sample": f"3 full decode rows at context {ctx} (median {seconds * 1e3:.0f} ms each), "
-                                          "oracle restatement of cpp/reference/qwen35.cpp:316-370 over the BF16 cache"}
+                                          "oracle restatement of cpp/reference/qwen35.cpp:316-370 over the BF16 cache; "
+                                          "the threads are this harness's loop over query heads, the reference's "
+                                          "own code is single-threaded",
+                                "single_thread": {"value": gbs1, "unit": "GB/s", "cores": 1,
+                                                  "sample": f"the same 3 rows on one thread (median "
+                                                            f"{seconds1 * 1e3:.0f} ms each)"}}
         if args.extras:
             from raftinfer_b200 import benchmarks
 
@@ -313,6 +344,13 @@ def main():
 
         extra = benchmarks.run_distributed(dev, stream, hbm_peak, tensor_peak, rank, world, dist)
         line["extra"] = extra
+    if "extra" in line:
+        # last in the line, so that a reader of its tail finds every kernel's figure: name -> [ms, fraction of the
+        # measured roofline (HBM copy bandwidth or BF16 tensor peak, whichever bounds that kernel)]
+        from raftinfer_b200 import benchmarks
+
+        line["summary"] = benchmarks.summarize(line["extra"])
+        line["summary"]["decode_ctx%d" % ctx] = [round(device_ms / steps, 5), round(per_gpu_gbs / hbm_peak, 4)]
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -340,6 +340,16 @@ Rib200Status rib200_online_attention_prefill_scatter(const void *query, const vo
  * buffer.  epoch must grow from call to call.  A wait that runs out sets RIB200_DEVICE_WAIT_TIMED_OUT. */
 Rib200Status rib200_peer_rendezvous(uint32_t *const *flags, size_t world, size_t rank, uint32_t epoch,
                                     void *stream);
+/* The same rendezvous with the caller's bound on the wait, in SM clock cycles (rib200_peer_rendezvous waits for
+ * 2^31, about a second).  For callers that would rather learn of a missing peer after milliseconds, and for the
+ * test that makes the wait run out: the kernel then sets RIB200_DEVICE_WAIT_TIMED_OUT and returns, and the CUDA
+ * context stays usable.
+ * The rendezvous only says that the peers' tiles of THIS step have arrived.  A peer that has passed it may start
+ * its next step and store into this rank's buffer while this rank's readers of the current step are still
+ * running, so a buffer may be rewritten only after every rank has consumed it: put a second rendezvous (a new
+ * epoch) behind the consumers, or alternate between two buffers. */
+Rib200Status rib200_peer_rendezvous_bounded(uint32_t *const *flags, size_t world, size_t rank, uint32_t epoch,
+                                            uint64_t limit_cycles, void *stream);
 /* Device memory that other processes on the box can map: allocation (zero-filled) with its 64-byte
  * handle, mapping of a peer's handle, and their releases. */
 Rib200Status rib200_shared_alloc(size_t bytes, void **pointer, uint8_t handle[64]);
@@ -361,18 +371,24 @@ Rib200Status rib200_online_attention_decode_from_host(const void *host_token, vo
                                                       const Rib200OnlineDecodePlan *plan,
                                                       const uint32_t *device_position, void *stream);
 
-/* Opt-in for rib200_online_attention_decode with a host position (no counterpart in the reference).  A decode
- * step reads cache rows [0, past_tokens) that earlier calls wrote and four token rows the kernel in front of it
- * produced.  With the option on, the partition kernel starts fetching the cache rows as soon as it is resident --
- * under programmatic dependent launch that can be while the kernels in front of it are still running -- and waits
- * for them only before it touches the token's rows and before it writes anything.  The caller promises in return
- * that whatever wrote rows [0, past_tokens) of that KV cache has completed, or is separated from the step by at
- * least one ordinary kernel launch on the stream (a kernel that does not release its dependents early; the two
- * kernels of a decode step of this library do release them early).  True for the reference's executor, where the
- * previous writer of a layer's cache is the previous token's step, a whole model pass earlier; false for two
- * steps enqueued directly one after the other on the same cache with advancing positions.  Off by default;
- * process-wide; calls with a device position or a batch ignore it.  enabled: 0 or 1. */
-Rib200Status rib200_set_decode_early_kv_fetch(int32_t enabled);
+/* rib200_online_attention_decode with the early cache fetch (no counterpart in the reference); host position
+ * only.  A decode step reads cache rows [0, past_tokens) that earlier calls wrote and four token rows the kernel
+ * in front of it produced.  Through this entry point the kernel starts fetching the cache rows as soon as it is
+ * resident -- under programmatic dependent launch that can be while the kernel in front of it is still running --
+ * and waits for that kernel only before it touches the token's rows, before it writes anything and before it lets
+ * the kernel behind it become resident.  The caller promises in return that whatever wrote rows [0, past_tokens)
+ * of that KV cache has completed, or is separated from this step by at least one ordinary kernel launch on the
+ * stream (a kernel that does not release its dependents early; the decode kernels of this library do release them
+ * early).  True for the reference's executor, where the previous writer of a layer's cache is the previous
+ * token's step, a whole model pass earlier; false for two steps enqueued directly one after the other on the same
+ * cache with advancing positions.  The choice is per call: nothing is remembered between calls. */
+Rib200Status rib200_online_attention_decode_early_kv_fetch(const void *query, const void *key, const void *value,
+                                                           const void *gate, void *output, void *kv_cache,
+                                                           size_t kv_cache_bytes, void *workspace,
+                                                           size_t workspace_bytes, const Rib200AttentionShape *shape,
+                                                           int32_t activation_dtype, uint8_t cache_dtype,
+                                                           uint8_t cache_layout, const Rib200OnlineDecodePlan *plan,
+                                                           void *stream);
 
 /* Reads and clears the status word the kernels of this library set on the current device.  It
  * synchronises `stream` first, so it is not for use inside a graph capture. */

@@ -90,6 +90,7 @@ PROTOTYPES = {
     "rib200_online_attention_prefill_scatter": [vp, vp, vp, vp, C.POINTER(vp), sz, sz, sz, sz, vp, sz,
                                                 C.POINTER(AttentionShape), C.c_int32, C.c_uint8, C.c_uint8, vp],
     "rib200_peer_rendezvous": [C.POINTER(vp), sz, sz, C.c_uint32, vp],
+    "rib200_peer_rendezvous_bounded": [C.POINTER(vp), sz, sz, C.c_uint32, C.c_uint64, vp],
     "rib200_qk_norm_rope": [vp, vp, vp, C.POINTER(QkNormRopeShape), C.c_float, C.c_int32, C.c_int32, vp, vp],
     "rib200_split_full_query_gate": [vp, vp, vp, sz, sz, sz, C.c_int32, vp],
     "rib200_attention_prologue": [vp, vp, vp, vp, vp, vp, vp, vp, vp, C.POINTER(AttentionShape), sz, C.c_float,
@@ -107,7 +108,9 @@ PROTOTYPES = {
     "rib200_batched_gdn_decode": [vp, vp, vp, vp, vp, vp, vp, sz, sz, sz, vp],
     "rib200_online_attention_decode_static_scratch": [vp, vp, vp, vp, vp, vp, sz, C.POINTER(AttentionShape), C.c_int32,
                                                       vp, vp],
-    "rib200_set_decode_early_kv_fetch": [C.c_int32],
+    "rib200_online_attention_decode_early_kv_fetch": [vp, vp, vp, vp, vp, vp, sz, vp, sz, C.POINTER(AttentionShape),
+                                                      C.c_int32, C.c_uint8, C.c_uint8,
+                                                      C.POINTER(OnlineDecodePlan), vp],
     "rib200_paged_decode_attention": [vp, vp, vp, vp, vp, vp, sz, vp, sz, vp, sz, vp, sz, vp],
     "rib200_device_status": [vp, C.POINTER(C.c_uint32)],
 }

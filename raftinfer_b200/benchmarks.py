@@ -55,8 +55,8 @@ def _bf16(gen, dev, *shape):
 
 def decode_contexts(dev, stream, hbm_peak, contexts=(4096, 131072), early_kv_fetch_contexts=(32768,)):
     """Single-sequence decode steps on caches visited round-robin.  For `early_kv_fetch_contexts` the same loop is
-    also timed with rib200_set_decode_early_kv_fetch on: no step of the loop writes a cache row another one reads,
-    which is what that option asks of the caller."""
+    also timed through rib200_online_attention_decode_early_kv_fetch: no step of the loop writes a cache row another
+    one reads, which is what that entry point asks of the caller."""
     out = {}
     contexts = tuple(contexts) + tuple(c for c in early_kv_fetch_contexts if c not in contexts)
     gen = torch.Generator(device=dev).manual_seed(11)
@@ -81,11 +81,12 @@ def decode_contexts(dev, stream, hbm_peak, contexts=(4096, 131072), early_kv_fet
         out[f"decode_ctx{ctx}"] = {"ms": ms, "cv": cv, "bytes": nbytes, "GB/s": nbytes / ms / 1e6,
                                    "frac_of_measured_hbm": nbytes / ms / 1e6 / hbm_peak, "caches_rotated": rotation}
         if ctx in early_kv_fetch_contexts:
-            K.set_decode_early_kv_fetch(True)
-            try:
-                ms, cv = _median_ms(fn, stream, warmup=5, reps=10, calls=8)
-            finally:
-                K.set_decode_early_kv_fetch(False)
+            def fn_early(i):
+                K.online_attention_decode_early_kv_fetch(q, k, v, gate, o, caches[i % rotation], caches[0].numel() * 2,
+                                                         ws, layout.bytes, shape, K.DTYPE_BF16, K.KV_BF16,
+                                                         K.HEAD_MAJOR, plan, stream)
+
+            ms, cv = _median_ms(fn_early, stream, warmup=5, reps=10, calls=8)
             out[f"decode_ctx{ctx}_early_kv_fetch"] = {"ms": ms, "cv": cv, "bytes": nbytes, "GB/s": nbytes / ms / 1e6,
                                                       "frac_of_measured_hbm": nbytes / ms / 1e6 / hbm_peak}
         del caches
@@ -192,6 +193,56 @@ def gdn_layer(dev, stream, hbm_peak, tensor_peak, tokens=4096, decode_steps=128)
     return res
 
 
+def gdn_packed_layer(dev, stream, hbm_peak, tensor_peak, tokens=4096, decode_steps=128, width=4):
+    """The reference's own entry point, qwen35_gated_delta: packed input [q | k | v | b | a | z] per token in BF16,
+    FP32 weights, causal conv of `width` + SiLU, L2 norm, gates, the recurrence, RMSNorm * SiLU(z).  Prefill over
+    `tokens` (states reset in front of every call), then single-token calls replayed from a graph."""
+    gen = torch.Generator(device=dev).manual_seed(31)
+    hidden = HV * DK
+    conv_dim = 2 * HK * DK + hidden
+    stride = conv_dim + 2 * HV + hidden
+    packed = _bf16(gen, dev, tokens + decode_steps, stride)
+    conv_w = 0.3 * torch.randn(conv_dim, width, device=dev, generator=gen)
+    rec_a = -torch.exp(0.3 * torch.randn(HV, device=dev, generator=gen))
+    dt_bias = 0.5 * torch.randn(HV, device=dev, generator=gen)
+    norm_w = 1.0 + 0.1 * torch.randn(DK, device=dev, generator=gen)
+    conv_state = torch.zeros(conv_dim, width - 1, device=dev)
+    rec_state = torch.zeros(HV, DK, DK, device=dev)
+    out = torch.zeros(tokens + decode_steps, hidden, device=dev, dtype=torch.bfloat16)
+    shape = K.GatedDeltaShape(tokens, hidden, HK, HV, DK, DK, width, 1.0e-6)
+    one = K.GatedDeltaShape(1, hidden, HK, HV, DK, DK, width, 1.0e-6)
+    ws_bytes = K.qwen35_gated_delta_workspace_bytes(shape)
+    ws = torch.zeros(ws_bytes // 4, device=dev)
+    policy, policy_one = K.qwen35_gated_delta_select_policy(shape, tokens), K.qwen35_gated_delta_select_policy(one, 1)
+
+    def prefill(i):
+        rec_state.zero_()
+        conv_state.zero_()
+        K.qwen35_gated_delta(packed, conv_w, rec_a, dt_bias, norm_w, out, conv_state, rec_state, ws, ws_bytes, shape,
+                             K.DTYPE_BF16, K.DTYPE_F32, stream, policy)
+
+    def decode(i):
+        t = tokens + (i % decode_steps)
+        K.qwen35_gated_delta(packed[t], conv_w, rec_a, dt_bias, norm_w, out[t], conv_state, rec_state, ws, ws_bytes,
+                             one, K.DTYPE_BF16, K.DTYPE_F32, stream, policy_one)
+
+    chunk = 64
+    flops = (tokens // chunk) * HV * (2 * chunk * chunk * (3 * DK + 2 * DK) + 6 * chunk * DK * DK)
+    io_bytes = tokens * stride * 2 + tokens * hidden * 2  # the packed input read once, the output written once
+    ms, cv = _median_ms(prefill, stream, warmup=3, reps=10)
+    res = {"prefill": {"tokens": tokens, "ms": ms, "cv": cv, "flops": flops, "TFLOP/s": flops / ms / 1e9,
+                       "frac_of_measured_bf16_peak": flops / ms / 1e9 / tensor_peak, "io_bytes": io_bytes,
+                       "io_GB/s": io_bytes / ms / 1e6,
+                       "note": "whole layer call: prologue (conv, SiLU, norms, gates), chunked recurrence, epilogue; "
+                               "time includes two state memsets"}}
+    ms, cv = _graph_ms(decode, stream, decode_steps, warmup=3, reps=8)
+    nbytes = 2 * HV * DK * DK * 4
+    res["decode_step"] = {"ms": ms, "cv": cv, "bytes": nbytes, "effective GB/s": nbytes / ms / 1e6,
+                          "steps_per_graph": decode_steps,
+                          "note": "single sequence, state L2-resident: latency of the three launches of a layer step"}
+    return res
+
+
 def prefill_attention(dev, stream, tensor_peak, token_counts=(128, 512, 4096)):
     gen = torch.Generator(device=dev).manual_seed(17)
     res = {}
@@ -269,11 +320,38 @@ def attention_prologue(dev, stream, hbm_peak, tokens=4096, rotary=64):
                                 "frac_of_measured_hbm": three_bytes / ms3 / 1e6 / hbm_peak}}
 
 
+def summarize(extra):
+    """{name: [ms, fraction of the measured roofline]} for every timed entry of an `extra` object, flat and short."""
+    flat = {}
+
+    def walk(prefix, node):
+        if not isinstance(node, dict):
+            return
+        ms = node.get("ms", node.get("ms_fused_peer_stores"))
+        if isinstance(ms, float):
+            frac = None
+            for key, value in node.items():
+                if key.startswith("frac_of_") and isinstance(value, float):
+                    frac = value
+                    break
+            flat[prefix] = [round(ms, 5), None if frac is None else round(frac, 4)]
+        for key, value in node.items():
+            walk(f"{prefix}.{key}" if prefix else key, value)
+
+    for section, node in extra.items():
+        short = {"decode_attention": "dec", "batched_serving_decode": "serve", "gated_delta": "gdn", "gated_delta_layer": "gdn_layer",
+                 "prefill_attention": "pre", "attention_prologue": "prol", "sharded_serving_decode": "serve_sharded",
+                 "head_split_prefill": "head_split"}.get(section, section)
+        walk(short, node)
+    return flat
+
+
 def run(dev, stream, hbm_peak, tensor_peak):
     extra = {}
     for name, fn in (("decode_attention", lambda: decode_contexts(dev, stream, hbm_peak)),
                      ("batched_serving_decode", lambda: batched_serving_decode(dev, stream, hbm_peak)),
                      ("gated_delta", lambda: gdn_layer(dev, stream, hbm_peak, tensor_peak)),
+                     ("gated_delta_layer", lambda: gdn_packed_layer(dev, stream, hbm_peak, tensor_peak)),
                      ("prefill_attention", lambda: prefill_attention(dev, stream, tensor_peak)),
                      ("attention_prologue", lambda: attention_prologue(dev, stream, hbm_peak))):
         try:
@@ -284,8 +362,10 @@ def run(dev, stream, hbm_peak, tensor_peak):
     return extra
 
 
-def _timed_max_over_ranks(fn, stream, dist, dev, warmup=3, reps=10):
-    """Median over `reps` of the slowest rank's CUDA-event time for fn(i); a barrier precedes every repetition."""
+def _timed_max_over_ranks(fn, stream, dist, dev, warmup=3, reps=10, calls=1):
+    """Median over `reps` of the slowest rank's CUDA-event time per fn(i) call; a barrier precedes every repetition.
+    calls > 1 puts that many consecutive calls between the two events, so that a step of tens of microseconds is not
+    measured as the host's launch latency (only for steps that need no rank to wait for another)."""
     for i in range(warmup):
         fn(i)
     torch.cuda.synchronize()
@@ -295,10 +375,11 @@ def _timed_max_over_ranks(fn, stream, dist, dev, warmup=3, reps=10):
         torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record(stream)
-        fn(i)
+        for c in range(calls):
+            fn(i * calls + c)
         b.record(stream)
         torch.cuda.synchronize()
-        t = torch.tensor([a.elapsed_time(b)], device=dev, dtype=torch.float64)
+        t = torch.tensor([a.elapsed_time(b) / calls], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         times.append(float(t.item()))
     return statistics.median(times)
@@ -337,7 +418,7 @@ def sharded_serving_decode(dev, stream, hbm_peak, rank, world, dist, batch=64, l
         K.batched_decode_attention(q, k, v, gate, o, ptrs, dcaps, dpos, b, largest, ws, ws_bytes, stream)
         K.batched_gdn_decode(gq, gk, gv, beta, logd, sptrs, go, b, HK, HV, stream)
 
-    ms = _timed_max_over_ranks(step, stream, dist, dev)
+    ms = _timed_max_over_ranks(step, stream, dist, dev, calls=4)
     nbytes = sum(4096 * n + 24576 for n in lengths) + batch * 2 * HV * DK * DK * 4
     return {"sequences": batch, "ranks": world, "context_tokens_per_rank": load, "ms": ms, "bytes": nbytes,
             "GB/s": nbytes / ms / 1e6, "frac_of_measured_hbm_all_ranks": nbytes / ms / 1e6 / (hbm_peak * world),
@@ -417,7 +498,7 @@ def run_distributed(dev, stream, hbm_peak, tensor_peak, rank, world, dist):
 
 
 def main(argv=None):
-    """python -m raftinfer_b200.benchmarks [decode] [serving] [gdn] [prefill] [--tokens N] [--reps R]
+    """python -m raftinfer_b200.benchmarks [decode] [serving] [gdn] [gdnlayer] [prefill] [prologue] [--tokens N]
 
     Prints one JSON object with the requested sections (all when none is named)."""
     import argparse
@@ -440,7 +521,7 @@ def main(argv=None):
     if os.path.exists(peaks_path):
         peaks = json.load(open(peaks_path))
         hbm, tensor = float(peaks["hbm_gbs"]), float(peaks["bf16_tflops"])
-    want = set(args.sections) or {"decode", "serving", "gdn", "prefill", "prologue"}
+    want = set(args.sections) or {"decode", "serving", "gdn", "gdnlayer", "prefill", "prologue"}
     out = {}
     if "decode" in want:
         out["decode_attention"] = decode_contexts(dev, stream, hbm, tuple(args.contexts or (4096, 32768, 131072)))
@@ -448,6 +529,8 @@ def main(argv=None):
         out["batched_serving_decode"] = batched_serving_decode(dev, stream, hbm)
     if "gdn" in want:
         out["gated_delta"] = gdn_layer(dev, stream, hbm, tensor, tokens=args.gdn_tokens)
+    if "gdnlayer" in want:
+        out["gated_delta_layer"] = gdn_packed_layer(dev, stream, hbm, tensor, tokens=args.gdn_tokens)
     if "prefill" in want:
         out["prefill_attention"] = prefill_attention(dev, stream, tensor, tuple(args.tokens or (128, 512, 4096)))
     if "prologue" in want:

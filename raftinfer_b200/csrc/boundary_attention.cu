@@ -267,7 +267,7 @@ void online_decode(const void *query, const void *key, const void *value, const 
                    void *kv_cache, std::size_t kv_cache_bytes, void *workspace, std::size_t workspace_bytes,
                    const Rib200AttentionShape &s, int32_t activation_dtype, std::uint8_t cache_dtype,
                    std::uint8_t cache_layout, const Rib200OnlineDecodePlan &plan,
-                   const std::uint32_t *device_position, cudaStream_t stream) {
+                   const std::uint32_t *device_position, cudaStream_t stream, bool early_kv_fetch = false) {
   require(query != nullptr, "online decode: query pointer is null");
   require(key != nullptr, "online decode: key pointer is null");
   require(value != nullptr, "online decode: value pointer is null");
@@ -325,6 +325,7 @@ void online_decode(const void *query, const void *key, const void *value, const 
   args.threshold_tokens = static_cast<std::uint32_t>(plan.split_k_threshold_tokens);
   args.partition_capacity = static_cast<std::uint32_t>(plan.active_partition_capacity);
   args.activations_f32 = activation_dtype == RIB200_DTYPE_F32;
+  args.early_kv_fetch = early_kv_fetch;
   if (layout.bytes != 0) {
     auto *base = static_cast<unsigned char *>(workspace);
     args.partial_max = reinterpret_cast<float *>(base + layout.max_offset_bytes);
@@ -449,6 +450,21 @@ Rib200Status rib200_online_attention_decode(const void *query, const void *key, 
     online_decode(query, key, value, gate, output, kv_cache, kv_cache_bytes, workspace, workspace_bytes,
                   deref(shape), activation_dtype, cache_dtype, cache_layout, *plan, device_position,
                   static_cast<cudaStream_t>(stream));
+  });
+}
+
+Rib200Status rib200_online_attention_decode_early_kv_fetch(const void *query, const void *key, const void *value,
+                                                           const void *gate, void *output, void *kv_cache,
+                                                           size_t kv_cache_bytes, void *workspace,
+                                                           size_t workspace_bytes, const Rib200AttentionShape *shape,
+                                                           int32_t activation_dtype, uint8_t cache_dtype,
+                                                           uint8_t cache_layout, const Rib200OnlineDecodePlan *plan,
+                                                           void *stream) {
+  return guarded([&] {
+    require(plan != nullptr, "online decode: plan pointer is null");
+    online_decode(query, key, value, gate, output, kv_cache, kv_cache_bytes, workspace, workspace_bytes,
+                  deref(shape), activation_dtype, cache_dtype, cache_layout, *plan, nullptr,
+                  static_cast<cudaStream_t>(stream), true);
   });
 }
 

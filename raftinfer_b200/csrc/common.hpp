@@ -86,6 +86,7 @@ struct DecodeArgs {
   std::uint32_t partition_capacity; // grid.x
   std::uint32_t max_partitions;     // stride of the partial arrays
   bool activations_f32;
+  bool early_kv_fetch; // host position only: the cache rows are fetched before the dependent-launch wait
 };
 // 128-byte opaque image of a driver tensor map (TMA descriptor); 64-byte aligned as the driver's type is.
 struct alignas(64) TensorMapBytes {
@@ -97,7 +98,6 @@ void encode_f32_rows_map(void *map_out, void *base, std::uint64_t row_floats, st
                          std::uint32_t box_floats, std::uint32_t box_rows);
 
 void launch_decode_attention(const DecodeArgs &args, cudaStream_t stream);
-void set_decode_early_kv_fetch(bool enabled);
 
 // One decode step for a batch of ragged sequences (BF16 activations).
 struct BatchedDecodeArgs {
@@ -142,7 +142,7 @@ struct PrefillArgs {
 void launch_prefill_attention(const PrefillArgs &args, cudaStream_t stream);
 // device-side rendezvous of the ranks of one box (peer.cu)
 void launch_peer_rendezvous(std::uint32_t *const *flags, std::uint32_t world, std::uint32_t rank, std::uint32_t epoch,
-                            cudaStream_t stream);
+                            cudaStream_t stream, long long limit_cycles);
 
 // ---- gated delta rule (gdn_recurrent.cu, gdn_chunk.cu, gdn_layer.cu) -------------------------
 // Operands of the recurrence for `sequences` independent sequences of `tokens` tokens each.

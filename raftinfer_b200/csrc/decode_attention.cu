@@ -4,8 +4,9 @@
 //
 // It replaces the four launches of cpp/kernels/qwen35_online_attention.cu:925-1015 (append, single
 // block, partition, merge) by two: a partition kernel that also appends the new token, and a combine
-// kernel.  The partial (max, sum, acc) contract and the workspace layout of
-// cpp/kernels/qwen35_online_attention.cu:603-691,1111-1143 are kept.
+// kernel whose sixteen-lane groups fold the split partials (shared memory and one pass of loads; the
+// probabilities inside the partition kernel travel by warp shuffles).  The partial (max, sum, acc) contract
+// and the workspace layout of cpp/kernels/qwen35_online_attention.cu:603-691,1111-1143 are kept.
 //
 // Bandwidth plan.  One CTA serves one (partition, KV head) and all four query heads of the group, so
 // every K and V byte is read from HBM once (the reference streams each KV head four times).  Each warp
@@ -31,9 +32,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
-#include <atomic>
 #include <cstdint>
-#include <cstdlib>
 #include <mutex>
 
 namespace rib200 {
@@ -267,10 +266,11 @@ __global__ void __launch_bounds__(T::kWarps * 32, T::kCtasPerSm) decode_partitio
   // the ordering is that of a plain launch, minus the launch latency.
   if (Batched || p.early_kv == 0) {
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    // Let the kernel behind this one become resident now; it blocks in its own griddepcontrol.wait until this
+    // whole grid has finished and flushed.  (With the early cache fetch the release comes after the wait further
+    // down, so that nothing launched behind this grid can start while the kernel in front of it still runs.)
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   }
-  // Let the combine kernel become resident now; it blocks in griddepcontrol.wait until this whole grid has
-  // finished and flushed.
-  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   [[maybe_unused]] const unsigned int trace_cta = blockIdx.x + gridDim.x * blockIdx.y;
   RIB200_DECODE_STAMP(g_decode_trace, trace_cta, 0);
 
@@ -423,12 +423,17 @@ __global__ void __launch_bounds__(T::kWarps * 32, T::kCtasPerSm) decode_partitio
       issue(n);
     }
   }
+  const bool whole_ring_early = !Batched && p.early_kv != 0;
+  if (whole_ring_early && static_cast<std::uint32_t>(kRingSlots - 1) < my_slots) {
+    issue(kRingSlots - 1); // nothing has been consumed yet: the last ring position can be filled now as well
+  }
   if (!Batched && p.early_kv != 0) {
     // Early cache fetch: the copies above read cache rows only, with every address taken from kernel
     // parameters, and the caller has promised that no kernel in flight writes those rows.  Everything the
     // kernel in front may have produced (query, key, value, gate) and everything this grid writes comes
     // after this wait.
     asm volatile("griddepcontrol.wait;\n" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   }
 
   // Query fragments (the B operand of the score product): lane (g, t) holds, for k-step ks, dims
@@ -482,7 +487,7 @@ __global__ void __launch_bounds__(T::kWarps * 32, T::kCtasPerSm) decode_partitio
     // ---- K slot: scores and softmax ----
     fence_proxy_async();
     __syncwarp(); // all lanes are done with the ring position that is refilled next
-    if (2 * i + kRingSlots - 1 < my_slots) {
+    if (2 * i + kRingSlots - 1 < my_slots && !(whole_ring_early && i == 0)) {
       issue(2 * i + kRingSlots - 1);
     }
     if (!wait_slot(2 * i)) {
@@ -821,58 +826,9 @@ void launch_pair_tiled(const DecodeParams &params, dim3 partition_grid, dim3 com
           "decode attention combine launch");
 }
 
-// RIB200_DECODE_TILE=<warps><slots> (e.g. 43) picks another CTA shape; a tuning aid, not an interface.
-int tuning_tile() {
-  static const int choice = [] {
-    const char *env = std::getenv("RIB200_DECODE_TILE");
-    return env != nullptr ? std::atoi(env) : 0;
-  }();
-  return choice;
-}
-
 template <bool F32, bool Batched>
 void launch_pair(const DecodeParams &params, dim3 partition_grid, dim3 combine_grid, bool combine,
                  cudaStream_t stream) {
-  switch (tuning_tile()) {
-  case 13:
-    launch_pair_tiled<F32, Batched, Tile<1, 3>>(params, partition_grid, combine_grid, combine, stream);
-    return;
-  case 14:
-    launch_pair_tiled<F32, Batched, Tile<1, 4>>(params, partition_grid, combine_grid, combine, stream);
-    return;
-  case 16:
-    launch_pair_tiled<F32, Batched, Tile<1, 6>>(params, partition_grid, combine_grid, combine, stream);
-    return;
-  case 23:
-    launch_pair_tiled<F32, Batched, Tile<2, 3>>(params, partition_grid, combine_grid, combine, stream);
-    return;
-  case 24:
-    launch_pair_tiled<F32, Batched, Tile<2, 4>>(params, partition_grid, combine_grid, combine, stream);
-    return;
-  case 26:
-    launch_pair_tiled<F32, Batched, Tile<2, 6>>(params, partition_grid, combine_grid, combine, stream);
-    return;
-  case 44:
-    launch_pair_tiled<F32, Batched, Tile<4, 4>>(params, partition_grid, combine_grid, combine, stream);
-    return;
-  case 46:
-    launch_pair_tiled<F32, Batched, Tile<4, 6>>(params, partition_grid, combine_grid, combine, stream);
-    return;
-  case 42:
-    launch_pair_tiled<F32, Batched, Tile<4, 2>>(params, partition_grid, combine_grid, combine, stream);
-    return;
-  case 43:
-    launch_pair_tiled<F32, Batched, Tile<4, 3>>(params, partition_grid, combine_grid, combine, stream);
-    return;
-  case 82:
-    launch_pair_tiled<F32, Batched, Tile<8, 2>>(params, partition_grid, combine_grid, combine, stream);
-    return;
-  case 83:
-    launch_pair_tiled<F32, Batched, Tile<8, 3>>(params, partition_grid, combine_grid, combine, stream);
-    return;
-  default:
-    break;
-  }
   const std::size_t ctas = static_cast<std::size_t>(partition_grid.x) * partition_grid.y * partition_grid.z;
   if (ctas <= 148) {
     launch_pair_tiled<F32, Batched, Tile<8, 3>>(params, partition_grid, combine_grid, combine, stream);
@@ -895,11 +851,6 @@ extern "C" int rib200_debug_read_decode_trace(long long *partition, long long *c
 }
 #endif
 
-// Process-wide opt-in set through rib200_set_decode_early_kv_fetch.
-std::atomic<int> g_early_kv_fetch{0};
-
-void set_decode_early_kv_fetch(bool enabled) { g_early_kv_fetch.store(enabled ? 1 : 0, std::memory_order_relaxed); }
-
 void launch_decode_attention(const DecodeArgs &a, cudaStream_t stream) {
   DecodeParams params{};
   params.query = a.query;
@@ -920,7 +871,7 @@ void launch_decode_attention(const DecodeArgs &a, cudaStream_t stream) {
   params.partial_value = a.partial_value;
   params.partial_stride = 0;
   params.status = device_status_word();
-  params.early_kv = (a.device_position == nullptr && g_early_kv_fetch.load(std::memory_order_relaxed) != 0) ? 1U : 0U;
+  params.early_kv = (a.device_position == nullptr && a.early_kv_fetch) ? 1U : 0U;
   const bool split = a.partition_tokens != 0;
   const dim3 partition_grid(split ? a.partition_capacity : 1, kKvHeads, 1);
   const dim3 combine_grid(kQueryHeads, 4, 1);

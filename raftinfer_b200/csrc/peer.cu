@@ -10,9 +10,10 @@
 #include <cstring>
 
 namespace rib200 {
-namespace {
 
 constexpr long long kRendezvousLimitCycles = 1LL << 31; // about a second
+
+namespace {
 
 struct RendezvousParams {
   std::uint32_t *flags[8];
@@ -20,6 +21,7 @@ struct RendezvousParams {
   std::uint32_t rank;
   std::uint32_t epoch;
   unsigned int *status;
+  long long limit_cycles;
 };
 
 // One warp.  Lane r < world publishes this rank's epoch in rank r's array, then waits for rank r's epoch in this
@@ -38,7 +40,7 @@ __global__ void peer_rendezvous_kernel(const RendezvousParams p) {
   const long long started = clock64();
   // epochs are compared as a signed difference, so they may wrap
   while (static_cast<std::int32_t>(*mine - p.epoch) < 0) {
-    if (clock64() - started > kRendezvousLimitCycles) {
+    if (clock64() - started > p.limit_cycles) {
       atomicOr(p.status, static_cast<unsigned int>(RIB200_DEVICE_WAIT_TIMED_OUT));
       return;
     }
@@ -49,7 +51,7 @@ __global__ void peer_rendezvous_kernel(const RendezvousParams p) {
 } // namespace
 
 void launch_peer_rendezvous(std::uint32_t *const *flags, std::uint32_t world, std::uint32_t rank, std::uint32_t epoch,
-                            cudaStream_t stream) {
+                            cudaStream_t stream, long long limit_cycles) {
   RendezvousParams p{};
   for (std::uint32_t r = 0; r < world; ++r) {
     p.flags[r] = flags[r];
@@ -58,6 +60,7 @@ void launch_peer_rendezvous(std::uint32_t *const *flags, std::uint32_t world, st
   p.rank = rank;
   p.epoch = epoch;
   p.status = device_status_word();
+  p.limit_cycles = limit_cycles > 0 ? limit_cycles : kRendezvousLimitCycles;
   peer_rendezvous_kernel<<<1, 32, 0, stream>>>(p);
   cuda_ok(cudaGetLastError(), "peer rendezvous launch");
 }
@@ -66,9 +69,10 @@ void launch_peer_rendezvous(std::uint32_t *const *flags, std::uint32_t world, st
 
 using namespace rib200;
 
-extern "C" Rib200Status rib200_peer_rendezvous(uint32_t *const *flags, size_t world, size_t rank, uint32_t epoch,
-                                               void *stream) {
+extern "C" Rib200Status rib200_peer_rendezvous_bounded(uint32_t *const *flags, size_t world, size_t rank,
+                                                       uint32_t epoch, uint64_t limit_cycles, void *stream) {
   return guarded([&] {
+    require(limit_cycles >= 1 && limit_cycles <= (1ULL << 40), "peer rendezvous: limit_cycles is out of range");
     require(flags != nullptr, "peer rendezvous: flag array list is null");
     require(world >= 1 && world <= 8, "peer rendezvous: world must be between 1 and 8");
     require(rank < world, "peer rendezvous: rank is out of range");
@@ -77,8 +81,14 @@ extern "C" Rib200Status rib200_peer_rendezvous(uint32_t *const *flags, size_t wo
       require(flags[r] != nullptr, "peer rendezvous: a flag array is null");
     }
     launch_peer_rendezvous(flags, static_cast<std::uint32_t>(world), static_cast<std::uint32_t>(rank), epoch,
-                           static_cast<cudaStream_t>(stream));
+                           static_cast<cudaStream_t>(stream), static_cast<long long>(limit_cycles));
   });
+}
+
+extern "C" Rib200Status rib200_peer_rendezvous(uint32_t *const *flags, size_t world, size_t rank, uint32_t epoch,
+                                               void *stream) {
+  return rib200_peer_rendezvous_bounded(flags, world, rank, epoch, static_cast<uint64_t>(kRendezvousLimitCycles),
+                                        stream);
 }
 
 extern "C" Rib200Status rib200_shared_alloc(size_t bytes, void **pointer, uint8_t handle[64]) {

@@ -1477,7 +1477,10 @@ template <bool F32, bool Pair, bool Split> void configure_once() {
   });
 }
 
-// RIB200_PREFILL_PAIR=0 keeps every shape on the single-CTA form (a tuning aid, not an interface).
+// Builds made with -DRIB200_TUNING read two switches from the environment, for A/B timing of the kernel forms:
+// RIB200_PREFILL_PAIR=0 keeps every shape on the single-CTA form, RIB200_PREFILL_SPLIT=0 never splits an item
+// over two CTA pairs.  The library as shipped has neither switch: both forms are chosen by shape alone.
+#ifdef RIB200_TUNING
 bool pair_form_enabled() {
   static const bool enabled = [] {
     const char *env = std::getenv("RIB200_PREFILL_PAIR");
@@ -1485,8 +1488,6 @@ bool pair_form_enabled() {
   }();
   return enabled;
 }
-
-// RIB200_PREFILL_SPLIT=0 never splits an item over two CTAs (a tuning aid, not an interface).
 bool split_form_enabled() {
   static const bool enabled = [] {
     const char *env = std::getenv("RIB200_PREFILL_SPLIT");
@@ -1494,6 +1495,10 @@ bool split_form_enabled() {
   }();
   return enabled;
 }
+#else
+constexpr bool pair_form_enabled() { return true; }
+constexpr bool split_form_enabled() { return true; }
+#endif
 
 template <bool F32, bool Pair, bool Split> void launch(const PrefillArgs &a, cudaStream_t stream) {
   configure_once<F32, Pair, Split>();

@@ -55,11 +55,4 @@ extern "C" Rib200Status rib200_device_status(void *stream, uint32_t *bits) {
   });
 }
 
-extern "C" Rib200Status rib200_set_decode_early_kv_fetch(int32_t enabled) {
-  return rib200::guarded([&] {
-    rib200::require(enabled == 0 || enabled == 1, "early KV fetch: enabled must be 0 or 1");
-    rib200::set_decode_early_kv_fetch(enabled == 1);
-  });
-}
-
 extern "C" const char *rib200_version(void) { return "rib200 0.1 sm_100a"; }

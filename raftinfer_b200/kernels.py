@@ -277,6 +277,12 @@ def peer_rendezvous(flag_arrays, rank, epoch, stream):
     _check(lib.rib200_peer_rendezvous(array, len(flag_arrays), rank, epoch, _stream(stream)))
 
 
+def peer_rendezvous_bounded(flag_arrays, rank, epoch, limit_cycles, stream):
+    """The rendezvous with the caller's bound on the device-side wait, in SM clock cycles."""
+    array = (C.c_void_p * len(flag_arrays))(*[_ptr(f) for f in flag_arrays])
+    _check(lib.rib200_peer_rendezvous_bounded(array, len(flag_arrays), rank, epoch, limit_cycles, _stream(stream)))
+
+
 def shared_alloc(nbytes):
     """Zero-filled device memory other processes can map: (pointer, 64-byte handle)."""
     ptr = C.c_void_p()
@@ -409,10 +415,18 @@ def batched_gdn_decode(q, k, v, beta, log_decay, states, out, batch, key_heads, 
            Qwen35DeltaError)
 
 
-def set_decode_early_kv_fetch(enabled):
-    """Opt-in described at rib200_set_decode_early_kv_fetch: the caller promises that no work in flight writes the
-    cache rows a decode step reads, and the step starts fetching them before the kernel in front has finished."""
-    _check(lib.rib200_set_decode_early_kv_fetch(1 if enabled else 0))
+def online_attention_decode_early_kv_fetch(query, key, value, gate, output, kv_cache, kv_cache_bytes, workspace,
+                                           workspace_bytes, shape, activation_dtype, cache_dtype, cache_layout, plan,
+                                           stream):
+    """rib200_online_attention_decode_early_kv_fetch: the decode step with a host position whose partition kernel
+    fetches cache rows before the kernel in front of it has finished.  The caller promises that no work in flight
+    writes the cache rows the step reads (see include/rib200.h)."""
+    s, p = shape.c(), plan.c()
+    _check(lib.rib200_online_attention_decode_early_kv_fetch(_ptr(query), _ptr(key), _ptr(value), _ptr(gate),
+                                                             _ptr(output), _ptr(kv_cache), kv_cache_bytes,
+                                                             _ptr(workspace), workspace_bytes, C.byref(s),
+                                                             activation_dtype, cache_dtype, cache_layout, C.byref(p),
+                                                             _stream(stream)))
 
 
 def device_status(stream):

@@ -29,7 +29,7 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 sys.path.insert(0, ROOT)
-REF = os.environ.get("REF", "/root/reference")
+REF = os.environ.get("REF") or sys.exit("set REF to the path of the RAFTInfer checkout")
 
 from oracle import bindings as ob  # noqa: E402
 from raftinfer_b200 import synth  # noqa: E402

@@ -23,6 +23,8 @@ def bf16_tensor(values_f32):
 def act_tensor(values_f32, dtype):
     if dtype == K.DTYPE_F32:
         return torch.from_numpy(np.ascontiguousarray(values_f32, dtype=np.float32)).to(dev())
+    if dtype == K.DTYPE_F16:
+        return torch.from_numpy(np.ascontiguousarray(values_f32, dtype=np.float32).astype(np.float16)).to(dev())
     return bf16_tensor(values_f32)
 
 

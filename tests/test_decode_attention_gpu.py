@@ -263,10 +263,11 @@ def test_back_to_back_steps_keep_stream_order():
 
 
 def test_early_kv_fetch_gives_the_same_bits():
-    """With the early cache fetch switched on the partition kernel reads cache rows before the kernels in front of it
-    have finished.  Under the conditions the option asks for, the results are those of the default ordering: (a) steps
-    enqueued back to back on different caches, none of which writes a row another one reads; (b) a chain on one cache
-    with advancing positions in which an ordinary kernel (the query update) sits between the steps."""
+    """Through the early-cache-fetch entry point the partition kernel reads cache rows before the kernels in front of
+    it have finished.  Under the conditions that entry point asks for, the results are those of the default ordering:
+    (a) steps enqueued back to back on different caches, none of which writes a row another one reads; (b) a chain on
+    one cache with advancing positions in which ordinary kernels sit between the steps: they rewrite the query AND the
+    gate directly in front of each step, so a step that read either of them too early would show."""
     max_ctx, ctx0, steps = 8192, 6000, 8
     q, gate, k, v = decode_operands(0xB2000B00, ctx0 + steps)
     shape_of = lambda pos: K.Qwen35AttentionShape(1, HQ, HKV, D, max_ctx, pos)
@@ -278,45 +279,48 @@ def test_early_kv_fetch_gives_the_same_bits():
     queries = [act_tensor(q * (1.0 + 0.1 * i), K.DTYPE_BF16) for i in range(steps)]
     stream = torch.cuda.current_stream()
 
-    def independent():
+    def call(early, *args):
+        if early:
+            K.online_attention_decode_early_kv_fetch(*args, stream)
+        else:
+            K.qwen35_online_attention_decode(*args, None, stream)
+
+    def independent(early):
         caches = [cache_to_device(make_cache(k, v, max_ctx, ctx0)) for _ in range(steps)]
         ws = torch.zeros(layout.bytes // 4, device=dev())
         outs = [torch.zeros(HQ, D, device=dev(), dtype=torch.bfloat16) for _ in range(steps)]
         torch.cuda.synchronize()
         for i in range(steps):
-            K.qwen35_online_attention_decode(queries[i], rows_k[0], rows_v[0], dg, outs[i], caches[i],
-                                             caches[i].numel() * 2, ws, layout.bytes, shape_of(ctx0), K.DTYPE_BF16,
-                                             K.KV_BF16, K.HEAD_MAJOR, plan, None, stream)
+            call(early, queries[i], rows_k[0], rows_v[0], dg, outs[i], caches[i], caches[i].numel() * 2, ws,
+                 layout.bytes, shape_of(ctx0), K.DTYPE_BF16, K.KV_BF16, K.HEAD_MAJOR, plan)
         torch.cuda.synchronize()
         return torch.stack(outs), torch.stack(caches)
 
-    def chain():
+    def chain(early, moving_gate=True):
         cache = cache_to_device(make_cache(k, v, max_ctx, ctx0))
         ws = torch.zeros(layout.bytes // 4, device=dev())
         dq = queries[0].clone()
+        step_gate = dg.clone()
         outs = []
         for i in range(steps):
             out = torch.zeros(HQ, D, device=dev(), dtype=torch.bfloat16)
-            K.qwen35_online_attention_decode(dq, rows_k[i], rows_v[i], dg, out, cache, cache.numel() * 2, ws,
-                                             layout.bytes, shape_of(ctx0 + i), K.DTYPE_BF16, K.KV_BF16, K.HEAD_MAJOR,
-                                             plan, None, stream)
+            call(early, dq, rows_k[i], rows_v[i], step_gate, out, cache, cache.numel() * 2, ws, layout.bytes,
+                 shape_of(ctx0 + i), K.DTYPE_BF16, K.KV_BF16, K.HEAD_MAJOR, plan)
             dq = (dq.float() * 0.5 + out.float() * 4.0).to(torch.bfloat16)
+            if moving_gate:  # rewritten in place, at the same address, by an ordinary kernel
+                step_gate.copy_((step_gate.float() * 0.75 - out.float() * 3.0).to(torch.bfloat16))
             outs.append(out)
         torch.cuda.synchronize()
         return torch.stack(outs), cache
 
-    plain = independent(), chain()
-    K.set_decode_early_kv_fetch(True)
-    try:
-        early = independent(), chain()
-    finally:
-        K.set_decode_early_kv_fetch(False)
+    plain = independent(False), chain(False)
+    early = independent(True), chain(True)
     assert K.device_status(stream) == 0
     for (want_out, want_cache), (got_out, got_cache) in zip(plain, early):
         assert torch.equal(got_out, want_out)
         assert torch.equal(got_cache, want_cache)
-    with pytest.raises(K.Qwen35PrimitiveError):
-        K._check(K.lib.rib200_set_decode_early_kv_fetch(2))
+    # the chain's gates really moved: its outputs differ from those of a chain whose gate is held constant
+    assert not torch.equal(plain[1][0], chain(False, moving_gate=False)[0])
 
 
 def test_decode_from_host_buffers():

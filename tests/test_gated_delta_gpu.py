@@ -190,7 +190,7 @@ class LayerRun:
         ws_bytes = K.qwen35_gated_delta_workspace_bytes(shape)
         ws = torch.zeros(ws_bytes // 4, device=dev())
         out = torch.zeros(tokens, hidden, device=dev(),
-                          dtype=torch.float32 if self.dtype == K.DTYPE_F32 else torch.bfloat16)
+                          dtype={K.DTYPE_F32: torch.float32, K.DTYPE_F16: torch.float16}.get(self.dtype, torch.bfloat16))
         d_in = act_tensor(chunk, self.dtype)
         K.qwen35_gated_delta(d_in, self.d_conv_w, self.d_rec_a, self.d_dt, self.d_norm, out, self.d_cs, self.d_rs, ws,
                              ws_bytes, shape, self.dtype, self.wdtype, torch.cuda.current_stream())
@@ -221,6 +221,26 @@ def test_layer_small_heads(tokens, dtype, wdtype):
     run = LayerRun(0xB2002000 + tokens, 2, 4, 3, dtype, wdtype, tokens)
     out, want, _ = run.step(tokens)
     run.check(out, want)
+
+
+@pytest.mark.parametrize("tokens", [3, 150])
+@pytest.mark.parametrize("wdtype", [K.DTYPE_F32, K.DTYPE_F16])
+def test_layer_f16_activations(tokens, wdtype):
+    """FP16 input and output (the reference's delta launcher takes F32, F16 and BF16, cpp/kernels/qwen35_delta.cu:
+    811-897): operands that FP16 holds exactly on both sides, the recurrent kernel (3 tokens) and the chunked one."""
+    run = LayerRun(0xB2002600 + tokens, 2, 4, 4, K.DTYPE_F16, wdtype, tokens)
+    half = lambda x: x.astype(np.float16).astype(np.float32)
+    run.inp = half(run.inp)
+    if wdtype == K.DTYPE_F16:
+        run.conv_w, run.rec_a, run.dt_bias, run.norm_w = (half(x) for x in (run.conv_w, run.rec_a, run.dt_bias,
+                                                                             run.norm_w))
+        run.d_conv_w, run.d_rec_a = act_tensor(run.conv_w, wdtype), act_tensor(run.rec_a, wdtype)
+        run.d_dt, run.d_norm = act_tensor(run.dt_bias, wdtype), act_tensor(run.norm_w, wdtype)
+    out, want, _ = run.step(tokens)
+    m = compare(to_numpy_f32(out), want)
+    assert m["nonfinite"] == 0 and m["max_abs"] <= 3.0e-2 and m["rel_l2"] <= 1.0e-2, m
+    assert compare(to_numpy_f32(run.d_cs).reshape(-1), run.cs.reshape(-1))["max_abs"] == 0.0
+    assert compare(to_numpy_f32(run.d_rs).reshape(-1), run.rs.reshape(-1))["rel_l2"] <= 1.0e-3
 
 
 def test_layer_model_shape_prefill_then_decode_then_continued_prefill():

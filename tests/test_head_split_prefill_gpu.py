@@ -80,6 +80,31 @@ def test_scatter_rejects_bad_arguments():
                                            K.KV_BF16, K.HEAD_MAJOR, stream)
 
 
+def test_rendezvous_wait_runs_out_and_the_context_stays_usable():
+    """A rank that never arrives: world 2 on one GPU with two flag arrays this process owns, rank 0 calls, nothing ever
+    writes rank 1's slot.  The wait is bounded (two million cycles, about a millisecond), so the kernel gives up,
+    records RIB200_DEVICE_WAIT_TIMED_OUT and returns; the status word reads back, clears, and the next calls on the
+    same stream work as usual.  This is what stands where the reference traps
+    (cpp/kernels/qwen35_online_attention.cu:714-717): a status the host reads, not a lost context."""
+    stream = torch.cuda.current_stream()
+    mine = torch.zeros(2, device=dev(), dtype=torch.int32)
+    theirs = torch.zeros(2, device=dev(), dtype=torch.int32)
+    assert K.device_status(stream) == 0
+    K.peer_rendezvous_bounded([mine, theirs], 0, 1, 2_000_000, stream)
+    torch.cuda.synchronize()
+    assert K.device_status(stream) == K.DEVICE_WAIT_TIMED_OUT
+    assert mine.tolist() == [1, 0] and theirs.tolist() == [1, 0]  # rank 0 published its epoch in both arrays
+    assert K.device_status(stream) == 0  # reading cleared it
+    # the peer arrives after all (its slot is written by hand): the same epoch now completes within the bound
+    mine[1] = 1
+    K.peer_rendezvous_bounded([mine, theirs], 0, 1, 2_000_000, stream)
+    K.peer_rendezvous([mine], 0, 5, stream)
+    torch.cuda.synchronize()
+    assert K.device_status(stream) == 0 and int(mine[0].item()) == 5
+    with pytest.raises(K.Qwen35PrimitiveError):
+        K.peer_rendezvous_bounded([mine, theirs], 0, 2, 0, stream)
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_two_ranks_fused_equals_all_gather():
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")

@@ -5,13 +5,15 @@ memory all went to a pool at start-up, a plugin that only sees the operator's ow
 cannot afford cudaMalloc's device-wide synchronisation.  For them the split-k partials live in an array inside the
 library.  This file checks, through the C ABI, that the entry point gives the same output and the same appended
 cache row as the workspace entry point on the same inputs, on two calls in a row that share the built-in array
-(different positions, the second one shorter so stale partials of the first stay behind it), and that it refuses
-caches beyond the size the array was built for.  It is collected last on purpose.
+(different positions, the second one shorter so stale partials of the first stay behind it), that both agree with the
+CPU oracle, that the largest cache the array was built for (32768 rows, last partition) works, and that it refuses
+caches beyond that size.  It is collected last on purpose.
 """
 import numpy as np
 import pytest
 import torch
 
+from oracle import bindings as ob
 from raftinfer_b200 import kernels as K
 
 from gpu_util import (D, HKV, HQ, act_tensor, cache_bits_of, cache_to_device, compare, decode_operands, dev,
@@ -45,6 +47,11 @@ def _both_entry_points(ctx, max_ctx, dtype, seed, device_position):
     metrics = compare(to_numpy_f32(out_b), to_numpy_f32(out_a))
     gate_bf16_outputs(metrics)  # max abs <= 3e-2, relative L2 <= 1e-2: the tolerance of the decode tests
     assert np.array_equal(cache_bits_of(cache_b), cache_bits_of(cache_a))
+    # and against the CPU oracle on the cache as the step leaves it (the new row appended)
+    full = make_cache(k, v, max_ctx, ctx)
+    assert np.array_equal(cache_bits_of(cache_b).reshape(full.shape), full)
+    want = ob.attention_core_cache(q[None], gate[None], full, max_ctx, pos)[0]
+    gate_bf16_outputs(compare(to_numpy_f32(out_b), want))
     return metrics
 
 
@@ -55,6 +62,17 @@ def test_static_scratch_decode_matches_workspace_decode_on_two_calls_in_a_row():
     third = _both_entry_points(100, 1024, K.DTYPE_BF16, 0xB2003002, device_position=False)  # below the threshold
     for metrics in (first, second, third):
         assert metrics["max_abs"] <= 3.0e-2 and metrics["rel_l2"] <= 1.0e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("ctx,max_ctx", [(32768, 32768), (32700, 32700), (32513, 32768)])
+def test_static_scratch_decode_at_the_size_limit_of_its_array(ctx, max_ctx):
+    """The built-in array holds 16 heads x 128 partitions: a 32768-row cache with the position in the last partition
+    uses its last partial, and a capacity that is not a multiple of 256 rounds the partition count up to the same
+    128.  An array one partial too small, or an offset computed from the wrong partition count, shows here."""
+    _both_entry_points(ctx, max_ctx, K.DTYPE_BF16, 0xB2003010 + ctx, device_position=False)
+    # a short call straight afterwards, in the other activation type, finds the long call's partials still in the array
+    _both_entry_points(300, 512, K.DTYPE_F32, 0xB2003020, device_position=True)
 
 
 def test_static_scratch_decode_refuses_caches_beyond_its_array():
