@@ -5,8 +5,9 @@
 //   state     shift of the convolution history [channel][W-1] (cpp/kernels/qwen35_delta.cu:267-275);
 //   epilogue  per-head RMSNorm(128) * weight * SiLU(z) (cpp/kernels/qwen35_delta.cu:579-621).
 // Unlike the reference's convolution kernel, which walks the tokens serially per channel, every
-// (token, head vector) pair is its own CTA: a tap is read from the token stream or, for the first W-1
-// tokens, from the carried history.
+// (token, head vector) pair is independent: a tap is read from the token stream or, for the first W-1
+// tokens, from the carried history.  conv_width 4 on aligned tensors takes the warp-per-vector kernels
+// (16-byte accesses); other widths and odd alignments take the one-CTA-per-vector kernels.
 
 #include "common.hpp"
 
@@ -117,6 +118,196 @@ __global__ void __launch_bounds__(kDim) gdn_prologue_kernel(const LayerParams p)
   p.convolved[static_cast<std::size_t>(tok) * p.conv_dim + channel] = value;
 }
 
+// ---- fast forms for conv_width == 4 (the model's width) ---------------------------------------------
+// A warp owns one head vector (128 channels, four per lane) over eight consecutive tokens: the eleven input rows
+// it needs are fetched once, 8 or 16 bytes per lane and row, whole 256/512-byte segments per warp, and slide
+// through registers; the sum of squares of a q or k vector is five shuffles.  Dtype is a template parameter.
+template <int Dtype> struct Io;
+template <> struct Io<RIB200_DTYPE_F32> {
+  static __device__ __forceinline__ float4 load4(const void *base, std::size_t index) {
+    return *reinterpret_cast<const float4 *>(static_cast<const float *>(base) + index);
+  }
+  static __device__ __forceinline__ void store4(void *base, std::size_t index, float4 v) {
+    *reinterpret_cast<float4 *>(static_cast<float *>(base) + index) = v;
+  }
+};
+template <> struct Io<RIB200_DTYPE_BF16> {
+  static __device__ __forceinline__ float4 load4(const void *base, std::size_t index) {
+    const uint2 raw = *reinterpret_cast<const uint2 *>(static_cast<const __nv_bfloat16 *>(base) + index);
+    return make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xFFFF0000U),
+                       __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xFFFF0000U));
+  }
+  static __device__ __forceinline__ void store4(void *base, std::size_t index, float4 v) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y);
+    const __nv_bfloat162 hi = __floats2bfloat162_rn(v.z, v.w);
+    *reinterpret_cast<uint2 *>(static_cast<__nv_bfloat16 *>(base) + index) =
+        make_uint2(*reinterpret_cast<const std::uint32_t *>(&lo), *reinterpret_cast<const std::uint32_t *>(&hi));
+  }
+};
+template <> struct Io<RIB200_DTYPE_F16> {
+  static __device__ __forceinline__ float4 load4(const void *base, std::size_t index) {
+    const uint2 raw = *reinterpret_cast<const uint2 *>(static_cast<const __half *>(base) + index);
+    const float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&raw.x));
+    const float2 hi = __half22float2(*reinterpret_cast<const __half2 *>(&raw.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+  }
+  static __device__ __forceinline__ void store4(void *base, std::size_t index, float4 v) {
+    const __half2 lo = __floats2half2_rn(v.x, v.y);
+    const __half2 hi = __floats2half2_rn(v.z, v.w);
+    *reinterpret_cast<uint2 *>(static_cast<__half *>(base) + index) =
+        make_uint2(*reinterpret_cast<const std::uint32_t *>(&lo), *reinterpret_cast<const std::uint32_t *>(&hi));
+  }
+};
+
+// SiLU on the special-function unit (ex2 + rcp instead of a full-precision exponential and division): the vector
+// kernels are bound by instruction issue otherwise.  Relative error about 1e-6.
+__device__ __forceinline__ float silu_fast(float x) { return x * __frcp_rn(1.0F + __expf(-x)); }
+
+constexpr int kTokensPerWarp = 8;
+constexpr int kFastWidth = 4;
+
+// grid (ceil(tokens / 8), ceil((2 Hk + Hv + 1) / 8)), 256 threads: warp w of the CTA takes head vector
+// 8 blockIdx.y + w; the vector after the last one stands for the gates (lane = value head, any head count).
+template <int Dtype> __global__ void __launch_bounds__(256, 4) gdn_prologue_w4_kernel(const LayerParams p) {
+  const int lane = threadIdx.x & 31;
+  const std::uint32_t vec = blockIdx.y * 8 + (threadIdx.x >> 5);
+  const std::uint32_t vectors = 2 * p.key_heads + p.value_heads;
+  const std::uint32_t tok0 = blockIdx.x * kTokensPerWarp;
+  if (vec > vectors) {
+    return;
+  }
+  if (vec == vectors) {
+    for (std::uint32_t head = lane; head < p.value_heads; head += 32) {
+      const float a_coeff = load_any(p.recurrent_a, head, p.weight_dtype);
+      const float dt = load_any(p.dt_bias, head, p.weight_dtype);
+      for (std::uint32_t tok = tok0; tok < min(p.tokens, tok0 + kTokensPerWarp); ++tok) {
+        const std::size_t gates = static_cast<std::size_t>(tok) * p.token_stride + p.conv_dim;
+        const float b = load_any(p.input, gates + head, p.dtype);
+        const float a = load_any(p.input, gates + p.value_heads + head, p.dtype);
+        p.beta[static_cast<std::size_t>(tok) * p.value_heads + head] = 1.0F / (1.0F + expf(-b));
+        p.log_decay[static_cast<std::size_t>(tok) * p.value_heads + head] = a_coeff * softplus(a + dt);
+      }
+    }
+    return;
+  }
+  const std::uint32_t channel = vec * kDim + 4 * lane;
+  // taps of this lane's four channels: weight[channel][4], oldest first
+  float w[4][kFastWidth];
+  if (p.weight_dtype == RIB200_DTYPE_F32) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const float4 taps = *reinterpret_cast<const float4 *>(static_cast<const float *>(p.conv_weight) +
+                                                            static_cast<std::size_t>(channel + c) * kFastWidth);
+      w[c][0] = taps.x;
+      w[c][1] = taps.y;
+      w[c][2] = taps.z;
+      w[c][3] = taps.w;
+    }
+  } else {
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+#pragma unroll
+      for (int h = 0; h < kFastWidth; ++h) {
+        w[c][h] = load_any(p.conv_weight, static_cast<std::size_t>(channel + c) * kFastWidth + h, p.weight_dtype);
+      }
+    }
+  }
+  // rows tok0 - 3 .. tok0 + 7 of [history | tokens]
+  float4 x[kTokensPerWarp + kFastWidth - 1];
+#pragma unroll
+  for (int r = 0; r < kTokensPerWarp + kFastWidth - 1; ++r) {
+    const long long tok = static_cast<long long>(tok0) + r - (kFastWidth - 1);
+    if (tok >= 0 && tok < static_cast<long long>(p.tokens)) {
+      x[r] = Io<Dtype>::load4(p.input, static_cast<std::size_t>(tok) * p.token_stride + channel);
+    } else {
+      x[r] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+    }
+  }
+  if (tok0 == 0) {
+    // history [channel][3]: element h is the token 3 - h steps before this call's first one
+    const float *hist = p.convolution_state + static_cast<std::size_t>(channel) * (kFastWidth - 1);
+#pragma unroll
+    for (int h = 0; h < kFastWidth - 1; ++h) {
+      x[h] = make_float4(hist[h], hist[(kFastWidth - 1) + h], hist[2 * (kFastWidth - 1) + h],
+                         hist[3 * (kFastWidth - 1) + h]);
+    }
+  }
+  const bool is_qk = vec < 2 * p.key_heads;
+  const float q_scale = vec < p.key_heads ? rsqrtf(static_cast<float>(kDim)) : 1.0F;
+#pragma unroll
+  for (int i = 0; i < kTokensPerWarp; ++i) {
+    const std::uint32_t tok = tok0 + i;
+    float4 sum = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+    // the reference adds the current token's tap first, then the history taps oldest first
+    sum.x = x[i + 3].x * w[0][3];
+    sum.y = x[i + 3].y * w[1][3];
+    sum.z = x[i + 3].z * w[2][3];
+    sum.w = x[i + 3].w * w[3][3];
+#pragma unroll
+    for (int h = 0; h < kFastWidth - 1; ++h) {
+      sum.x += x[i + h].x * w[0][h];
+      sum.y += x[i + h].y * w[1][h];
+      sum.z += x[i + h].z * w[2][h];
+      sum.w += x[i + h].w * w[3][h];
+    }
+    float4 value = make_float4(silu_fast(sum.x), silu_fast(sum.y), silu_fast(sum.z), silu_fast(sum.w));
+    if (is_qk) {
+      float squares = (value.x * value.x + value.y * value.y) + (value.z * value.z + value.w * value.w);
+#pragma unroll
+      for (int offset = 16; offset > 0; offset >>= 1) {
+        squares += __shfl_xor_sync(0xFFFFFFFFU, squares, offset);
+      }
+      const float scale = rsqrtf(squares + kQkEpsilon) * q_scale;
+      value.x *= scale;
+      value.y *= scale;
+      value.z *= scale;
+      value.w *= scale;
+    }
+    if (tok < p.tokens) {
+      *reinterpret_cast<float4 *>(p.convolved + static_cast<std::size_t>(tok) * p.conv_dim + channel) = value;
+    }
+  }
+}
+
+// grid (ceil(tokens * value_heads / 8)), 256 threads: a warp per (token, value head), four channels per lane
+template <int Dtype> __global__ void __launch_bounds__(256) gdn_epilogue_warp_kernel(const LayerParams p) {
+  const int lane = threadIdx.x & 31;
+  const std::size_t item = static_cast<std::size_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  if (item >= static_cast<std::size_t>(p.tokens) * p.value_heads) {
+    return;
+  }
+  const std::size_t tok = item / p.value_heads;
+  const std::uint32_t head = static_cast<std::uint32_t>(item % p.value_heads);
+  const std::size_t index = item * kDim + 4 * lane; // [token][head][128]
+  const float4 value = *reinterpret_cast<const float4 *>(p.raw + index);
+  const float4 z = Io<Dtype>::load4(p.input, tok * p.token_stride + p.conv_dim + 2 * p.value_heads + head * kDim +
+                                                 4 * lane);
+  float squares = (value.x * value.x + value.y * value.y) + (value.z * value.z + value.w * value.w);
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) {
+    squares += __shfl_xor_sync(0xFFFFFFFFU, squares, offset);
+  }
+  const float scale = rsqrtf(squares / static_cast<float>(kDim) + p.epsilon);
+  float4 out;
+  out.x = value.x * scale * load_any(p.output_norm_weight, 4 * lane, p.weight_dtype) * silu_fast(z.x);
+  out.y = value.y * scale * load_any(p.output_norm_weight, 4 * lane + 1, p.weight_dtype) * silu_fast(z.y);
+  out.z = value.z * scale * load_any(p.output_norm_weight, 4 * lane + 2, p.weight_dtype) * silu_fast(z.z);
+  out.w = value.w * scale * load_any(p.output_norm_weight, 4 * lane + 3, p.weight_dtype) * silu_fast(z.w);
+  Io<Dtype>::store4(p.output, index, out);
+}
+
+// Whether the vector forms apply: every row segment a lane touches must start on the boundary of its access.
+bool vector_forms_apply(const LayerParams &p) {
+  const std::size_t element = p.dtype == RIB200_DTYPE_F32 ? 4 : 2;
+  const std::size_t access = 4 * element;
+  if (p.weight_dtype == RIB200_DTYPE_F32 && reinterpret_cast<std::uintptr_t>(p.conv_weight) % 16 != 0) {
+    return false; // the four taps of a channel are fetched as one 16-byte word
+  }
+  return reinterpret_cast<std::uintptr_t>(p.input) % access == 0 &&
+         reinterpret_cast<std::uintptr_t>(p.output) % access == 0 && (p.token_stride * element) % access == 0 &&
+         ((p.conv_dim + 2 * p.value_heads) * element) % access == 0;
+}
+
 // one thread per channel: new history[h] = element tokens + h of [old history | token stream]
 __global__ void gdn_conv_state_kernel(const LayerParams p) {
   const std::uint32_t channel = blockIdx.x * blockDim.x + threadIdx.x;
@@ -183,7 +374,19 @@ LayerParams make_params(const GdnLayerArgs &a) {
 
 void launch_gdn_prologue(const GdnLayerArgs &a, cudaStream_t stream) {
   const LayerParams p = make_params(a);
-  gdn_prologue_kernel<<<dim3(2 * a.key_heads + a.value_heads, a.tokens), kDim, 0, stream>>>(p);
+  // a call of a few tokens is latency, not bandwidth: the one-CTA-per-vector kernel spreads it wider
+  if (a.conv_width == kFastWidth && a.tokens >= 2 * kTokensPerWarp && vector_forms_apply(p)) {
+    const dim3 grid((a.tokens + kTokensPerWarp - 1) / kTokensPerWarp, (2 * a.key_heads + a.value_heads + 1 + 7) / 8);
+    if (a.dtype == RIB200_DTYPE_F32) {
+      gdn_prologue_w4_kernel<RIB200_DTYPE_F32><<<grid, 256, 0, stream>>>(p);
+    } else if (a.dtype == RIB200_DTYPE_F16) {
+      gdn_prologue_w4_kernel<RIB200_DTYPE_F16><<<grid, 256, 0, stream>>>(p);
+    } else {
+      gdn_prologue_w4_kernel<RIB200_DTYPE_BF16><<<grid, 256, 0, stream>>>(p);
+    }
+  } else {
+    gdn_prologue_kernel<<<dim3(2 * a.key_heads + a.value_heads, a.tokens), kDim, 0, stream>>>(p);
+  }
   cuda_ok(cudaGetLastError(), "gated-delta prologue launch");
   if (a.conv_width > 1) {
     gdn_conv_state_kernel<<<(p.conv_dim + 255) / 256, 256, 0, stream>>>(p);
@@ -193,6 +396,19 @@ void launch_gdn_prologue(const GdnLayerArgs &a, cudaStream_t stream) {
 
 void launch_gdn_epilogue(const GdnLayerArgs &a, cudaStream_t stream) {
   const LayerParams p = make_params(a);
+  if (vector_forms_apply(p)) {
+    const std::size_t items = static_cast<std::size_t>(a.tokens) * a.value_heads;
+    const unsigned int grid = static_cast<unsigned int>((items + 7) / 8);
+    if (a.dtype == RIB200_DTYPE_F32) {
+      gdn_epilogue_warp_kernel<RIB200_DTYPE_F32><<<grid, 256, 0, stream>>>(p);
+    } else if (a.dtype == RIB200_DTYPE_F16) {
+      gdn_epilogue_warp_kernel<RIB200_DTYPE_F16><<<grid, 256, 0, stream>>>(p);
+    } else {
+      gdn_epilogue_warp_kernel<RIB200_DTYPE_BF16><<<grid, 256, 0, stream>>>(p);
+    }
+    cuda_ok(cudaGetLastError(), "gated-delta epilogue launch");
+    return;
+  }
   gdn_epilogue_kernel<<<dim3(a.value_heads, a.tokens), kDim, 0, stream>>>(p);
   cuda_ok(cudaGetLastError(), "gated-delta epilogue launch");
 }
