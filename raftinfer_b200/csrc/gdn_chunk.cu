@@ -12,14 +12,16 @@
 // Every decay factor is exp of a non-positive number.  A ragged last chunk is padded with inert rows
 // (beta = 0, log decay = 0, k = q = v = 0), which leave the state untouched.
 //
-// Two kernels.  `prepare` is parallel over (chunk, value head): T by forward substitution in FP32, the four
-// dense products on mma.sync TF32 tensor-core tiles; it leaves every operand the apply kernel multiplies with as a
-// ready shared-memory image (K-major, 128-byte swizzle) in the workspace.  `apply` walks the chunks in order for one
-// (value head, 32-column slice of the state): the slice lives in registers (FP32) and, rounded to TF32, in shared
-// memory as the B operand; [Q; W] S0, P Delta and K^T diag(e) Delta are tcgen05.mma.kind::tf32 products with
-// accumulators in tensor memory.  State columns are independent, so the four slices of a head never talk to each
-// other.  TF32 (10-bit mantissa, FP32 accumulate) rather than BF16 keeps the FP32 state within 1e-3 relative L2 of
-// the sequential recurrence over 64 chunks.
+// Two kernels, both on tcgen05 TF32 products with accumulators in tensor memory.  `prepare` is parallel over
+// (chunk, value head), one persistent CTA per SM: [K; Q] K^T as one product, T by a blocked inversion in FP32
+// (16 x 16 diagonal blocks by substitution, the rest by block products), then [T diag(beta exp(G)); T diag(beta)]
+// times K and times V, whose B operands are K and V exactly as they are stored (token rows, dims contiguous:
+// "MN-major" operands, no transposition).  It leaves every operand the apply kernel multiplies with as a ready
+// shared-memory image in the workspace.  `apply` walks the chunks in order for one (value head, 32-column slice
+// of the state): the slice lives in registers (FP32) and, rounded to TF32, in shared memory as the B operand;
+// [Q; W] S0, P Delta and (diag(e) K)^T Delta are the products.  State columns are independent, so the four slices
+// of a head never talk to each other.  TF32 (10-bit mantissa, FP32 accumulate) rather than BF16 keeps the FP32
+// state within 1e-3 relative L2 of the sequential recurrence over 64 chunks.
 //
 // Dense flops per launch: chunks * value_heads * [2 C^2 (3 dk + 2 dv) + 6 C dk dv].
 
@@ -37,19 +39,17 @@ namespace {
 constexpr int kDim = 128;
 constexpr int kChunk = 64;
 constexpr int kSlice = 32;          // state columns per apply CTA
-constexpr int kPitchRow = 132;      // [row][k] operands read along k by lane%4: pitch = 4 mod 32
-constexpr int kPitchCol = 136;      // [k][n] operands read along n by lane/4: pitch = 8 mod 32
-constexpr int kPitchSq = 68;        // 64-wide [row][k] operands
-// Workspace record of one (chunk, value head), in bytes.  A1, A2 and A3 are images of tcgen05 shared-memory
-// operands: K-major, 32 TF32 elements (128 bytes) per row and k-block, [k-block][row][128 bytes], the 16-byte chunk
-// index of a row XORed with row % 8 (SWIZZLE_128B).
+constexpr int kPitchSq = 68;        // 64-wide FP32 matrices of the inversion: pitch = 4 mod 32 words
+// Workspace record of one (chunk, value head), in bytes.  A1 and A2 are images of K-major tcgen05 operands:
+// 32 TF32 elements (128 bytes) per row and k-block, [k-block][row][128 bytes], the 16-byte piece index of a row
+// XORed with row % 8 (SWIZZLE_128B).  A3 is the image of an MN-major operand (see mn_offset).
 constexpr std::uint32_t kRowBytes = 128;
 constexpr std::uint32_t kA1Block = 128 * kRowBytes;               // rows 0..63 Q, rows 64..127 W; 4 k-blocks
 constexpr std::uint32_t kA1Bytes = 4 * kA1Block;
 constexpr std::uint32_t kA2Block = kChunk * kRowBytes;            // P, 64 rows; 2 k-blocks
 constexpr std::uint32_t kA2Bytes = 2 * kA2Block;
-constexpr std::uint32_t kA3Block = kDim * kRowBytes;              // (K diag(e))^T, 128 rows; 2 k-blocks
-constexpr std::uint32_t kA3Bytes = 2 * kA3Block;
+constexpr std::uint32_t kA3AtomBytes = kChunk * kRowBytes;        // diag(e) K: 4 groups of 32 key dims x 64 tokens
+constexpr std::uint32_t kA3Bytes = 4 * kA3AtomBytes;
 constexpr int kPitchU = 36;                                        // U slice [64][36] FP32, then gamma [64]
 constexpr std::uint32_t kUBytes = (kChunk * kPitchU + kChunk) * 4;
 constexpr std::uint32_t kRecA1 = 0;
@@ -59,9 +59,14 @@ constexpr std::uint32_t kRecU = kRecA3 + kA3Bytes;                // [4 slices] 
 constexpr std::uint32_t kRecBytes = kRecU + (kDim / kSlice) * kUBytes;
 static_assert(kRecBytes % 16 == 0 && kUBytes % 16 == 0, "16-byte blocks");
 
-// Byte offset of element (row, k) inside an operand image whose k-blocks are block_bytes apart.
+// Byte offset of element (row, k) inside a K-major operand image whose k-blocks are block_bytes apart.
 __host__ __device__ constexpr std::uint32_t image_offset(std::uint32_t row, std::uint32_t k, std::uint32_t block_bytes) {
   return (k >> 5) * block_bytes + row * kRowBytes + ((((k & 31U) >> 2) ^ (row & 7U)) << 4) + ((k & 3U) << 2);
+}
+// Byte offset of element (token, dim) of a [token][128 dims] matrix stored as an MN-major operand: groups of 32
+// dims `atom_bytes` apart, inside a group one 128-byte row per token, the 32-byte piece index XORed with token % 4.
+__host__ __device__ constexpr std::uint32_t mn_offset(std::uint32_t token, std::uint32_t dim, std::uint32_t atom_bytes) {
+  return (dim >> 5) * atom_bytes + token * kRowBytes + ((((dim & 31U) >> 3) ^ (token & 3U)) << 5) + ((dim & 7U) << 2);
 }
 
 struct ChunkParams {
@@ -84,14 +89,7 @@ __device__ __forceinline__ std::uint32_t tf32(float x) {
   asm("cvt.rna.tf32.f32 %0, %1;\n" : "=r"(r) : "f"(x));
   return r;
 }
-
-__device__ __forceinline__ void mma_tf32(float (&c)[4], const std::uint32_t (&a)[4], std::uint32_t b0,
-                                         std::uint32_t b1) {
-  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-               "{%0,%1,%2,%3};\n"
-               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
+__device__ __forceinline__ float tf32f(float x) { return __uint_as_float(tf32(x)); }
 
 // Rows [tok0, tok0 + 64) of a [token][heads][128] operand (head `head`) go to dst[64][pitch] as FP32 in two halves,
 // so that other work can run while the loads are in flight: fetch_rows reads this thread's 32 elements of its row
@@ -174,296 +172,6 @@ __device__ long long g_gdn_trace[128 * 16];
   } while (0)
 #endif
 
-// ---- prepare: per (chunk, value head) ---------------------------------------------------------------
-constexpr int kPrepSmemFloats = kChunk * kPitchRow + kChunk * kPitchCol + 2 * kChunk * kPitchSq + 4 * kChunk;
-
-template <bool F32>
-__global__ void __launch_bounds__(256, 2) gdn_chunk_prepare_kernel(const ChunkParams p) {
-  extern __shared__ __align__(16) float prep_smem[];
-  float *sK = prep_smem;                      // [64][132]
-  float *sX = sK + kChunk * kPitchRow;        // [64][136]  Q, later V
-  float *sA = sX + kChunk * kPitchCol;        // [64][68]
-  float *sT = sA + kChunk * kPitchSq;         // [64][68]
-  float *sG = sT + kChunk * kPitchSq;         // [64] inclusive running log decay
-  float *sBeta = sG + kChunk;                 // [64]
-  float *sBg = sBeta + kChunk;                // [64] beta * exp(G)
-  float *sE = sBg + kChunk;                   // [64] exp(G_C - G)
-
-  const std::uint32_t chunk = blockIdx.x;
-  const std::uint32_t head = blockIdx.y;
-  const std::uint32_t key_head = head % p.key_heads;
-  const std::uint32_t tok0 = chunk * kChunk;
-  unsigned char *rec = p.workspace + (static_cast<std::size_t>(chunk) * p.value_heads + head) * kRecBytes;
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-  const int g = lane >> 2;
-  const int t = lane & 3;
-
-  if (threadIdx.x == 0 && blockIdx.x == 0) {
-    RIB200_GDN_STAMP(127, 0);
-  }
-  {
-    const RowRegs<F32> k_regs = fetch_rows<F32>(p.k, p.k_stride, key_head, tok0, p.tokens);
-    const RowRegs<F32> q_regs = fetch_rows<F32>(p.q, p.q_stride, key_head, tok0, p.tokens);
-    if (warp == 0) { // running sum of the log decays: two tokens per lane, warp scan
-      const std::uint32_t tok_a = tok0 + lane;
-      const std::uint32_t tok_b = tok_a + 32;
-      float a = tok_a < p.tokens ? p.log_decay[static_cast<std::size_t>(tok_a) * p.value_heads + head] : 0.0F;
-      float b = tok_b < p.tokens ? p.log_decay[static_cast<std::size_t>(tok_b) * p.value_heads + head] : 0.0F;
-#pragma unroll
-      for (int d = 1; d < 32; d <<= 1) {
-        const float ua = __shfl_up_sync(0xFFFFFFFFU, a, d);
-        const float ub = __shfl_up_sync(0xFFFFFFFFU, b, d);
-        if (lane >= d) {
-          a += ua;
-          b += ub;
-        }
-      }
-      b += __shfl_sync(0xFFFFFFFFU, a, 31);
-      sG[lane] = a;
-      sG[lane + 32] = b;
-    } else if (warp <= 2) {
-      const std::uint32_t tok = tok0 + lane + 32 * (warp - 1);
-      sBeta[lane + 32 * (warp - 1)] =
-          tok < p.tokens ? p.beta[static_cast<std::size_t>(tok) * p.value_heads + head] : 0.0F;
-    }
-    store_rows<F32>(sK, kPitchRow, k_regs);
-    store_rows<F32>(sX, kPitchRow, q_regs); // Q is read along k like K: same pitch; V will use the full pitch
-  }
-  __syncthreads();
-  if (threadIdx.x == 0 && blockIdx.x == 0) {
-    RIB200_GDN_STAMP(127, 1);
-  }
-  // Q rows of the [Q; W] operand image, rounded to TF32 (zero rows past the last token)
-  for (int i = threadIdx.x; i < kChunk * (kDim / 4); i += 256) {
-    const int r = i / (kDim / 4);
-    const int c = (i % (kDim / 4)) * 4;
-    const float4 qv = *reinterpret_cast<const float4 *>(sX + r * kPitchRow + c);
-    *reinterpret_cast<float4 *>(rec + kRecA1 + image_offset(r, c, kA1Block)) =
-        make_float4(__uint_as_float(tf32(qv.x)), __uint_as_float(tf32(qv.y)), __uint_as_float(tf32(qv.z)),
-                    __uint_as_float(tf32(qv.w)));
-  }
-  if (threadIdx.x < kChunk) {
-    const float gamma = expf(sG[threadIdx.x]);
-    sBg[threadIdx.x] = sBeta[threadIdx.x] * gamma;
-    sE[threadIdx.x] = expf(sG[kChunk - 1] - sG[threadIdx.x]);
-#pragma unroll
-    for (int slice = 0; slice < kDim / kSlice; ++slice) {
-      reinterpret_cast<float *>(rec + kRecU + slice * kUBytes)[kChunk * kPitchU + threadIdx.x] = gamma;
-    }
-  }
-
-  if (threadIdx.x == 0 && blockIdx.x == 0) {
-    RIB200_GDN_STAMP(127, 2);
-  }
-  // K K^T and Q K^T, 64 x 64 each, contraction over the 128 dims.  Warp: rows 16*(warp&3).., columns 32*(warp>>2)..
-  {
-    const int mt = warp & 3;
-    const int nt0 = (warp >> 2) * 4;
-    float acc_k[4][4] = {};
-    float acc_q[4][4] = {};
-#pragma unroll 4
-    for (int ks = 0; ks < 16; ++ks) {
-      std::uint32_t ak[4];
-      std::uint32_t aq[4];
-      const int col = ks * 8 + t;
-      ak[0] = tf32(sK[(16 * mt + g) * kPitchRow + col]);
-      ak[1] = tf32(sK[(16 * mt + g + 8) * kPitchRow + col]);
-      ak[2] = tf32(sK[(16 * mt + g) * kPitchRow + col + 4]);
-      ak[3] = tf32(sK[(16 * mt + g + 8) * kPitchRow + col + 4]);
-      aq[0] = tf32(sX[(16 * mt + g) * kPitchRow + col]);
-      aq[1] = tf32(sX[(16 * mt + g + 8) * kPitchRow + col]);
-      aq[2] = tf32(sX[(16 * mt + g) * kPitchRow + col + 4]);
-      aq[3] = tf32(sX[(16 * mt + g + 8) * kPitchRow + col + 4]);
-#pragma unroll
-      for (int n = 0; n < 4; ++n) {
-        const int j = 8 * (nt0 + n) + g;
-        const std::uint32_t b0 = tf32(sK[j * kPitchRow + col]);
-        const std::uint32_t b1 = tf32(sK[j * kPitchRow + col + 4]);
-        mma_tf32(acc_k[n], ak, b0, b1);
-        mma_tf32(acc_q[n], aq, b0, b1);
-      }
-    }
-#pragma unroll
-    for (int n = 0; n < 4; ++n) {
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        const int i = 16 * mt + g + half * 8;
-        const int j0 = 8 * (nt0 + n) + 2 * t;
-        float pv[2];
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int j = j0 + e;
-          const float decay = j <= i ? __expf(sG[i] - sG[j]) : 0.0F;
-          sA[i * kPitchSq + j] = j < i ? sBeta[i] * decay * acc_k[n][2 * half + e] : 0.0F;
-          pv[e] = __uint_as_float(tf32(decay * acc_q[n][2 * half + e]));
-        }
-        *reinterpret_cast<float2 *>(rec + kRecA2 + image_offset(i, j0, kA2Block)) = make_float2(pv[0], pv[1]);
-      }
-    }
-  }
-  __syncthreads();
-  if (threadIdx.x == 0 && blockIdx.x == 0) {
-    RIB200_GDN_STAMP(127, 3);
-  }
-
-  // V replaces Q; T = (I + A)^-1 by forward substitution in FP32.
-  const RowRegs<F32> v_regs = fetch_rows<F32>(p.v, p.v_stride, head, tok0, p.tokens); // lands during the substitution
-  if (threadIdx.x == 0 && blockIdx.x == 0) {
-    RIB200_GDN_STAMP(127, 4);
-  }
-  if (threadIdx.x < kChunk) {
-    // Two warps, a column of T per thread, all of it in registers: row i costs i multiply-adds in four
-    // independent chains and no exchange between lanes; only the term with T[i-1] waits for the row before.
-    const int c = threadIdx.x;
-    float tcol[kChunk];
-#pragma unroll
-    for (int i = 0; i < kChunk; ++i) {
-      tcol[i] = 0.0F;
-    }
-#pragma unroll
-    for (int i = 0; i < kChunk; ++i) {
-      float acc0 = 0.0F;
-      float acc1 = 0.0F;
-      float acc2 = 0.0F;
-      float acc3 = 0.0F;
-#pragma unroll
-      for (int j = 0; j < i; j += 4) { // A is zero on and above the diagonal, entries not yet known are zero
-        const float4 a = *reinterpret_cast<const float4 *>(sA + i * kPitchSq + j);
-        acc0 -= a.x * tcol[j];
-        acc1 -= a.y * tcol[j + 1];
-        acc2 -= a.z * tcol[j + 2];
-        acc3 -= a.w * tcol[j + 3];
-      }
-      tcol[i] = (i == c ? 1.0F : 0.0F) + ((acc0 + acc1) + (acc2 + acc3));
-    }
-#pragma unroll
-    for (int i = 0; i < kChunk; ++i) {
-      sT[i * kPitchSq + c] = tcol[i];
-    }
-    if (threadIdx.x == 0 && blockIdx.x == 0) {
-      RIB200_GDN_STAMP(127, 7);
-    }
-  } else {
-    // The other six warps meanwhile: their share of V, and the (K diag(e))^T operand image (row = key dim,
-    // k = token).  A thread gathers four tokens of one dim from sK; a warp covers 16 dims x 2 token quads per item,
-    // which reads 32 different banks and writes whole 32-byte sectors.
-    store_rows<F32>(sX, kPitchCol, v_regs);
-    for (int item = warp - 2; item < 64; item += 6) {
-      const int d = 16 * (item & 7) + (lane & 15);
-      const int j = 4 * (2 * (item >> 3) + (lane >> 4));
-      const float4 e4 = *reinterpret_cast<const float4 *>(sE + j);
-      *reinterpret_cast<float4 *>(rec + kRecA3 + image_offset(d, j, kA3Block)) =
-          make_float4(__uint_as_float(tf32(sK[j * kPitchRow + d] * e4.x)),
-                      __uint_as_float(tf32(sK[(j + 1) * kPitchRow + d] * e4.y)),
-                      __uint_as_float(tf32(sK[(j + 2) * kPitchRow + d] * e4.z)),
-                      __uint_as_float(tf32(sK[(j + 3) * kPitchRow + d] * e4.w)));
-    }
-    if (threadIdx.x == 64 && blockIdx.x == 0) {
-      RIB200_GDN_STAMP(127, 8);
-    }
-  }
-  if (threadIdx.x < kChunk) {
-    store_rows<F32>(sX, kPitchCol, v_regs);
-  }
-  __syncthreads();
-  if (threadIdx.x == 0 && blockIdx.x == 0) {
-    RIB200_GDN_STAMP(127, 5);
-  }
-
-  // W = T (diag(beta exp(G)) K), U = T (diag(beta) V): 64 x 128 each, contraction over the 64 tokens.
-  // Warp: rows 16*(warp&3).., columns 64*(warp>>2)...  T is lower triangular: k-steps above the tile are skipped.
-  {
-    const int mt = warp & 3;
-    const int n0 = (warp >> 2) * 64;
-    float acc_w[8][4] = {};
-    float acc_u[8][4] = {};
-    const int ks_end = 2 * mt + 2;
-    for (int ks = 0; ks < ks_end; ++ks) {
-      std::uint32_t a[4];
-      const int col = ks * 8 + t;
-      a[0] = tf32(sT[(16 * mt + g) * kPitchSq + col]);
-      a[1] = tf32(sT[(16 * mt + g + 8) * kPitchSq + col]);
-      a[2] = tf32(sT[(16 * mt + g) * kPitchSq + col + 4]);
-      a[3] = tf32(sT[(16 * mt + g + 8) * kPitchSq + col + 4]);
-      const float bg0 = sBg[col];
-      const float bg1 = sBg[col + 4];
-      const float be0 = sBeta[col];
-      const float be1 = sBeta[col + 4];
-#pragma unroll
-      for (int n = 0; n < 8; ++n) {
-        const int d = n0 + 8 * n + g;
-        mma_tf32(acc_w[n], a, tf32(sK[col * kPitchRow + d] * bg0), tf32(sK[(col + 4) * kPitchRow + d] * bg1));
-        mma_tf32(acc_u[n], a, tf32(sX[col * kPitchCol + d] * be0), tf32(sX[(col + 4) * kPitchCol + d] * be1));
-      }
-    }
-#pragma unroll
-    for (int n = 0; n < 8; ++n) {
-      const int d = n0 + 8 * n + 2 * t;
-      const int i = 16 * mt + g;
-      // W only ever feeds TF32 products: round it here, once
-      *reinterpret_cast<float2 *>(rec + kRecA1 + image_offset(kChunk + i, d, kA1Block)) =
-          make_float2(__uint_as_float(tf32(acc_w[n][0])), __uint_as_float(tf32(acc_w[n][1])));
-      *reinterpret_cast<float2 *>(rec + kRecA1 + image_offset(kChunk + i + 8, d, kA1Block)) =
-          make_float2(__uint_as_float(tf32(acc_w[n][2])), __uint_as_float(tf32(acc_w[n][3])));
-      float *u = reinterpret_cast<float *>(rec + kRecU + (d / kSlice) * kUBytes) + d % kSlice;
-      *reinterpret_cast<float2 *>(u + i * kPitchU) = make_float2(acc_u[n][0], acc_u[n][1]);
-      *reinterpret_cast<float2 *>(u + (i + 8) * kPitchU) = make_float2(acc_u[n][2], acc_u[n][3]);
-    }
-  }
-  if (threadIdx.x == 0 && blockIdx.x == 0) {
-    RIB200_GDN_STAMP(127, 6);
-  }
-}
-
-// ---- apply: per (state slice, value head), chunks in order ---------------------------------------------
-// 192 threads.  Warps 0-3 own the 128 lanes of tensor memory (thread = row of every product), warp 4 issues the
-// tcgen05 products (whole warp in step, one elected lane issuing), lane 0 of warp 5 streams the operand images of
-// each chunk into shared memory with bulk copies counted on mbarriers.  Per chunk:
-//   X  = [Q; W] S0            M 128 (rows 0..63 Q S0, rows 64..127 W S0), N 32, K 128
-//   warps 2-3: Delta = U - X[64..]  ->  B operand (TF32);   warps 0-1: keep gamma_i (Q S0)_i
-//   SD = (K diag(e))^T Delta  M 128, N 32, K 64
-//   O2 = P Delta              M 128 (rows 64..127 are don't-care), N 32, K 64
-//   all: S = gamma_C S + SD (FP32 registers) -> B operand (TF32): the next chunk's first product waits for this
-//   warps 0-1: O = gamma_i (Q S0)_i + O2, each row through shared memory and out with a bulk copy
-// Every mbarrier wait is bounded; when one runs out the CTA records RIB200_DEVICE_WAIT_TIMED_OUT, stops waiting
-// and copying, and runs to its end (its results are then meaningless, as the status word says).
-constexpr int kApplyThreads = 192;
-constexpr std::uint32_t kSmA1 = 0;                         // two stages of the [Q; W] image
-constexpr std::uint32_t kSmA23 = kSmA1 + 2 * kA1Bytes;     // P image, then the (K diag(e))^T image
-constexpr std::uint32_t kSmB1 = kSmA23 + kA2Bytes + kA3Bytes; // S^T, [4 k-blocks][32 rows][128 bytes]
-constexpr std::uint32_t kB1Block = kSlice * kRowBytes;
-constexpr std::uint32_t kSmBD = kSmB1 + 4 * kB1Block;      // Delta^T, [2 k-blocks][32 rows][128 bytes]
-constexpr std::uint32_t kSmU = kSmBD + 2 * kB1Block;       // two stages of U slice + gamma
-constexpr std::uint32_t kUStage = 10240;                   // stage stride: the output tile that reuses a stage wants 1 KiB alignment
-constexpr std::uint32_t kSmBars = kSmU + 2 * kUStage;
-enum : std::uint32_t {
-  kBarA1Full = 0,   // [2] bytes of a [Q; W] image
-  kBarA1Empty = 2,  // [2] the product that read it has completed
-  kBarA23Full = 4,
-  kBarA23Empty = 5,
-  kBarUFull = 6,    // [2]
-  kBarUEmpty = 8,   // [2] 128 readers
-  kBarXDone = 10,   // X is in tensor memory
-  kBarDReady = 11,  // Delta^T is in shared memory (64 writers)
-  kBarSdDone = 12,  // SD is in tensor memory
-  kBarSReady = 13,  // S^T is in shared memory, X and SD have been read (128 threads)
-  kBarO2Done = 14,  // O2 is in tensor memory
-  kBarO2Free = 15,  // O2 has been read (64 threads)
-  kBarCount = 16
-};
-constexpr std::uint32_t kSmTmemSlot = kSmBars + kBarCount * 8;
-constexpr std::uint32_t kSmAbort = kSmTmemSlot + 4;
-constexpr std::uint32_t kApplySmemBytes = kSmAbort + 4 + 1024; // + room to align the base to 1 KiB
-static_assert(kUStage >= kUBytes && kSmA23 % 1024 == 0 && kSmB1 % 1024 == 0 && kSmBD % 1024 == 0 && kSmU % 1024 == 0 &&
-                  kSmBars % 8 == 0,
-              "operand images sit on 1 KiB boundaries");
-static_assert(kApplySmemBytes <= 232448, "apply kernel exceeds the shared memory of an SM");
-constexpr long long kWaitLimitCycles = 1LL << 28;
-constexpr std::uint32_t kTmemColumns = 128; // X at 0, O2 at 32, SD at 64
-constexpr std::uint32_t kPrefetchAhead = 3;   // chunks between an L2 prefetch and the copy that uses it
-constexpr std::uint32_t kCopyPiece = 16384;  // the operand images come in as several bulk copies in flight at once
-
 __device__ __forceinline__ std::uint32_t smem_address(const void *p) {
   return static_cast<std::uint32_t>(__cvta_generic_to_shared(p));
 }
@@ -494,6 +202,11 @@ __device__ __forceinline__ void bulk_copy_g2s(std::uint32_t dst, const void *src
                "l"(src), "r"(bytes), "r"(bar)
                : "memory");
 }
+// bulk copy shared -> global, completion tracked by the issuing thread's bulk groups
+__device__ __forceinline__ void bulk_copy_s2g(void *dst, std::uint32_t src, std::uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;\n" ::"l"(dst), "r"(src), "r"(bytes)
+               : "memory");
+}
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
@@ -517,17 +230,36 @@ __device__ __forceinline__ std::uint64_t smem_desc(std::uint32_t addr) {
   d |= static_cast<std::uint64_t>(2) << 61;            // SWIZZLE_128B
   return d;
 }
-// Instruction descriptor: TF32 x TF32 -> FP32, both operands K-major, M 128, N 32.
-constexpr std::uint32_t kIdesc = (1U << 4) | (2U << 7) | (2U << 10) | (static_cast<std::uint32_t>(kSlice >> 3) << 17) |
-                                 (static_cast<std::uint32_t>(128 >> 4) << 24);
+// Shared-memory matrix descriptor of an operand whose M (or N) index is the contiguous one ("MN-major"), 32-bit
+// elements: rows of 128 bytes hold 32 consecutive M/N elements of one k index, four such rows (512 bytes) form an
+// atom inside which the 32-byte piece index is XORed with the row index (the 32-byte-base form of the 128-byte
+// swizzle, the only MN-major form for 32-bit elements); atoms follow each other `k_atom_bytes` apart along k and
+// `mn_atom_bytes` apart along M/N.
+__device__ __forceinline__ std::uint64_t smem_desc_mn(std::uint32_t addr, std::uint32_t mn_atom_bytes,
+                                                      std::uint32_t k_atom_bytes) {
+  std::uint64_t d = 0;
+  d |= static_cast<std::uint64_t>((addr & 0x3FFFFU) >> 4);
+  d |= static_cast<std::uint64_t>(mn_atom_bytes >> 4) << 16; // leading-dimension offset: between M/N atoms
+  d |= static_cast<std::uint64_t>(k_atom_bytes >> 4) << 32;  // stride offset: between k atoms
+  d |= static_cast<std::uint64_t>(1) << 46;                  // version
+  d |= static_cast<std::uint64_t>(1) << 61;                  // SWIZZLE_128B with a 32-byte base
+  return d;
+}
+// Instruction descriptor: TF32 x TF32 -> FP32, M 128, N columns; bit 15 / bit 16 mark an MN-major A / B operand.
+__host__ __device__ constexpr std::uint32_t idesc_tf32(std::uint32_t n, bool a_mn_major, bool b_mn_major) {
+  return (1U << 4) | (2U << 7) | (2U << 10) | (a_mn_major ? 1U << 15 : 0U) | (b_mn_major ? 1U << 16 : 0U) |
+         ((n >> 3) << 17) | (static_cast<std::uint32_t>(128 >> 4) << 24);
+}
+constexpr std::uint32_t kIdesc = idesc_tf32(kSlice, false, false);
+constexpr std::uint32_t kIdescMnA = idesc_tf32(kSlice, true, false);
 __device__ __forceinline__ void umma_tf32(std::uint32_t d_tmem, std::uint64_t a_desc, std::uint64_t b_desc,
-                                          std::uint32_t accumulate) {
+                                          std::uint32_t accumulate, std::uint32_t idesc = kIdesc) {
   asm volatile("{\n"
                ".reg .pred p;\n"
                "setp.ne.b32 p, %4, 0;\n"
                "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n"
                "}\n" ::"r"(d_tmem),
-               "l"(a_desc), "l"(b_desc), "r"(kIdesc), "r"(accumulate)
+               "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
                : "memory");
 }
 __device__ __forceinline__ void umma_commit(std::uint32_t bar) {
@@ -569,6 +301,612 @@ __device__ __forceinline__ float4 lds128(std::uint32_t addr) {
   asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
   return v;
 }
+
+// ---- prepare: per (chunk, value head), persistent CTAs --------------------------------------------------
+// 512 threads.  Thread (row = tid / 8, part = tid % 8) owns dims 64 a + 8 part .. + 7 (a = 0, 1) of token `row` of
+// K, Q and V; the rows of the next item are already in flight while the current one is worked on.  Per item:
+//   images   K and Q rounded to TF32 into the K-major image [K; Q] (A and B of the first product); K and V into
+//            MN-major images (B of the last two); Q and diag(e) K also go to the workspace record from registers
+//   G        = [K; Q] K^T            M 128, N 64, K 128   -> rows 0..63 K K^T, rows 64..127 Q K^T
+//   rows 0..63: A = beta_i decay_ij (K K^T)_ij below the diagonal -> shared memory;  rows 64..127: P -> record
+//            (a warp reads 32 rows x 16 columns of tensor memory; decay_ij = exp(G_i - G_j) is one exponential per
+//            element only inside the diagonal 16 x 16 blocks, elsewhere the product of a row and a column factor
+//            taken against the running sum at the end of the column block, both <= 1)
+//   T        = (I + A)^-1 in FP32, all warps
+//   [W; *]   = [T diag(beta gamma); T diag(beta)] K      M 128, N 128, K 64   (rows 0..63 are W)
+//   [*; U]   = [T diag(beta gamma); T diag(beta)] V      M 128, N 128, K 64   (rows 64..127 are U)
+//   rows 0..63: W -> record (TF32 image);  rows 64..127: U, gamma -> record (a warp reads 32 rows x 32 columns)
+// Record pieces leave through shared-memory staging and bulk copies.  Every mbarrier wait is bounded as in the
+// apply kernel.
+constexpr int kPrepThreads = 512;
+constexpr std::uint32_t kPsKQ = 0;                          // [K; Q] image, 64 KiB; later:
+constexpr std::uint32_t kPsTstack = kPsKQ;                  //   [T diag(beta gamma); T diag(beta)] image, 32 KiB
+constexpr std::uint32_t kPsWstage = kPsKQ;                  //   W image on its way to the record, 32 KiB
+constexpr std::uint32_t kPsKb = 65536;                      // K as an MN-major operand, 32 KiB
+constexpr std::uint32_t kPsVb = kPsKb + 32768;              // V as an MN-major operand, 32 KiB
+constexpr std::uint32_t kPsUstage = kPsKb;                  //   later: the four U slices on their way to the record
+constexpr std::uint32_t kPsKe = kPsVb + 32768;              // diag(e) K on its way to the record, 32 KiB
+constexpr std::uint32_t kPsPstage = kPsKe + 32768;          // P image on its way to the record, 16 KiB
+constexpr std::uint32_t kPsA = kPsPstage + 16384;           // A, FP32 [64][68]
+constexpr std::uint32_t kPsT = kPsA + kChunk * kPitchSq * 4; // T, FP32 [64][68]
+constexpr std::uint32_t kPsVec = kPsT + kChunk * kPitchSq * 4; // G, beta, beta gamma, column factors: 4 x 64 floats
+constexpr std::uint32_t kPsBars = kPsVec + 1024;
+constexpr std::uint32_t kPsTmemSlot = kPsBars + 16;
+constexpr std::uint32_t kPsAbort = kPsTmemSlot + 4;
+constexpr std::uint32_t kPrepSmemBytes = kPsAbort + 4 + 1024; // + room to align the base to 1 KiB
+static_assert((kDim / kSlice) * kUBytes <= 65536 && kPsA % 16 == 0 && kPsBars % 8 == 0, "staging fits, alignment");
+static_assert(kPrepSmemBytes <= 232448, "prepare kernel exceeds the shared memory of an SM");
+constexpr long long kPrepWaitLimitCycles = 1LL << 28;
+constexpr std::uint32_t kPrepTmemColumns = 512;  // G at 0 (64 columns), [W; *] at 64, [*; U] at 192
+constexpr std::uint32_t kIdescG = idesc_tf32(kChunk, false, false);
+constexpr std::uint32_t kIdescWU = idesc_tf32(kDim, false, true);
+
+// Two 8-element pieces of one row per thread: FP32 inputs take four 16-byte words, BF16 inputs two.
+template <bool F32> struct HalfRowRegs {
+  uint4 v[F32 ? 4 : 2];
+};
+template <bool F32> struct ItemRegs {
+  HalfRowRegs<F32> k, q, v;
+  float gate;  // warp 0: log decay of token lane; warp 1: beta of token lane; warp 2: beta of token lane + 32
+  float gate2; // warp 0: log decay of token lane + 32
+};
+
+// Pieces `part` and `part + 8` of row tok0 + tid / 8 of a [token][heads][128] operand.  Rows at or past `tokens`
+// read the last row instead (the caller discards them when it unpacks): the function is loads and nothing that
+// waits for them, so that a call made an item ahead really runs ahead.
+template <bool F32>
+__device__ __forceinline__ HalfRowRegs<F32> fetch_half_rows(const void *src, std::size_t stride, std::uint32_t head,
+                                                            std::uint32_t tok0, std::uint32_t tokens) {
+  HalfRowRegs<F32> regs;
+  const std::uint32_t tok = min(tok0 + (threadIdx.x >> 3), tokens - 1);
+  const std::size_t first = static_cast<std::size_t>(tok) * stride + head * kDim + (threadIdx.x & 7U) * 8;
+#pragma unroll
+  for (int a = 0; a < 2; ++a) {
+    if constexpr (F32) {
+      const uint4 *s = reinterpret_cast<const uint4 *>(static_cast<const float *>(src) + first + 64 * a);
+      regs.v[2 * a] = s[0];
+      regs.v[2 * a + 1] = s[1];
+    } else {
+      regs.v[a] = *reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(src) + first + 64 * a);
+    }
+  }
+  return regs;
+}
+
+// the eight values of piece `a` of a fetched row; all zero when the row lies past the last token
+template <bool F32>
+__device__ __forceinline__ void unpack_piece(const HalfRowRegs<F32> &regs, int a, bool live, float (&f)[8]) {
+  if constexpr (F32) {
+    const uint4 lo = regs.v[2 * a];
+    const uint4 hi = regs.v[2 * a + 1];
+    f[0] = __uint_as_float(lo.x); f[1] = __uint_as_float(lo.y); f[2] = __uint_as_float(lo.z); f[3] = __uint_as_float(lo.w);
+    f[4] = __uint_as_float(hi.x); f[5] = __uint_as_float(hi.y); f[6] = __uint_as_float(hi.z); f[7] = __uint_as_float(hi.w);
+  } else {
+    const std::uint32_t w[4] = {regs.v[a].x, regs.v[a].y, regs.v[a].z, regs.v[a].w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000U);
+    }
+  }
+  if (!live) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      f[i] = 0.0F;
+    }
+  }
+}
+
+__device__ __forceinline__ void tmem_ld16(std::uint32_t taddr, float (&v)[16]) {
+  std::uint32_t r[16];
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+               "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+               : "r"(taddr)
+               : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    v[i] = __uint_as_float(r[i]);
+  }
+}
+
+template <bool F32>
+__global__ void __launch_bounds__(kPrepThreads, 1) gdn_chunk_prepare_kernel(const ChunkParams p) {
+  extern __shared__ unsigned char prep_smem_raw[];
+  const std::uint32_t base = (smem_address(prep_smem_raw) + 1023U) & ~1023U;
+  unsigned char *smem = prep_smem_raw + (base - smem_address(prep_smem_raw));
+  float *sA = reinterpret_cast<float *>(smem + kPsA);
+  float *sT = reinterpret_cast<float *>(smem + kPsT);
+  float *sG = reinterpret_cast<float *>(smem + kPsVec);  // inclusive running log decay
+  float *sBeta = sG + kChunk;
+  float *sBg = sBeta + kChunk;                            // beta * exp(G)
+  float *sCf = sBg + kChunk;                              // exp(G at the end of the token's block of 16 - G)
+  const std::uint32_t bar_g = base + kPsBars;
+  const std::uint32_t bar_wu = base + kPsBars + 8;
+  volatile std::uint32_t *tmem_slot = reinterpret_cast<volatile std::uint32_t *>(smem + kPsTmemSlot);
+  volatile std::uint32_t *abort_flag = reinterpret_cast<volatile std::uint32_t *>(smem + kPsAbort);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const std::uint32_t row = tid >> 3;
+  const std::uint32_t part = tid & 7;
+  const std::uint32_t items = p.chunks * p.value_heads;
+
+  if (tid == 0) {
+    mbarrier_init(bar_g, 1);
+    mbarrier_init(bar_wu, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  if (warp == 4) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(base + kPsTmemSlot),
+                 "r"(kPrepTmemColumns)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const std::uint32_t tmem = *tmem_slot;
+  const bool issuer = warp == 4 && elect_one();
+  // One lane of the last warp issues every bulk copy to the record (bulk groups belong to the issuing thread) and
+  // waits for them to have read their staging areas before those are written again.
+  const bool copier = tid == kPrepThreads - 32;
+
+  auto wait = [&](std::uint32_t b, std::uint32_t parity) {
+    if (*abort_flag != 0 || mbarrier_try_wait(b, parity)) {
+      return;
+    }
+    const long long started = clock64();
+    while (!mbarrier_try_wait(b, parity)) {
+      if (*abort_flag != 0) {
+        return;
+      }
+      if (clock64() - started > kPrepWaitLimitCycles) {
+        *abort_flag = 1;
+        atomicOr(p.status, static_cast<unsigned int>(RIB200_DEVICE_WAIT_TIMED_OUT));
+        return;
+      }
+    }
+  };
+
+  auto fetch = [&](std::uint32_t item) {
+    ItemRegs<F32> regs;
+    const std::uint32_t chunk = item / p.value_heads;
+    const std::uint32_t head = item % p.value_heads;
+    const std::uint32_t key_head = head % p.key_heads;
+    const std::uint32_t tok0 = chunk * kChunk;
+    regs.k = fetch_half_rows<F32>(p.k, p.k_stride, key_head, tok0, p.tokens);
+    regs.q = fetch_half_rows<F32>(p.q, p.q_stride, key_head, tok0, p.tokens);
+    regs.v = fetch_half_rows<F32>(p.v, p.v_stride, head, tok0, p.tokens);
+    // gates of tokens at or past `tokens` are read from the last token and discarded by the consumer
+    const std::uint32_t last = p.tokens - 1;
+    const std::uint32_t tok_a = min(tok0 + lane + 32 * (warp == 2 ? 1 : 0), last);
+    const std::uint32_t tok_b = min(tok0 + lane + 32, last);
+    const float *gates = warp == 0 ? p.log_decay : p.beta;
+    regs.gate = gates[static_cast<std::size_t>(tok_a) * p.value_heads + head];
+    regs.gate2 = gates[static_cast<std::size_t>(tok_b) * p.value_heads + head];
+    return regs;
+  };
+
+  // Rows of an item are pulled into L2 while the item before it is worked on (a prefetch has no destination
+  // register, so nothing in between ever waits for it); the loads at the top of the item then find them there.
+  auto prefetch = [&](std::uint32_t item) {
+    constexpr std::uint32_t kLines = F32 ? 4 : 2; // 128-byte lines per row of one head
+    const std::uint32_t chunk = item / p.value_heads;
+    const std::uint32_t head = item % p.value_heads;
+    const std::uint32_t key_head = head % p.key_heads;
+    const std::size_t tok = min(chunk * kChunk + row, p.tokens - 1);
+    if (part >= 6) { // the token's two gates
+      const float *gates = part == 6 ? p.beta : p.log_decay;
+      asm volatile("prefetch.global.L2 [%0];\n" ::"l"(gates + tok * p.value_heads + head));
+    }
+    if (part >= kLines) {
+      return;
+    }
+    constexpr std::size_t kElement = F32 ? 4 : 2;
+    const char *k_line = static_cast<const char *>(p.k) + (tok * p.k_stride + key_head * kDim) * kElement + part * 128;
+    const char *q_line = static_cast<const char *>(p.q) + (tok * p.q_stride + key_head * kDim) * kElement + part * 128;
+    const char *v_line = static_cast<const char *>(p.v) + (tok * p.v_stride + head * kDim) * kElement + part * 128;
+    asm volatile("prefetch.global.L2 [%0];\n" ::"l"(k_line));
+    asm volatile("prefetch.global.L2 [%0];\n" ::"l"(q_line));
+    asm volatile("prefetch.global.L2 [%0];\n" ::"l"(v_line));
+  };
+  ItemRegs<F32> cur;
+  std::uint32_t iteration = 0;
+  for (std::uint32_t item = blockIdx.x; item < items; item += gridDim.x, ++iteration) {
+    const std::uint32_t phase = iteration & 1U;
+    cur = fetch(item);
+    if (item + gridDim.x < items) {
+      prefetch(item + gridDim.x);
+    }
+    unsigned char *rec = p.workspace + static_cast<std::size_t>(item) * kRecBytes; // item = chunk * value_heads + head
+
+    // ---- gates: running sum of the log decays (two tokens per lane, warp scan), beta ----
+    const std::uint32_t tok0 = (item / p.value_heads) * kChunk;
+    if (warp == 0) {
+      float a = tok0 + lane < p.tokens ? cur.gate : 0.0F;
+      float b = tok0 + lane + 32 < p.tokens ? cur.gate2 : 0.0F;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const float ua = __shfl_up_sync(0xFFFFFFFFU, a, d);
+        const float ub = __shfl_up_sync(0xFFFFFFFFU, b, d);
+        if (lane >= d) {
+          a += ua;
+          b += ub;
+        }
+      }
+      b += __shfl_sync(0xFFFFFFFFU, a, 31);
+      sG[lane] = a;
+      sG[lane + 32] = b;
+    } else if (warp <= 2) {
+      sBeta[lane + 32 * (warp - 1)] = tok0 + lane + 32 * (warp - 1) < p.tokens ? cur.gate : 0.0F;
+    }
+    if (copier) { // the previous item's W and U copies must have read their staging areas
+      asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
+    }
+    __syncthreads();
+    if (tid < kChunk) {
+      sBg[tid] = sBeta[tid] * __expf(sG[tid]);
+      sCf[tid] = __expf(sG[tid | 15] - sG[tid]);
+    }
+
+    // ---- operand images ----
+    {
+      const float e_row = __expf(sG[kChunk - 1] - sG[row]); // exp(G_C - G_row) <= 1
+      const bool live = tok0 + row < p.tokens;
+      // A piece is two 16-byte stores.  The eight lanes that store together are the eight parts of one row; parts
+      // p and p + 4 fall into the same banks (their k-blocks lie 16 KiB apart), so parts 4..7 store their second
+      // half first.
+      const bool swap = (part & 4U) != 0;
+      auto store_piece = [&](std::uint32_t first, std::uint32_t second, const float (&f)[8]) {
+        const std::uint32_t o0 = swap ? second : first;
+        const std::uint32_t o1 = swap ? first : second;
+        sts128(o0, swap ? f[4] : f[0], swap ? f[5] : f[1], swap ? f[6] : f[2], swap ? f[7] : f[3]);
+        sts128(o1, swap ? f[0] : f[4], swap ? f[1] : f[5], swap ? f[2] : f[6], swap ? f[3] : f[7]);
+      };
+#pragma unroll
+      for (int a = 0; a < 2; ++a) {
+        const std::uint32_t dim = 64 * a + 8 * part;
+        const std::uint32_t mn = mn_offset(row, dim, kA3AtomBytes); // the eight dims are one 32-byte piece
+        float f[8];
+        float scaled[8];
+        unpack_piece<F32>(cur.k, a, live, f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          f[i] = tf32f(f[i]);
+          scaled[i] = tf32f(f[i] * e_row);
+        }
+        store_piece(base + kPsKQ + image_offset(row, dim, kA1Block), base + kPsKQ + image_offset(row, dim + 4, kA1Block), f);
+        store_piece(base + kPsKb + mn, base + kPsKb + mn + 16, f);
+        store_piece(base + kPsKe + mn, base + kPsKe + mn + 16, scaled);
+
+        unpack_piece<F32>(cur.q, a, live, f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          f[i] = tf32f(f[i]);
+        }
+        store_piece(base + kPsKQ + image_offset(kChunk + row, dim, kA1Block),
+                    base + kPsKQ + image_offset(kChunk + row, dim + 4, kA1Block), f);
+
+        unpack_piece<F32>(cur.v, a, live, f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          f[i] = tf32f(f[i]);
+        }
+        store_piece(base + kPsVb + mn, base + kPsVb + mn + 16, f);
+      }
+    }
+    fence_proxy_async();
+    tcgen05_fence_before();
+    __syncthreads();
+
+    // ---- G = [K; Q] K^T ----
+    if (copier && *abort_flag == 0) {
+      // Q is rows 64..127 of every k-block of the [K; Q] image and rows 0..63 of the record's [Q; W] image
+#pragma unroll
+      for (std::uint32_t kb = 0; kb < 4; ++kb) {
+        bulk_copy_s2g(rec + kRecA1 + kb * kA1Block, base + kPsKQ + kb * kA1Block + kChunk * kRowBytes, kChunk * kRowBytes);
+      }
+      bulk_copy_s2g(rec + kRecA3, base + kPsKe, kA3Bytes);
+      asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+    }
+    if (warp == 4) {
+      tcgen05_fence_after();
+      if (issuer && *abort_flag == 0) {
+        const std::uint64_t kq_desc = smem_desc(base + kPsKQ);
+#pragma unroll
+        for (std::uint32_t ks = 0; ks < 16; ++ks) {
+          const std::uint64_t step = static_cast<std::uint64_t>(((ks >> 2) * kA1Block + (ks & 3U) * 32U) >> 4);
+          umma_tf32(tmem, kq_desc + step, kq_desc + step, ks, kIdescG);
+        }
+        umma_commit(bar_g);
+      }
+      __syncwarp();
+    }
+
+    // ---- rows of G: A (lower triangle, to shared memory) and P (to its staging image) ----
+    {
+      wait(bar_g, phase);
+      tcgen05_fence_after();
+      const std::uint32_t quarter = warp & 3;       // the 32 tensor-memory lanes this warp may read
+      const std::uint32_t cg = warp >> 2;           // its 16 columns
+      const std::uint32_t lane_base = (quarter * 32U) << 16;
+      const std::uint32_t i = (quarter & 1U) * 32 + lane; // token of the row
+      const bool is_p = quarter >= 2;               // rows 64..127 hold Q K^T
+      float g[16];
+      tmem_ld16(tmem + lane_base + 16 * cg, g);
+      const float g_i = sG[i];
+      const float scale_i = is_p ? 1.0F : sBeta[i];
+      float out[16];
+      if (16 * cg > i) {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          out[e] = 0.0F;
+        }
+      } else if ((i >> 4) == cg) { // diagonal block: one exponential per element
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          const std::uint32_t j = 16 * cg + e;
+          const bool live = is_p ? j <= i : j < i;
+          out[e] = live ? scale_i * __expf(g_i - sG[j]) * g[e] : 0.0F;
+        }
+      } else { // below it: exp(G_i - G_j) = exp(G_i - R) exp(R - G_j), R the running sum at the end of the column block
+        const float row_factor = scale_i * __expf(g_i - sG[16 * cg + 15]);
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          out[e] = row_factor * sCf[16 * cg + e] * g[e];
+        }
+      }
+      if (!is_p) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          *reinterpret_cast<float4 *>(sA + i * kPitchSq + 16 * cg + 4 * c) =
+              make_float4(out[4 * c], out[4 * c + 1], out[4 * c + 2], out[4 * c + 3]);
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          sts128(base + kPsPstage + image_offset(i, 16 * cg + 4 * c, kA2Block), tf32f(out[4 * c]), tf32f(out[4 * c + 1]),
+                 tf32f(out[4 * c + 2]), tf32f(out[4 * c + 3]));
+        }
+      }
+      fence_proxy_async();
+      tcgen05_fence_before();
+    }
+    __syncthreads();
+    if (copier && *abort_flag == 0) {
+      bulk_copy_s2g(rec + kRecA2, base + kPsPstage, kA2Bytes);
+      asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+    }
+
+    // ---- T = (I + A)^-1: diagonal 16 x 16 blocks by forward substitution, a column per thread ... ----
+    if (tid < kChunk) {
+      const int b = tid >> 4;
+      const int c = tid & 15;
+      float tcol[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        float acc = i == c ? 1.0F : 0.0F;
+        const float *a_row = sA + (16 * b + i) * kPitchSq + 16 * b;
+#pragma unroll
+        for (int j = 0; j < i; ++j) {
+          acc -= a_row[j] * tcol[j];
+        }
+        tcol[i] = acc;
+      }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        sT[(16 * b + i) * kPitchSq + 16 * b + c] = tcol[i];
+      }
+    } else {
+      // ... while the other threads clear the blocks above the diagonal
+      for (int e = tid - kChunk; e < 6 * 256; e += kPrepThreads - kChunk) {
+        const int blk = e >> 8; // (0,1) (0,2) (0,3) (1,2) (1,3) (2,3)
+        const int bi = blk < 3 ? 0 : (blk < 5 ? 1 : 2);
+        const int bj = blk < 3 ? blk + 1 : (blk < 5 ? blk - 1 : 3);
+        sT[(16 * bi + ((e >> 4) & 15)) * kPitchSq + 16 * bj + (e & 15)] = 0.0F;
+      }
+    }
+    __syncthreads();
+    // ... then block (i, b) below the diagonal, one sub-diagonal at a time:
+    //   T_ib = -T_ii (sum over k = b .. i-1 of A_ik T_kb).
+    // A warp owns a whole block: lane (pair = lane / 4, quad = lane % 4) computes rows 2 pair, 2 pair + 1 and columns
+    // 4 quad .. + 3 of it, so a k step is two scalar loads of A, one 16-byte load of T and eight multiply-adds, and
+    // the intermediate sum goes through the block's own place in shared memory with warp-level ordering only.
+    {
+      const int pair = lane >> 2;
+      const int quad = lane & 3;
+#pragma unroll
+      for (int d = 1; d < 4; ++d) {
+        const int b = warp;
+        const int i = b + d;
+        if (i < 4) {
+          float y0[4] = {0.0F, 0.0F, 0.0F, 0.0F};
+          float y1[4] = {0.0F, 0.0F, 0.0F, 0.0F};
+          const float *a0 = sA + (16 * i + 2 * pair) * kPitchSq;
+          const float *a1 = a0 + kPitchSq;
+          const float *t_col = sT + 16 * b + 4 * quad;
+#pragma unroll 4
+          for (int k = 16 * b; k < 16 * i; ++k) {
+            const float4 t4 = *reinterpret_cast<const float4 *>(t_col + k * kPitchSq);
+            const float x0 = a0[k];
+            const float x1 = a1[k];
+            y0[0] += x0 * t4.x; y0[1] += x0 * t4.y; y0[2] += x0 * t4.z; y0[3] += x0 * t4.w;
+            y1[0] += x1 * t4.x; y1[1] += x1 * t4.y; y1[2] += x1 * t4.z; y1[3] += x1 * t4.w;
+          }
+          float *block = sT + (16 * i) * kPitchSq + 16 * b + 4 * quad;
+          *reinterpret_cast<float4 *>(block + (2 * pair) * kPitchSq) = make_float4(y0[0], y0[1], y0[2], y0[3]);
+          *reinterpret_cast<float4 *>(block + (2 * pair + 1) * kPitchSq) = make_float4(y1[0], y1[1], y1[2], y1[3]);
+          __syncwarp();
+          float z0[4] = {0.0F, 0.0F, 0.0F, 0.0F};
+          float z1[4] = {0.0F, 0.0F, 0.0F, 0.0F};
+          const float *d0 = sT + (16 * i + 2 * pair) * kPitchSq + 16 * i; // T_ii is lower triangular: zeros above
+          const float *d1 = d0 + kPitchSq;
+#pragma unroll 4
+          for (int m = 0; m < 16; ++m) {
+            const float4 y4 = *reinterpret_cast<const float4 *>(block + m * kPitchSq);
+            const float x0 = d0[m];
+            const float x1 = d1[m];
+            z0[0] -= x0 * y4.x; z0[1] -= x0 * y4.y; z0[2] -= x0 * y4.z; z0[3] -= x0 * y4.w;
+            z1[0] -= x1 * y4.x; z1[1] -= x1 * y4.y; z1[2] -= x1 * y4.z; z1[3] -= x1 * y4.w;
+          }
+          __syncwarp();
+          *reinterpret_cast<float4 *>(block + (2 * pair) * kPitchSq) = make_float4(z0[0], z0[1], z0[2], z0[3]);
+          *reinterpret_cast<float4 *>(block + (2 * pair + 1) * kPitchSq) = make_float4(z1[0], z1[1], z1[2], z1[3]);
+        }
+        if (d == 3 && copier) {
+          // what follows overwrites the Q rows of the [K; Q] image: their copies to the record must have read them
+          asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
+        }
+        __syncthreads();
+      }
+    }
+
+    // ---- [T diag(beta gamma); T diag(beta)] as one K-major image (the first product has completed, and the copies
+    // of the Q rows, issued long ago, have read them: thread 0 made sure before the barrier above) ----
+    {
+      const std::uint32_t j0 = 8 * part;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const float4 t4 = *reinterpret_cast<const float4 *>(sT + row * kPitchSq + j0 + 4 * c);
+        const float4 bg = *reinterpret_cast<const float4 *>(sBg + j0 + 4 * c);
+        const float4 be = *reinterpret_cast<const float4 *>(sBeta + j0 + 4 * c);
+        sts128(base + kPsTstack + image_offset(row, j0 + 4 * c, kA1Block), tf32f(t4.x * bg.x), tf32f(t4.y * bg.y),
+               tf32f(t4.z * bg.z), tf32f(t4.w * bg.w));
+        sts128(base + kPsTstack + image_offset(kChunk + row, j0 + 4 * c, kA1Block), tf32f(t4.x * be.x),
+               tf32f(t4.y * be.y), tf32f(t4.z * be.z), tf32f(t4.w * be.w));
+      }
+    }
+    fence_proxy_async();
+    tcgen05_fence_before();
+    __syncthreads();
+
+    // ---- the two products with T: B operands are K and V as stored (eight tokens = 1 KiB per step) ----
+    if (warp == 4) {
+      tcgen05_fence_after();
+      if (issuer && *abort_flag == 0) {
+        const std::uint64_t t_desc = smem_desc(base + kPsTstack);
+        const std::uint64_t kb_desc = smem_desc_mn(base + kPsKb, kA3AtomBytes, 512);
+        const std::uint64_t vb_desc = smem_desc_mn(base + kPsVb, kA3AtomBytes, 512);
+#pragma unroll
+        for (std::uint32_t ks = 0; ks < 8; ++ks) {
+          const std::uint64_t a_step = static_cast<std::uint64_t>(((ks >> 2) * kA1Block + (ks & 3U) * 32U) >> 4);
+          umma_tf32(tmem + 64, t_desc + a_step, kb_desc + static_cast<std::uint64_t>(ks * 1024U >> 4), ks, kIdescWU);
+        }
+#pragma unroll
+        for (std::uint32_t ks = 0; ks < 8; ++ks) {
+          const std::uint64_t a_step = static_cast<std::uint64_t>(((ks >> 2) * kA1Block + (ks & 3U) * 32U) >> 4);
+          umma_tf32(tmem + 192, t_desc + a_step, vb_desc + static_cast<std::uint64_t>(ks * 1024U >> 4), ks, kIdescWU);
+        }
+        umma_commit(bar_wu);
+      }
+      __syncwarp();
+    }
+
+    // ---- W (rows 0..63 of the first) and U (rows 64..127 of the second) to their staging images ----
+    {
+      wait(bar_wu, phase);
+      tcgen05_fence_after();
+      const std::uint32_t quarter = warp & 3;
+      const std::uint32_t cg = warp >> 2;           // 32 columns: k-block `cg` of W, slice `cg` of U
+      const std::uint32_t lane_base = (quarter * 32U) << 16;
+      const std::uint32_t i = (quarter & 1U) * 32 + lane;
+      float x[32];
+      if (quarter < 2) { // W only ever feeds TF32 products: round it here, once
+        tmem_ld32(tmem + lane_base + 64 + 32 * cg, x);
+#pragma unroll
+        for (std::uint32_t c = 0; c < 8; ++c) {
+          sts128(base + kPsWstage + cg * (kChunk * kRowBytes) + i * kRowBytes + ((c ^ (i & 7U)) << 4), tf32f(x[4 * c]),
+                 tf32f(x[4 * c + 1]), tf32f(x[4 * c + 2]), tf32f(x[4 * c + 3]));
+        }
+      } else {
+        tmem_ld32(tmem + lane_base + 192 + 32 * cg, x);
+        const std::uint32_t stage = base + kPsUstage + cg * kUBytes;
+#pragma unroll
+        for (std::uint32_t c = 0; c < 8; ++c) {
+          sts128(stage + (i * kPitchU + 4 * c) * 4, x[4 * c], x[4 * c + 1], x[4 * c + 2], x[4 * c + 3]);
+        }
+        sts32(stage + (kChunk * kPitchU + i) * 4, __float_as_uint(__expf(sG[i])));
+      }
+      fence_proxy_async();
+      tcgen05_fence_before();
+    }
+    __syncthreads();
+    if (copier && *abort_flag == 0) {
+#pragma unroll
+      for (std::uint32_t kb = 0; kb < 4; ++kb) { // rows 64..127 of every k-block of the [Q; W] image
+        bulk_copy_s2g(rec + kRecA1 + kb * kA1Block + kChunk * kRowBytes, base + kPsWstage + kb * (kChunk * kRowBytes),
+                      kChunk * kRowBytes);
+      }
+      bulk_copy_s2g(rec + kRecU, base + kPsUstage, (kDim / kSlice) * kUBytes);
+      asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
+    }
+    // The staging areas are the next item's operand images: the copier waits for the copies to have read them
+    // before the barrier that precedes the next image stores (top of the loop), not here.
+  }
+  if (copier) {
+    asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    tcgen05_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(kPrepTmemColumns) : "memory");
+  }
+}
+
+// ---- apply: per (state slice, value head), chunks in order ---------------------------------------------
+// 192 threads.  Warps 0-3 own the 128 lanes of tensor memory (thread = row of every product), warp 4 issues the
+// tcgen05 products (whole warp in step, one elected lane issuing), lane 0 of warp 5 streams the operand images of
+// each chunk into shared memory with bulk copies counted on mbarriers.  Per chunk:
+//   X  = [Q; W] S0            M 128 (rows 0..63 Q S0, rows 64..127 W S0), N 32, K 128
+//   warps 2-3: Delta = U - X[64..]  ->  B operand (TF32);   warps 0-1: keep gamma_i (Q S0)_i
+//   SD = (diag(e) K)^T Delta  M 128, N 32, K 64 (A operand MN-major: diag(e) K in token order)
+//   O2 = P Delta              M 128 (rows 64..127 are don't-care), N 32, K 64
+//   all: S = gamma_C S + SD (FP32 registers) -> B operand (TF32): the next chunk's first product waits for this
+//   warps 0-1: O = gamma_i (Q S0)_i + O2, each row through shared memory and out with a bulk copy
+// Every mbarrier wait is bounded; when one runs out the CTA records RIB200_DEVICE_WAIT_TIMED_OUT, stops waiting
+// and copying, and runs to its end (its results are then meaningless, as the status word says).
+constexpr int kApplyThreads = 192;
+constexpr std::uint32_t kSmA1 = 0;                         // two stages of the [Q; W] image
+constexpr std::uint32_t kSmA23 = kSmA1 + 2 * kA1Bytes;     // P image, then the (K diag(e))^T image
+constexpr std::uint32_t kSmB1 = kSmA23 + kA2Bytes + kA3Bytes; // S^T, [4 k-blocks][32 rows][128 bytes]
+constexpr std::uint32_t kB1Block = kSlice * kRowBytes;
+constexpr std::uint32_t kSmBD = kSmB1 + 4 * kB1Block;      // Delta^T, [2 k-blocks][32 rows][128 bytes]
+constexpr std::uint32_t kSmU = kSmBD + 2 * kB1Block;       // two stages of U slice + gamma
+constexpr std::uint32_t kUStage = 10240;                   // stage stride: the output tile that reuses a stage wants 1 KiB alignment
+constexpr std::uint32_t kSmBars = kSmU + 2 * kUStage;
+enum : std::uint32_t {
+  kBarA1Full = 0,   // [2] bytes of a [Q; W] image
+  kBarA1Empty = 2,  // [2] the product that read it has completed
+  kBarA23Full = 4,
+  kBarA23Empty = 5,
+  kBarUFull = 6,    // [2]
+  kBarUEmpty = 8,   // [2] 128 readers
+  kBarXDone = 10,   // X is in tensor memory
+  kBarDReady = 11,  // Delta^T is in shared memory (64 writers)
+  kBarSdDone = 12,  // SD is in tensor memory
+  kBarSReady = 13,  // S^T is in shared memory, X and SD have been read (128 threads)
+  kBarO2Done = 14,  // O2 is in tensor memory
+  kBarO2Free = 15,  // O2 has been read (64 threads)
+  kBarCount = 16
+};
+constexpr std::uint32_t kSmTmemSlot = kSmBars + kBarCount * 8;
+constexpr std::uint32_t kSmAbort = kSmTmemSlot + 4;
+constexpr std::uint32_t kApplySmemBytes = kSmAbort + 4 + 1024; // + room to align the base to 1 KiB
+static_assert(kUStage >= kUBytes && kSmA23 % 1024 == 0 && kSmB1 % 1024 == 0 && kSmBD % 1024 == 0 && kSmU % 1024 == 0 &&
+                  kSmBars % 8 == 0,
+              "operand images sit on 1 KiB boundaries");
+static_assert(kApplySmemBytes <= 232448, "apply kernel exceeds the shared memory of an SM");
+constexpr long long kWaitLimitCycles = 1LL << 28;
+constexpr std::uint32_t kTmemColumns = 128; // X at 0, O2 at 32, SD at 64
+constexpr std::uint32_t kPrefetchAhead = 3;   // chunks between an L2 prefetch and the copy that uses it
+constexpr std::uint32_t kCopyPiece = 16384;  // the operand images come in as several bulk copies in flight at once
 
 __global__ void __launch_bounds__(kApplyThreads, 1)
     gdn_chunk_apply_kernel(const ChunkParams p, const __grid_constant__ TensorMapBytes out_map) {
@@ -722,7 +1060,8 @@ __global__ void __launch_bounds__(kApplyThreads, 1)
     const std::uint64_t b1_desc = smem_desc(base + kSmB1);
     const std::uint64_t bd_desc = smem_desc(base + kSmBD);
     const std::uint64_t a2_desc = smem_desc(base + kSmA23);
-    const std::uint64_t a3_desc = smem_desc(base + kSmA23 + kA2Bytes);
+    // diag(e) K as stored: [token][key dim], the key dim (M of this product) contiguous
+    const std::uint64_t a3_desc = smem_desc_mn(base + kSmA23 + kA2Bytes, kA3AtomBytes, 512);
     // descriptor address field counts 16-byte units: a k-step inside a k-block is 32 bytes = 2 units
     auto step = [](std::uint32_t ks, std::uint32_t block_bytes) {
       return static_cast<std::uint64_t>(((ks >> 2) * block_bytes + (ks & 3U) * 32U) >> 4);
@@ -759,7 +1098,9 @@ __global__ void __launch_bounds__(kApplyThreads, 1)
       if (issuer && *abort_flag == 0) {
 #pragma unroll
         for (std::uint32_t ks = 0; ks < 8; ++ks) {
-          umma_tf32(tmem + 64, a3_desc + step(ks, kA3Block), bd_desc + step(ks, kB1Block), ks);
+          // eight tokens per product = two k atoms = 1 KiB of the image
+          umma_tf32(tmem + 64, a3_desc + static_cast<std::uint64_t>(ks * 1024U >> 4), bd_desc + step(ks, kB1Block), ks,
+                    kIdescMnA);
         }
         umma_commit(bar(kBarSdDone));
       }
@@ -938,7 +1279,7 @@ template <bool F32> void configure_once() {
   require(device >= 0 && device < 64, "device ordinal out of range", RIB200_STATUS_INTERNAL);
   std::call_once(flags[device], [] {
     cuda_ok(cudaFuncSetAttribute(gdn_chunk_prepare_kernel<F32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 kPrepSmemFloats * 4),
+                                 kPrepSmemBytes),
             "gated-delta prepare shared-memory opt-in");
     cuda_ok(cudaFuncSetAttribute(gdn_chunk_apply_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  kApplySmemBytes),
@@ -946,10 +1287,25 @@ template <bool F32> void configure_once() {
   });
 }
 
+// SMs of the current device: the prepare kernel runs one persistent CTA on each
+int sm_count() {
+  static int counts[64] = {};
+  int device = 0;
+  cuda_ok(cudaGetDevice(&device), "cudaGetDevice");
+  require(device >= 0 && device < 64, "device ordinal out of range", RIB200_STATUS_INTERNAL);
+  if (counts[device] == 0) {
+    int count = 0;
+    cuda_ok(cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device), "SM count");
+    counts[device] = count > 0 ? count : 1;
+  }
+  return counts[device];
+}
+
 template <bool F32> void launch(const ChunkParams &params, cudaStream_t stream) {
   configure_once<F32>();
-  gdn_chunk_prepare_kernel<F32>
-      <<<dim3(params.chunks, params.value_heads), 256, kPrepSmemFloats * 4, stream>>>(params);
+  const std::uint32_t items = params.chunks * params.value_heads;
+  const std::uint32_t prepare_ctas = items < static_cast<std::uint32_t>(sm_count()) ? items : sm_count();
+  gdn_chunk_prepare_kernel<F32><<<prepare_ctas, kPrepThreads, kPrepSmemBytes, stream>>>(params);
   cuda_ok(cudaGetLastError(), "gated-delta prepare launch");
   TensorMapBytes out_map;
   encode_f32_rows_map(&out_map, params.out, static_cast<std::uint64_t>(params.value_heads) * kDim, params.tokens,

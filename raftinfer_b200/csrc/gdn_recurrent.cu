@@ -130,8 +130,8 @@ __global__ void __launch_bounds__(256, 4) gdn_recurrent_kernel(const RecurrentPa
   }
 }
 
-// Batched decode step: one token for each of many sequences.  A CTA of sixteen warps owns one value head for a
-// strided share of the sequences.  The head's whole 64 KiB state - one contiguous block of memory - streams through
+// Batched decode step: one token for each of many sequences.  One CTA of sixteen warps per SM walks an equal share
+// of the (sequence, value head) pairs.  A head's whole 64 KiB state - one contiguous block of memory - streams through
 // a three-stage cp.async ring in shared memory, so the next sequences' states are in flight while the current one
 // is updated; the update is written back into its stage and leaves as full 512-byte rows.  (Splitting a head's
 // columns over two CTAs, as the single-sequence kernel does, makes each of them touch only half of every DRAM
@@ -155,27 +155,33 @@ __global__ void __launch_bounds__(kBatchedThreads, 1)
   extern __shared__ __align__(16) unsigned char ring[];
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const std::uint32_t head = blockIdx.x;
-  const std::uint32_t key_head = head % p.key_heads;
   const int col0 = warp * 8;
-  const std::uint32_t first = blockIdx.y;
-  const std::uint32_t step = gridDim.y;
-  const std::uint32_t count = first < sequences ? (sequences - first + step - 1) / step : 0;
+  // Work units are (sequence, value head) pairs in that order; the CTAs split them into contiguous ranges whose
+  // lengths differ by at most one, so that every SM streams the same number of states (64 sequences x 32 heads
+  // over 148 CTAs: 13 or 14 each).
+  const std::uint32_t units = sequences * p.value_heads;
+  const std::uint32_t unit0 = static_cast<std::uint32_t>(static_cast<std::uint64_t>(units) * blockIdx.x / gridDim.x);
+  const std::uint32_t unit1 = static_cast<std::uint32_t>(static_cast<std::uint64_t>(units) * (blockIdx.x + 1) / gridDim.x);
+  const std::uint32_t count = unit1 - unit0;
   const std::uint32_t ring_base = static_cast<std::uint32_t>(__cvta_generic_to_shared(ring));
 
-  // The state pointers of this CTA's first sequences are read once: a dependent pointer load in front of every copy
-  // and every write-back would sit on the critical path of each sequence.
+  // The state pointers of this CTA's first units are read once: a dependent pointer load in front of every copy
+  // and every write-back would sit on the critical path of each unit.
   constexpr std::uint32_t kKnownPointers = 64;
   __shared__ float *known[kKnownPointers];
   if (threadIdx.x < kKnownPointers && threadIdx.x < count) {
-    known[threadIdx.x] = p.states[first + threadIdx.x * step];
+    known[threadIdx.x] = p.states[(unit0 + threadIdx.x) / p.value_heads];
   }
   __syncthreads();
-  auto state_of = [&](std::uint32_t n) { return n < kKnownPointers ? known[n] : p.states[first + n * step]; };
+  auto state_of = [&](std::uint32_t n) {
+    return n < kKnownPointers ? known[n] : p.states[(unit0 + n) / p.value_heads];
+  };
 
   // copy the head's 128 x 128 state of this CTA's n-th sequence into stage n % kStages
   auto issue = [&](std::uint32_t n) {
-    const std::uint32_t seq = first + n * step;
+    const std::uint32_t seq = (unit0 + n) / p.value_heads;
+    const std::uint32_t head = (unit0 + n) % p.value_heads;
+    const std::uint32_t key_head = head % p.key_heads;
     const float *src = state_of(n) + static_cast<std::size_t>(head) * kDim * kDim;
     const std::uint32_t dst = ring_base + (n % kStages) * kStageBytes;
 #pragma unroll
@@ -213,8 +219,8 @@ __global__ void __launch_bounds__(kBatchedThreads, 1)
   }
 
   for (std::uint32_t n = 0; n < count; ++n) {
-    const std::uint32_t seq = first + n * step;
-    const std::size_t item = seq;
+    const std::size_t item = (unit0 + n) / p.value_heads;
+    const std::uint32_t head = (unit0 + n) % p.value_heads;
 
     // Stage (n-1) % kStages is refilled next: its write-back was issued by all threads before they arrived here.
     __syncthreads();
@@ -347,13 +353,12 @@ void launch_gdn_recurrent(const GdnCoreArgs &a, cudaStream_t stream) {
                                    kBatchedSmemBytes),
               "gated-delta batched decode shared-memory opt-in");
     });
-    // one CTA per SM: about that many CTAs, each walking at least four sequences when the batch allows
+    // one CTA per SM, each walking its share of the (sequence, head) units
     int sm_count = 148;
     cuda_ok(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device), "SM count query");
-    const std::uint32_t groups =
-        std::max(1U, std::min(a.sequences / 4, static_cast<std::uint32_t>(sm_count) / a.value_heads));
-    gdn_batched_decode_kernel<<<dim3(a.value_heads, groups), kBatchedThreads, kBatchedSmemBytes, stream>>>(
-        p, a.sequences);
+    const std::uint32_t units = a.sequences * a.value_heads;
+    const std::uint32_t ctas = std::max(1U, std::min(units / 2, static_cast<std::uint32_t>(sm_count)));
+    gdn_batched_decode_kernel<<<ctas, kBatchedThreads, kBatchedSmemBytes, stream>>>(p, a.sequences);
     cuda_ok(cudaGetLastError(), "gated-delta batched decode launch");
     return;
   }
