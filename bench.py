@@ -235,12 +235,23 @@ def main():
         return float(t.item())
 
     # ---- device-resident timing ---------------------------------------------------------------
-    for i in range(warmup):
-        step(i)
-    barrier()
+    # The clock sampler (an nvidia-smi process polling every 100 ms) is started before the warm-up and is already
+    # delivering samples when the timed region begins: its start-up would otherwise fall into the region, which at
+    # 20 steps lasts less than a millisecond.
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    for i in range(warmup):
+        step(i)
+    barrier()
+    if rank == 0:
+        deadline = time.time() + 3.0
+        i = 0
+        while not sampler.rows and time.time() < deadline:  # keep the GPU busy until the first sample is in
+            step(i)
+            i += 1
+            if i % 64 == 0:
+                torch.cuda.synchronize()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     start.record(stream)
