@@ -119,7 +119,7 @@ __global__ void __launch_bounds__(kDim) gdn_prologue_kernel(const LayerParams p)
 }
 
 // ---- fast forms for conv_width == 4 (the model's width) ---------------------------------------------
-// A warp owns one head vector (128 channels, four per lane) over eight consecutive tokens: the eleven input rows
+// A warp owns one head vector (128 channels, four per lane) over four consecutive tokens: the seven input rows
 // it needs are fetched once, 8 or 16 bytes per lane and row, whole 256/512-byte segments per warp, and slide
 // through registers; the sum of squares of a q or k vector is five shuffles.  Dtype is a template parameter.
 template <int Dtype> struct Io;
@@ -163,10 +163,10 @@ template <> struct Io<RIB200_DTYPE_F16> {
 // kernels are bound by instruction issue otherwise.  Relative error about 1e-6.
 __device__ __forceinline__ float silu_fast(float x) { return x * __frcp_rn(1.0F + __expf(-x)); }
 
-constexpr int kTokensPerWarp = 8;
+constexpr int kTokensPerWarp = 4;
 constexpr int kFastWidth = 4;
 
-// grid (ceil(tokens / 8), ceil((2 Hk + Hv + 1) / 8)), 256 threads: warp w of the CTA takes head vector
+// grid (ceil(tokens / 4), ceil((2 Hk + Hv + 1) / 8)), 256 threads: warp w of the CTA takes head vector
 // 8 blockIdx.y + w; the vector after the last one stands for the gates (lane = value head, any head count).
 template <int Dtype> __global__ void __launch_bounds__(256, 4) gdn_prologue_w4_kernel(const LayerParams p) {
   const int lane = threadIdx.x & 31;

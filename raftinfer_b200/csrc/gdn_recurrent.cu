@@ -62,6 +62,12 @@ __global__ void __launch_bounds__(256, 4) gdn_recurrent_kernel(const RecurrentPa
   const std::uint32_t key_head = head % p.key_heads;
   const int col0 = blockIdx.x * 64 + warp * 8;
   const int row0 = lane * 4;
+  // Launched with programmatic stream serialisation: the grid may be resident while the kernel in front of it (the
+  // previous token's step, in a run of decode steps) is still finishing.  Nothing is read or written before that
+  // kernel has completed, so the ordering is that of a plain launch, minus most of the launch latency; the kernel
+  // behind this one is let in on the same terms.
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   float *state = (p.states != nullptr ? p.states[seq] : p.state) + static_cast<std::size_t>(head) * kDim * kDim;
 
   float s[4][8];
@@ -362,13 +368,21 @@ void launch_gdn_recurrent(const GdnCoreArgs &a, cudaStream_t stream) {
     cuda_ok(cudaGetLastError(), "gated-delta batched decode launch");
     return;
   }
-  const dim3 grid(2, a.value_heads, a.sequences);
+  cudaLaunchAttribute attribute{};
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t config{};
+  config.gridDim = dim3(2, a.value_heads, a.sequences);
+  config.blockDim = dim3(256, 1, 1);
+  config.dynamicSmemBytes = 0;
+  config.stream = stream;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
   if (a.qkv_f32) {
-    gdn_recurrent_kernel<true><<<grid, 256, 0, stream>>>(p);
+    cuda_ok(cudaLaunchKernelEx(&config, gdn_recurrent_kernel<true>, p), "gated-delta recurrent launch");
   } else {
-    gdn_recurrent_kernel<false><<<grid, 256, 0, stream>>>(p);
+    cuda_ok(cudaLaunchKernelEx(&config, gdn_recurrent_kernel<false>, p), "gated-delta recurrent launch");
   }
-  cuda_ok(cudaGetLastError(), "gated-delta recurrent launch");
 }
 
 } // namespace rib200
