@@ -485,3 +485,48 @@ def test_paged_decode_flags_a_page_outside_the_pool():
     with pytest.raises(K.Qwen35PrimitiveError):
         K.paged_decode_attention(dq, dk, dv, dg, out, pool, s["pool_pages"], tables, s["max_blocks"], dpos, batch, ws,
                                  ws_bytes // 2, stream)
+
+
+def test_serving_decode_64_ragged_sequences_at_full_size():
+    """The batched serving configuration at its full size: 64 sequences, contexts uniform in [1024, 32768] from a
+    seed (about 1.1 M tokens, 4.7 GB of caches), one launch pair.  The caches are drawn on the device; the oracle runs
+    on the shortest, the longest and four more sequences, whose caches are copied back, and every sequence's appended
+    row and output are checked for the properties that need no oracle: the row equals the new token's K and V bit for
+    bit, nothing else in the cache moved (a checksum of the other rows), the output is finite."""
+    batch, lo, hi, seed = 64, 1024, 32768, 0xB2000004
+    cpu_gen = torch.Generator().manual_seed(seed)
+    lengths = torch.randint(lo, hi + 1, (batch,), generator=cpu_gen).tolist()
+    caps = [-(-n // 256) * 256 for n in lengths]
+    largest = max(caps)
+    gen = torch.Generator(device=dev()).manual_seed(seed)
+    rand = lambda *shape: torch.randn(*shape, device=dev(), generator=gen, dtype=torch.float32).to(torch.bfloat16)
+    caches = [rand(2, HKV, c, D) for c in caps]
+    q, gate = rand(batch, HQ, D), rand(batch, HQ, D)
+    k, v = rand(batch, HKV, D), rand(batch, HKV, D)
+    out = torch.zeros(batch, HQ, D, device=dev(), dtype=torch.bfloat16)
+    ptrs = torch.tensor([c.data_ptr() for c in caches], device=dev(), dtype=torch.int64)
+    dcaps = torch.tensor(caps, device=dev(), dtype=torch.int32)
+    dpos = torch.tensor([n - 1 for n in lengths], device=dev(), dtype=torch.int32)
+    ws_bytes = K.batched_decode_workspace_bytes(batch, largest)
+    ws = torch.zeros(ws_bytes // 4, device=dev())
+    # checksums of everything but the row that is appended (as 16-bit integers, wrapping 64-bit sums)
+    def checksum(cache, row):
+        bits = cache.view(torch.int16).to(torch.int64)
+        return int(bits.sum().item()) - int(bits[:, :, row].sum().item())
+    before = [checksum(c, n - 1) for c, n in zip(caches, lengths)]
+    stream = torch.cuda.current_stream()
+    K.batched_decode_attention(q, k, v, gate, out, ptrs, dcaps, dpos, batch, largest, ws, ws_bytes, stream)
+    torch.cuda.synchronize()
+    assert K.device_status(stream) == 0
+    assert torch.isfinite(out.float()).all()
+    for i, n in enumerate(lengths):
+        assert torch.equal(caches[i][0, :, n - 1], k[i]) and torch.equal(caches[i][1, :, n - 1], v[i])
+        assert checksum(caches[i], n - 1) == before[i], f"sequence {i}: a row other than the appended one changed"
+    order = sorted(range(batch), key=lambda i: lengths[i])
+    sampled = {order[0], order[-1], order[batch // 2], 0, 17, 63}
+    got = to_numpy_f32(out)
+    for i in sampled:
+        bits = cache_bits_of(caches[i])
+        want = ob.attention_core_cache(to_numpy_f32(q[i])[None], to_numpy_f32(gate[i])[None], bits, caps[i],
+                                       lengths[i] - 1)[0]
+        gate_bf16_outputs(compare(got[i], want))

@@ -296,3 +296,25 @@ def test_layer_saturation_edges_stay_finite():
     out, want, _ = run.step(tokens)
     assert np.isfinite(to_numpy_f32(out)).all() and np.isfinite(to_numpy_f32(run.d_rs)).all()
     run.check(out, want)
+
+
+def test_batched_decode_step_64_sequences_at_full_size():
+    """The serving configuration's gated-delta half at its full size: one recurrent step on each of 64 sequences'
+    FP32 [32][128][128] states in one launch (the kernel that splits the (sequence, head) units evenly over the SMs);
+    every sequence's output and new state against the oracle."""
+    batch, seed = 64, 0xB2001600
+    q, k, v, beta, g = core_operands(seed, batch)  # one token per sequence
+    gen = torch.Generator(device=dev()).manual_seed(seed)
+    states = [0.05 * torch.randn(HV, DK, DK, device=dev(), generator=gen) for _ in range(batch)]
+    states0 = [to_numpy_f32(s) for s in states]
+    ptrs = torch.tensor([s.data_ptr() for s in states], device=dev(), dtype=torch.int64)
+    out = torch.zeros(batch, HV, DK, device=dev())
+    K.batched_gdn_decode(bf16_tensor(q), bf16_tensor(k), bf16_tensor(v), torch.from_numpy(beta).to(dev()),
+                         torch.from_numpy(g).to(dev()), ptrs, out, batch, HK, HV, torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    got = to_numpy_f32(out)
+    for i in range(batch):
+        want_out, want_state = ob.gdn_core(q[i:i + 1], k[i:i + 1], v[i:i + 1], beta[i:i + 1], np.exp(g[i:i + 1]),
+                                           states0[i])
+        assert compare(got[i], want_out[0])["rel_l2"] <= 1.0e-4, i
+        assert compare(to_numpy_f32(states[i]), want_state)["rel_l2"] <= 1.0e-5, i
