@@ -59,7 +59,8 @@ enum {
   RIB200_DEVICE_DECODE_CAPACITY_EXCEEDED = 1u << 0, /* live context needs more partitions than the plan holds */
   RIB200_DEVICE_POSITION_OUT_OF_RANGE = 1u << 1,    /* *device_position >= max_context_tokens */
   RIB200_DEVICE_WAIT_TIMED_OUT = 1u << 2,           /* a bounded on-device wait gave up */
-  RIB200_DEVICE_PAGE_OUT_OF_RANGE = 1u << 3         /* a block table names a page the pool does not hold */
+  RIB200_DEVICE_PAGE_OUT_OF_RANGE = 1u << 3,        /* a block table names a page the pool does not hold */
+  RIB200_DEVICE_POINTER_MISALIGNED = 1u << 4        /* a pointer read on the device is off its required boundary */
 };
 
 /* cpp/kernels/qwen35_attention.cuh:14-21 */
@@ -261,9 +262,11 @@ Rib200Status rib200_paged_decode_attention(const void *query, const void *key, c
                                            const uint32_t *block_tables, size_t max_blocks_per_sequence,
                                            const uint32_t *positions, size_t batch, void *workspace,
                                            size_t workspace_bytes, void *stream);
-/* Recurrent gated-delta decode step for a batch of sequences: states[i] FP32 [value_heads][128][128]
- * (array of device pointers, itself in device memory); q,k BF16 [batch][key_heads][128], v BF16
- * [batch][value_heads][128], beta/log_decay FP32 [batch][value_heads], out FP32 [batch][value_heads][128]. */
+/* Recurrent gated-delta decode step for a batch of sequences: states[i] FP32 [value_heads][128][128], 16-byte
+ * aligned (array of device pointers, itself in device memory); q,k BF16 [batch][key_heads][128], v BF16
+ * [batch][value_heads][128], beta/log_decay FP32 [batch][value_heads], out FP32 [batch][value_heads][128].
+ * A states[i] off a 16-byte boundary sets RIB200_DEVICE_POINTER_MISALIGNED; the states and outputs of that call are
+ * then undefined. */
 Rib200Status rib200_batched_gdn_decode(const void *q, const void *k, const void *v, const float *beta,
                                        const float *log_decay, float *const *states, float *out, size_t batch,
                                        size_t key_heads, size_t value_heads, void *stream);

@@ -26,6 +26,7 @@ OK, INVALID_ARGUMENT, UNAVAILABLE, CUDA_ERROR, INTERNAL, UNSUPPORTED, RESOURCE_E
 # device status bits
 DEVICE_DECODE_CAPACITY_EXCEEDED, DEVICE_POSITION_OUT_OF_RANGE, DEVICE_WAIT_TIMED_OUT = 1, 2, 4
 DEVICE_PAGE_OUT_OF_RANGE = 8
+DEVICE_POINTER_MISALIGNED = 16
 
 
 class Qwen35PrimitiveError(RuntimeError):

@@ -318,3 +318,60 @@ def test_batched_decode_step_64_sequences_at_full_size():
                                            states0[i])
         assert compare(got[i], want_out[0])["rel_l2"] <= 1.0e-4, i
         assert compare(to_numpy_f32(states[i]), want_state)["rel_l2"] <= 1.0e-5, i
+
+
+@pytest.mark.parametrize("batch", [8, 9, 37, 300])
+def test_batched_decode_step_streaming_kernel(batch):
+    """The batches the streaming kernel takes (8 sequences and up): unit counts that do not divide by the SM count,
+    one or two units a CTA, and more units per CTA (300 x 32 over 148) than state pointers it keeps in shared memory.
+    At 300 sequences every seventh one is checked against the oracle."""
+    seed = 0xB2001700 + batch
+    q, k, v, beta, g = core_operands(seed, batch)
+    gen = torch.Generator(device=dev()).manual_seed(seed)
+    states = [0.05 * torch.randn(HV, DK, DK, device=dev(), generator=gen) for _ in range(batch)]
+    checked = range(batch) if batch <= 64 else range(0, batch, 7)
+    states0 = {i: to_numpy_f32(states[i]) for i in checked}
+    ptrs = torch.tensor([s.data_ptr() for s in states], device=dev(), dtype=torch.int64)
+    out = torch.zeros(batch, HV, DK, device=dev())
+    stream = torch.cuda.current_stream()
+    K.batched_gdn_decode(bf16_tensor(q), bf16_tensor(k), bf16_tensor(v), torch.from_numpy(beta).to(dev()),
+                         torch.from_numpy(g).to(dev()), ptrs, out, batch, HK, HV, stream)
+    torch.cuda.synchronize()
+    assert K.device_status(stream) == 0
+    got = to_numpy_f32(out)
+    for i in checked:
+        want_out, want_state = ob.gdn_core(q[i:i + 1], k[i:i + 1], v[i:i + 1], beta[i:i + 1], np.exp(g[i:i + 1]),
+                                           states0[i])
+        assert compare(got[i], want_out[0])["rel_l2"] <= 1.0e-4, i
+        assert compare(to_numpy_f32(states[i]), want_state)["rel_l2"] <= 1.0e-5, i
+
+
+def test_batched_decode_step_reports_a_state_pointer_off_its_boundary():
+    """The state pointers live in device memory, so the host cannot check them.  The streaming kernel looks at each
+    one before it copies from it: a pointer off a 16-byte boundary is not read (the copy would fault); the kernel sets
+    RIB200_DEVICE_POINTER_MISALIGNED instead, and the context carries on with the next, well-formed call."""
+    batch, seed = 16, 0xB2001800
+    q, k, v, beta, g = core_operands(seed, batch)
+    gen = torch.Generator(device=dev()).manual_seed(seed)
+    pool = 0.05 * torch.randn(batch, HV * DK * DK + 4, device=dev(), generator=gen)
+    addresses = [pool[i].data_ptr() for i in range(batch)]
+    bad = list(addresses)
+    bad[5] += 4
+    out = torch.zeros(batch, HV, DK, device=dev())
+    stream = torch.cuda.current_stream()
+    operands = (bf16_tensor(q), bf16_tensor(k), bf16_tensor(v), torch.from_numpy(beta).to(dev()),
+                torch.from_numpy(g).to(dev()))
+    assert K.device_status(stream) == 0
+    K.batched_gdn_decode(*operands, torch.tensor(bad, device=dev(), dtype=torch.int64), out, batch, HK, HV, stream)
+    torch.cuda.synchronize()
+    assert K.device_status(stream) == K.DEVICE_POINTER_MISALIGNED
+    assert K.device_status(stream) == 0  # reading cleared it
+    fresh = 0.05 * torch.randn(batch, HV * DK * DK + 4, device=dev(), generator=gen)
+    before = to_numpy_f32(fresh[3, :HV * DK * DK]).reshape(HV, DK, DK)
+    K.batched_gdn_decode(*operands, torch.tensor([fresh[i].data_ptr() for i in range(batch)], device=dev(),
+                                                 dtype=torch.int64), out, batch, HK, HV, stream)
+    torch.cuda.synchronize()
+    assert K.device_status(stream) == 0
+    want_out, want_state = ob.gdn_core(q[3:4], k[3:4], v[3:4], beta[3:4], np.exp(g[3:4]), before)
+    assert compare(to_numpy_f32(out)[3], want_out[0])["rel_l2"] <= 1.0e-4
+    assert compare(to_numpy_f32(fresh[3, :HV * DK * DK]).reshape(HV, DK, DK), want_state)["rel_l2"] <= 1.0e-5
