@@ -97,6 +97,13 @@ struct alignas(64) TensorMapBytes {
 void encode_f32_rows_map(void *map_out, void *base, std::uint64_t row_floats, std::uint64_t rows,
                          std::uint32_t box_floats, std::uint32_t box_rows);
 
+// Tiled map without swizzle over rows of FP32 or BF16 elements: `rows` rows of `row_elements` elements that lie
+// `row_stride_elements` apart (a head range inside wider token rows); box [box_rows][box_elements]; rows past the
+// last one arrive as zeros.  Base and row stride must be multiples of 16 bytes.
+void encode_plain_rows_map(void *map_out, const void *base, bool f32, std::uint64_t row_elements,
+                           std::uint64_t row_stride_elements, std::uint64_t rows, std::uint32_t box_elements,
+                           std::uint32_t box_rows);
+
 void launch_decode_attention(const DecodeArgs &args, cudaStream_t stream);
 
 // One decode step for a batch of ragged sequences (BF16 activations).

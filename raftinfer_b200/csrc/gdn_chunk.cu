@@ -13,11 +13,13 @@
 // (beta = 0, log decay = 0, k = q = v = 0), which leave the state untouched.
 //
 // Two kernels, both on tcgen05 TF32 products with accumulators in tensor memory.  `prepare` is parallel over
-// (chunk, value head), one persistent CTA per SM: [K; Q] K^T as one product, T by a blocked inversion in FP32
-// (16 x 16 diagonal blocks by substitution, the rest by block products), then [T diag(beta exp(G)); T diag(beta)]
-// times K and times V, whose B operands are K and V exactly as they are stored (token rows, dims contiguous:
-// "MN-major" operands, no transposition).  It leaves every operand the apply kernel multiplies with as a ready
-// shared-memory image in the workspace.  `apply` walks the chunks in order for one (value head, 32-column slice
+// (chunk, value head), one persistent CTA per SM: the raw K, Q, V rows of an item arrive by tensor-map copies issued
+// while the item before it is in its last third (into areas of shared memory that are idle by then); [K; Q] K^T is
+// one product; T comes from a blocked inversion at FP32 accuracy (16 x 16 diagonal blocks by substitution, then the
+// blocks below them by doubling, -M22^-1 M21 M11^-1, on warp-level tensor tiles with operands split in two TF32
+// parts); then [T diag(beta exp(G)); T diag(beta)] times K and times V, whose B operands are K and V exactly as
+// they are stored (token rows, dims contiguous: "MN-major" operands, no transposition).  It leaves every operand the
+// apply kernel multiplies with as a ready shared-memory image in the workspace.  `apply` walks the chunks in order for one (value head, 32-column slice
 // of the state): the slice lives in registers (FP32) and, rounded to TF32, in shared memory as the B operand;
 // [Q; W] S0, P Delta and (diag(e) K)^T Delta are the products.  State columns are independent, so the four slices
 // of a head never talk to each other.  TF32 (10-bit mantissa, FP32 accumulate) rather than BF16 keeps the FP32
@@ -171,6 +173,13 @@ __device__ long long g_gdn_trace[128 * 16];
   do {                                \
   } while (0)
 #endif
+// the prepare kernel's first CTA: rows 100.. of the probe, one per item it walks
+#define PREP_STAMP(slot)                              \
+  do {                                                \
+    if (threadIdx.x == 0) {                           \
+      RIB200_GDN_STAMP(100 + iteration, slot);        \
+    }                                                 \
+  } while (0)
 
 __device__ __forceinline__ std::uint32_t smem_address(const void *p) {
   return static_cast<std::uint32_t>(__cvta_generic_to_shared(p));
@@ -200,6 +209,13 @@ __device__ __forceinline__ void bulk_copy_g2s(std::uint32_t dst, const void *src
                                               std::uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
                "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+// tiled tensor-map load of one box, completion counted on an mbarrier
+__device__ __forceinline__ void tma_load_2d(std::uint32_t dst, const void *map, int c0, int c1, std::uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::
+                   "r"(dst),
+               "l"(reinterpret_cast<std::uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar)
                : "memory");
 }
 // bulk copy shared -> global, completion tracked by the issuing thread's bulk groups
@@ -296,6 +312,11 @@ __device__ __forceinline__ float lds32(std::uint32_t addr) {
   asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(value) : "r"(addr));
   return value;
 }
+__device__ __forceinline__ uint4 lds128u(std::uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
 __device__ __forceinline__ float4 lds128(std::uint32_t addr) {
   float4 v;
   asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
@@ -330,8 +351,16 @@ constexpr std::uint32_t kPsPstage = kPsKe + 32768;          // P image on its wa
 constexpr std::uint32_t kPsA = kPsPstage + 16384;           // A, FP32 [64][68]
 constexpr std::uint32_t kPsT = kPsA + kChunk * kPitchSq * 4; // T, FP32 [64][68]
 constexpr std::uint32_t kPsVec = kPsT + kChunk * kPitchSq * 4; // G, beta, beta gamma, column factors: 4 x 64 floats
-constexpr std::uint32_t kPsBars = kPsVec + 1024;
-constexpr std::uint32_t kPsTmemSlot = kPsBars + 16;
+constexpr std::uint32_t kPsGateNext = kPsVec + 1024;         // the next item's log decays [64] and betas [64]
+constexpr std::uint32_t kPsBars = kPsGateNext + 512;
+constexpr std::uint32_t kPsTmemSlot = kPsBars + 32;
+// The raw rows of the next item land, by tensor-map copies issued while the current item is in its last third, in
+// areas that are idle by then: K in the diag(e) K staging area, Q in the upper half of the [K; Q] image, V in the P
+// staging area and A.  FP32 rows take 32 KiB per operand, BF16 rows 16 KiB.
+constexpr std::uint32_t kPsRawK = kPsKe;
+constexpr std::uint32_t kPsRawQ = kPsKQ + 32768;
+constexpr std::uint32_t kPsRawV = kPsPstage;
+static_assert(kPsA + kChunk * kPitchSq * 4 - kPsPstage >= 32768, "raw V rows fit in the P staging area and A");
 constexpr std::uint32_t kPsAbort = kPsTmemSlot + 4;
 constexpr std::uint32_t kPrepSmemBytes = kPsAbort + 4 + 1024; // + room to align the base to 1 KiB
 static_assert((kDim / kSlice) * kUBytes <= 65536 && kPsA % 16 == 0 && kPsBars % 8 == 0, "staging fits, alignment");
@@ -347,27 +376,26 @@ template <bool F32> struct HalfRowRegs {
 };
 template <bool F32> struct ItemRegs {
   HalfRowRegs<F32> k, q, v;
-  float gate;  // warp 0: log decay of token lane; warp 1: beta of token lane; warp 2: beta of token lane + 32
-  float gate2; // warp 0: log decay of token lane + 32
 };
 
-// Pieces `part` and `part + 8` of row tok0 + tid / 8 of a [token][heads][128] operand.  Rows at or past `tokens`
-// read the last row instead (the caller discards them when it unpacks): the function is loads and nothing that
-// waits for them, so that a call made an item ahead really runs ahead.
-template <bool F32>
-__device__ __forceinline__ HalfRowRegs<F32> fetch_half_rows(const void *src, std::size_t stride, std::uint32_t head,
-                                                            std::uint32_t tok0, std::uint32_t tokens) {
+// Pieces `part` and `part + 8` of row tid / 8 of a raw [64][128] tile in shared memory.  FP32 pieces are two 16-byte
+// words 32 bytes apart from the next lane's: the upper four parts read theirs in the other order, so that the eight
+// lanes of a row never meet in a bank.
+template <bool F32> __device__ __forceinline__ HalfRowRegs<F32> read_half_rows(std::uint32_t tile) {
   HalfRowRegs<F32> regs;
-  const std::uint32_t tok = min(tok0 + (threadIdx.x >> 3), tokens - 1);
-  const std::size_t first = static_cast<std::size_t>(tok) * stride + head * kDim + (threadIdx.x & 7U) * 8;
+  const std::uint32_t row = threadIdx.x >> 3;
+  const std::uint32_t part = threadIdx.x & 7U;
 #pragma unroll
   for (int a = 0; a < 2; ++a) {
     if constexpr (F32) {
-      const uint4 *s = reinterpret_cast<const uint4 *>(static_cast<const float *>(src) + first + 64 * a);
-      regs.v[2 * a] = s[0];
-      regs.v[2 * a + 1] = s[1];
+      const std::uint32_t at = tile + row * 512U + 256U * a + 32U * part;
+      const bool swap = (part & 4U) != 0;
+      const uint4 x = lds128u(at + (swap ? 16U : 0U));
+      const uint4 y = lds128u(at + (swap ? 0U : 16U));
+      regs.v[2 * a] = swap ? y : x;
+      regs.v[2 * a + 1] = swap ? x : y;
     } else {
-      regs.v[a] = *reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(src) + first + 64 * a);
+      regs.v[a] = lds128u(tile + row * 256U + 128U * a + 16U * part);
     }
   }
   return regs;
@@ -412,8 +440,75 @@ __device__ __forceinline__ void tmem_ld16(std::uint32_t taddr, float (&v)[16]) {
   }
 }
 
+// ---- small FP32-accurate block products on the warp-level tensor path (the inversion of I + A) ----
+__device__ __forceinline__ void mma_tf32(float (&c)[4], const std::uint32_t (&a)[4], std::uint32_t b0,
+                                         std::uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+               "{%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// x = hi + lo with both parts TF32: hi * hi + hi * lo + lo * hi of two such numbers is their product to FP32 accuracy
+__device__ __forceinline__ void split_tf32(float x, std::uint32_t &hi, std::uint32_t &lo) {
+  hi = tf32(x);
+  lo = tf32(x - __uint_as_float(hi));
+}
+// acc (a 16 x 16 block as two 16 x 8 accumulator tiles) += L[r0 .. r0+15][k0 .. k0+8 KSTEPS) R[k0 ..][c0 .. c0+15],
+// L and R row-major FP32 matrices of pitch kPitchSq in shared memory; one warp.  The three partial products run in
+// accumulators of their own, so that consecutive tensor instructions do not wait for each other.
+template <int KSTEPS>
+__device__ __forceinline__ void block_product(float (&acc)[2][4], const float *L, int r0, const float *R, int c0,
+                                              int k0) {
+  const int g = (threadIdx.x & 31) >> 2;
+  const int t = threadIdx.x & 3;
+  float lo_hi[2][4] = {};
+  float hi_lo[2][4] = {};
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS; ++ks) {
+    const int k = k0 + 8 * ks;
+    const float *l = L + (r0 + g) * kPitchSq + k + t;
+    std::uint32_t a_hi[4];
+    std::uint32_t a_lo[4];
+    split_tf32(l[0], a_hi[0], a_lo[0]);
+    split_tf32(l[8 * kPitchSq], a_hi[1], a_lo[1]);
+    split_tf32(l[4], a_hi[2], a_lo[2]);
+    split_tf32(l[8 * kPitchSq + 4], a_hi[3], a_lo[3]);
+#pragma unroll
+    for (int n = 0; n < 2; ++n) {
+      const float *r = R + (k + t) * kPitchSq + c0 + 8 * n + g;
+      std::uint32_t b_hi[2];
+      std::uint32_t b_lo[2];
+      split_tf32(r[0], b_hi[0], b_lo[0]);
+      split_tf32(r[4 * kPitchSq], b_hi[1], b_lo[1]);
+      mma_tf32(lo_hi[n], a_lo, b_hi[0], b_hi[1]);
+      mma_tf32(hi_lo[n], a_hi, b_lo[0], b_lo[1]);
+      mma_tf32(acc[n], a_hi, b_hi[0], b_hi[1]);
+    }
+  }
+#pragma unroll
+  for (int n = 0; n < 2; ++n) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      acc[n][e] += lo_hi[n][e] + hi_lo[n][e];
+    }
+  }
+}
+// the block goes to M[r0 ..][c0 ..] times `sign`
+__device__ __forceinline__ void store_block(float *M, int r0, int c0, const float (&acc)[2][4], float sign) {
+  const int g = (threadIdx.x & 31) >> 2;
+  const int t = threadIdx.x & 3;
+#pragma unroll
+  for (int n = 0; n < 2; ++n) {
+    float *at = M + (r0 + g) * kPitchSq + c0 + 8 * n + 2 * t;
+    *reinterpret_cast<float2 *>(at) = make_float2(sign * acc[n][0], sign * acc[n][1]);
+    *reinterpret_cast<float2 *>(at + 8 * kPitchSq) = make_float2(sign * acc[n][2], sign * acc[n][3]);
+  }
+}
+
 template <bool F32>
-__global__ void __launch_bounds__(kPrepThreads, 1) gdn_chunk_prepare_kernel(const ChunkParams p) {
+__global__ void __launch_bounds__(kPrepThreads, 1)
+    gdn_chunk_prepare_kernel(const ChunkParams p, const __grid_constant__ TensorMapBytes k_map,
+                             const __grid_constant__ TensorMapBytes q_map, const __grid_constant__ TensorMapBytes v_map) {
   extern __shared__ unsigned char prep_smem_raw[];
   const std::uint32_t base = (smem_address(prep_smem_raw) + 1023U) & ~1023U;
   unsigned char *smem = prep_smem_raw + (base - smem_address(prep_smem_raw));
@@ -425,6 +520,8 @@ __global__ void __launch_bounds__(kPrepThreads, 1) gdn_chunk_prepare_kernel(cons
   float *sCf = sBg + kChunk;                              // exp(G at the end of the token's block of 16 - G)
   const std::uint32_t bar_g = base + kPsBars;
   const std::uint32_t bar_wu = base + kPsBars + 8;
+  const std::uint32_t bar_raw = base + kPsBars + 16;
+  float *sGateNext = reinterpret_cast<float *>(smem + kPsGateNext);
   volatile std::uint32_t *tmem_slot = reinterpret_cast<volatile std::uint32_t *>(smem + kPsTmemSlot);
   volatile std::uint32_t *abort_flag = reinterpret_cast<volatile std::uint32_t *>(smem + kPsAbort);
 
@@ -438,6 +535,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) gdn_chunk_prepare_kernel(cons
   if (tid == 0) {
     mbarrier_init(bar_g, 1);
     mbarrier_init(bar_wu, 1);
+    mbarrier_init(bar_raw, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -473,63 +571,56 @@ __global__ void __launch_bounds__(kPrepThreads, 1) gdn_chunk_prepare_kernel(cons
     }
   };
 
-  auto fetch = [&](std::uint32_t item) {
-    ItemRegs<F32> regs;
-    const std::uint32_t chunk = item / p.value_heads;
+  // The raw K, Q and V rows of an item come in as three tensor-map copies (rows past the last token arrive as
+  // zeros), issued by the copier lane an item ahead; its gates are read by two otherwise idle warps at the same time.
+  constexpr std::uint32_t kRawBytes = kChunk * kDim * (F32 ? 4 : 2);
+  auto issue_rows = [&](std::uint32_t item) {
     const std::uint32_t head = item % p.value_heads;
-    const std::uint32_t key_head = head % p.key_heads;
-    const std::uint32_t tok0 = chunk * kChunk;
-    regs.k = fetch_half_rows<F32>(p.k, p.k_stride, key_head, tok0, p.tokens);
-    regs.q = fetch_half_rows<F32>(p.q, p.q_stride, key_head, tok0, p.tokens);
-    regs.v = fetch_half_rows<F32>(p.v, p.v_stride, head, tok0, p.tokens);
-    // gates of tokens at or past `tokens` are read from the last token and discarded by the consumer
-    const std::uint32_t last = p.tokens - 1;
-    const std::uint32_t tok_a = min(tok0 + lane + 32 * (warp == 2 ? 1 : 0), last);
-    const std::uint32_t tok_b = min(tok0 + lane + 32, last);
-    const float *gates = warp == 0 ? p.log_decay : p.beta;
-    regs.gate = gates[static_cast<std::size_t>(tok_a) * p.value_heads + head];
-    regs.gate2 = gates[static_cast<std::size_t>(tok_b) * p.value_heads + head];
-    return regs;
+    const int tok0 = static_cast<int>((item / p.value_heads) * kChunk);
+    const int key_x = static_cast<int>((head % p.key_heads) * kDim);
+    fence_proxy_async(); // the landing areas were last touched by ordinary loads and stores
+    mbarrier_expect_tx(bar_raw, 3 * kRawBytes);
+    tma_load_2d(base + kPsRawK, &k_map, key_x, tok0, bar_raw);
+    tma_load_2d(base + kPsRawQ, &q_map, key_x, tok0, bar_raw);
+    tma_load_2d(base + kPsRawV, &v_map, static_cast<int>(head * kDim), tok0, bar_raw);
   };
-
-  // Rows of an item are pulled into L2 while the item before it is worked on (a prefetch has no destination
-  // register, so nothing in between ever waits for it); the loads at the top of the item then find them there.
-  auto prefetch = [&](std::uint32_t item) {
-    constexpr std::uint32_t kLines = F32 ? 4 : 2; // 128-byte lines per row of one head
-    const std::uint32_t chunk = item / p.value_heads;
-    const std::uint32_t head = item % p.value_heads;
-    const std::uint32_t key_head = head % p.key_heads;
-    const std::size_t tok = min(chunk * kChunk + row, p.tokens - 1);
-    if (part >= 6) { // the token's two gates
-      const float *gates = part == 6 ? p.beta : p.log_decay;
-      asm volatile("prefetch.global.L2 [%0];\n" ::"l"(gates + tok * p.value_heads + head));
-    }
-    if (part >= kLines) {
-      return;
-    }
-    constexpr std::size_t kElement = F32 ? 4 : 2;
-    const char *k_line = static_cast<const char *>(p.k) + (tok * p.k_stride + key_head * kDim) * kElement + part * 128;
-    const char *q_line = static_cast<const char *>(p.q) + (tok * p.q_stride + key_head * kDim) * kElement + part * 128;
-    const char *v_line = static_cast<const char *>(p.v) + (tok * p.v_stride + head * kDim) * kElement + part * 128;
-    asm volatile("prefetch.global.L2 [%0];\n" ::"l"(k_line));
-    asm volatile("prefetch.global.L2 [%0];\n" ::"l"(q_line));
-    asm volatile("prefetch.global.L2 [%0];\n" ::"l"(v_line));
+  auto load_gates = [&](std::uint32_t item) { // warps 8 and 9: one token per thread
+    const std::uint32_t t = tid - 256;
+    const std::uint32_t tok = min((item / p.value_heads) * kChunk + t, p.tokens - 1);
+    const std::size_t at = static_cast<std::size_t>(tok) * p.value_heads + item % p.value_heads;
+    sGateNext[t] = p.log_decay[at];
+    sGateNext[kChunk + t] = p.beta[at];
   };
+  std::uint32_t rows_in_flight = 0;
+  if (blockIdx.x < items) {
+    if (copier) {
+      issue_rows(blockIdx.x);
+      rows_in_flight = 1;
+    }
+    if (warp == 8 || warp == 9) {
+      load_gates(blockIdx.x);
+    }
+  }
+  __syncthreads();
   ItemRegs<F32> cur;
   std::uint32_t iteration = 0;
   for (std::uint32_t item = blockIdx.x; item < items; item += gridDim.x, ++iteration) {
     const std::uint32_t phase = iteration & 1U;
-    cur = fetch(item);
-    if (item + gridDim.x < items) {
-      prefetch(item + gridDim.x);
+    PREP_STAMP(0);
+    wait(bar_raw, phase);
+    if (copier) {
+      rows_in_flight = 0;
     }
+    cur.k = read_half_rows<F32>(base + kPsRawK);
+    cur.q = read_half_rows<F32>(base + kPsRawQ);
+    cur.v = read_half_rows<F32>(base + kPsRawV);
     unsigned char *rec = p.workspace + static_cast<std::size_t>(item) * kRecBytes; // item = chunk * value_heads + head
 
     // ---- gates: running sum of the log decays (two tokens per lane, warp scan), beta ----
     const std::uint32_t tok0 = (item / p.value_heads) * kChunk;
     if (warp == 0) {
-      float a = tok0 + lane < p.tokens ? cur.gate : 0.0F;
-      float b = tok0 + lane + 32 < p.tokens ? cur.gate2 : 0.0F;
+      float a = tok0 + lane < p.tokens ? sGateNext[lane] : 0.0F;
+      float b = tok0 + lane + 32 < p.tokens ? sGateNext[lane + 32] : 0.0F;
 #pragma unroll
       for (int d = 1; d < 32; d <<= 1) {
         const float ua = __shfl_up_sync(0xFFFFFFFFU, a, d);
@@ -543,18 +634,20 @@ __global__ void __launch_bounds__(kPrepThreads, 1) gdn_chunk_prepare_kernel(cons
       sG[lane] = a;
       sG[lane + 32] = b;
     } else if (warp <= 2) {
-      sBeta[lane + 32 * (warp - 1)] = tok0 + lane + 32 * (warp - 1) < p.tokens ? cur.gate : 0.0F;
+      const std::uint32_t t = lane + 32 * (warp - 1);
+      sBeta[t] = tok0 + t < p.tokens ? sGateNext[kChunk + t] : 0.0F;
     }
-    if (copier) { // the previous item's W and U copies must have read their staging areas
-      asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
-    }
-    __syncthreads();
+    __syncthreads(); // every thread holds its pieces of the raw rows; the gates are in place
+    PREP_STAMP(1);
     if (tid < kChunk) {
       sBg[tid] = sBeta[tid] * __expf(sG[tid]);
       sCf[tid] = __expf(sG[tid | 15] - sG[tid]);
     }
 
     // ---- operand images ----
+    // The W and U staging areas of the item before (the lower half of the [K; Q] image, the MN-major K image and
+    // the head of the V image) are still being read by their copies to the record: the images that lie elsewhere
+    // are written first, the rest once the copier lane has seen those reads end.
     {
       const float e_row = __expf(sG[kChunk - 1] - sG[row]); // exp(G_C - G_row) <= 1
       const bool live = tok0 + row < p.tokens;
@@ -568,42 +661,62 @@ __global__ void __launch_bounds__(kPrepThreads, 1) gdn_chunk_prepare_kernel(cons
         sts128(o0, swap ? f[4] : f[0], swap ? f[5] : f[1], swap ? f[6] : f[2], swap ? f[7] : f[3]);
         sts128(o1, swap ? f[0] : f[4], swap ? f[1] : f[5], swap ? f[2] : f[6], swap ? f[3] : f[7]);
       };
+      auto rounded = [&](const HalfRowRegs<F32> &regs, int a, float (&f)[8]) {
+        unpack_piece<F32>(regs, a, live, f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          f[i] = tf32f(f[i]);
+        }
+      };
+      float f[8];
+      float scaled[8];
+      // first: diag(e) K (both halves of the dims), the upper k-blocks of [K; Q], the upper half of V
 #pragma unroll
       for (int a = 0; a < 2; ++a) {
-        const std::uint32_t dim = 64 * a + 8 * part;
-        const std::uint32_t mn = mn_offset(row, dim, kA3AtomBytes); // the eight dims are one 32-byte piece
-        float f[8];
-        float scaled[8];
-        unpack_piece<F32>(cur.k, a, live, f);
+        const std::uint32_t mn = mn_offset(row, 64 * a + 8 * part, kA3AtomBytes); // eight dims are one 32-byte piece
+        rounded(cur.k, a, f);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          f[i] = tf32f(f[i]);
           scaled[i] = tf32f(f[i] * e_row);
         }
-        store_piece(base + kPsKQ + image_offset(row, dim, kA1Block), base + kPsKQ + image_offset(row, dim + 4, kA1Block), f);
-        store_piece(base + kPsKb + mn, base + kPsKb + mn + 16, f);
         store_piece(base + kPsKe + mn, base + kPsKe + mn + 16, scaled);
-
-        unpack_piece<F32>(cur.q, a, live, f);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          f[i] = tf32f(f[i]);
-        }
+      }
+      {
+        const std::uint32_t dim = 64 + 8 * part;
+        const std::uint32_t mn = mn_offset(row, dim, kA3AtomBytes);
+        rounded(cur.k, 1, f);
+        store_piece(base + kPsKQ + image_offset(row, dim, kA1Block), base + kPsKQ + image_offset(row, dim + 4, kA1Block), f);
+        rounded(cur.q, 1, f);
         store_piece(base + kPsKQ + image_offset(kChunk + row, dim, kA1Block),
                     base + kPsKQ + image_offset(kChunk + row, dim + 4, kA1Block), f);
-
-        unpack_piece<F32>(cur.v, a, live, f);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          f[i] = tf32f(f[i]);
-        }
+        rounded(cur.v, 1, f);
         store_piece(base + kPsVb + mn, base + kPsVb + mn + 16, f);
+      }
+      if (copier) { // the previous item's W and U copies must have read their staging areas
+        asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
+      }
+      __syncthreads();
+      {
+        const std::uint32_t dim = 8 * part;
+        const std::uint32_t mn = mn_offset(row, dim, kA3AtomBytes);
+        rounded(cur.k, 0, f);
+        store_piece(base + kPsKQ + image_offset(row, dim, kA1Block), base + kPsKQ + image_offset(row, dim + 4, kA1Block), f);
+        store_piece(base + kPsKb + mn, base + kPsKb + mn + 16, f);
+        rounded(cur.q, 0, f);
+        store_piece(base + kPsKQ + image_offset(kChunk + row, dim, kA1Block),
+                    base + kPsKQ + image_offset(kChunk + row, dim + 4, kA1Block), f);
+        rounded(cur.v, 0, f);
+        store_piece(base + kPsVb + mn, base + kPsVb + mn + 16, f);
+        rounded(cur.k, 1, f);
+        const std::uint32_t mn1 = mn_offset(row, 64 + dim, kA3AtomBytes);
+        store_piece(base + kPsKb + mn1, base + kPsKb + mn1 + 16, f);
       }
     }
     fence_proxy_async();
     tcgen05_fence_before();
     __syncthreads();
 
+    PREP_STAMP(2);
     // ---- G = [K; Q] K^T ----
     if (copier && *abort_flag == 0) {
       // Q is rows 64..127 of every k-block of the [K; Q] image and rows 0..63 of the record's [Q; W] image
@@ -631,6 +744,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) gdn_chunk_prepare_kernel(cons
     // ---- rows of G: A (lower triangle, to shared memory) and P (to its staging image) ----
     {
       wait(bar_g, phase);
+    PREP_STAMP(3);
       tcgen05_fence_after();
       const std::uint32_t quarter = warp & 3;       // the 32 tensor-memory lanes this warp may read
       const std::uint32_t cg = warp >> 2;           // its 16 columns
@@ -639,6 +753,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) gdn_chunk_prepare_kernel(cons
       const bool is_p = quarter >= 2;               // rows 64..127 hold Q K^T
       float g[16];
       tmem_ld16(tmem + lane_base + 16 * cg, g);
+      PREP_STAMP(15);
       const float g_i = sG[i];
       const float scale_i = is_p ? 1.0F : sBeta[i];
       float out[16];
@@ -661,6 +776,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) gdn_chunk_prepare_kernel(cons
           out[e] = row_factor * sCf[16 * cg + e] * g[e];
         }
       }
+      PREP_STAMP(11);
       if (!is_p) {
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -674,10 +790,12 @@ __global__ void __launch_bounds__(kPrepThreads, 1) gdn_chunk_prepare_kernel(cons
                  tf32f(out[4 * c + 2]), tf32f(out[4 * c + 3]));
         }
       }
+      PREP_STAMP(12);
       fence_proxy_async();
       tcgen05_fence_before();
     }
     __syncthreads();
+    PREP_STAMP(4);
     if (copier && *abort_flag == 0) {
       bulk_copy_s2g(rec + kRecA2, base + kPsPstage, kA2Bytes);
       asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
@@ -712,60 +830,63 @@ __global__ void __launch_bounds__(kPrepThreads, 1) gdn_chunk_prepare_kernel(cons
       }
     }
     __syncthreads();
-    // ... then block (i, b) below the diagonal, one sub-diagonal at a time:
-    //   T_ib = -T_ii (sum over k = b .. i-1 of A_ik T_kb).
-    // A warp owns a whole block: lane (pair = lane / 4, quad = lane % 4) computes rows 2 pair, 2 pair + 1 and columns
-    // 4 quad .. + 3 of it, so a k step is two scalar loads of A, one 16-byte load of T and eight multiply-adds, and
-    // the intermediate sum goes through the block's own place in shared memory with warp-level ordering only.
-    {
-      const int pair = lane >> 2;
-      const int quad = lane & 3;
-#pragma unroll
-      for (int d = 1; d < 4; ++d) {
-        const int b = warp;
-        const int i = b + d;
-        if (i < 4) {
-          float y0[4] = {0.0F, 0.0F, 0.0F, 0.0F};
-          float y1[4] = {0.0F, 0.0F, 0.0F, 0.0F};
-          const float *a0 = sA + (16 * i + 2 * pair) * kPitchSq;
-          const float *a1 = a0 + kPitchSq;
-          const float *t_col = sT + 16 * b + 4 * quad;
-#pragma unroll 4
-          for (int k = 16 * b; k < 16 * i; ++k) {
-            const float4 t4 = *reinterpret_cast<const float4 *>(t_col + k * kPitchSq);
-            const float x0 = a0[k];
-            const float x1 = a1[k];
-            y0[0] += x0 * t4.x; y0[1] += x0 * t4.y; y0[2] += x0 * t4.z; y0[3] += x0 * t4.w;
-            y1[0] += x1 * t4.x; y1[1] += x1 * t4.y; y1[2] += x1 * t4.z; y1[3] += x1 * t4.w;
-          }
-          float *block = sT + (16 * i) * kPitchSq + 16 * b + 4 * quad;
-          *reinterpret_cast<float4 *>(block + (2 * pair) * kPitchSq) = make_float4(y0[0], y0[1], y0[2], y0[3]);
-          *reinterpret_cast<float4 *>(block + (2 * pair + 1) * kPitchSq) = make_float4(y1[0], y1[1], y1[2], y1[3]);
-          __syncwarp();
-          float z0[4] = {0.0F, 0.0F, 0.0F, 0.0F};
-          float z1[4] = {0.0F, 0.0F, 0.0F, 0.0F};
-          const float *d0 = sT + (16 * i + 2 * pair) * kPitchSq + 16 * i; // T_ii is lower triangular: zeros above
-          const float *d1 = d0 + kPitchSq;
-#pragma unroll 4
-          for (int m = 0; m < 16; ++m) {
-            const float4 y4 = *reinterpret_cast<const float4 *>(block + m * kPitchSq);
-            const float x0 = d0[m];
-            const float x1 = d1[m];
-            z0[0] -= x0 * y4.x; z0[1] -= x0 * y4.y; z0[2] -= x0 * y4.z; z0[3] -= x0 * y4.w;
-            z1[0] -= x1 * y4.x; z1[1] -= x1 * y4.y; z1[2] -= x1 * y4.z; z1[3] -= x1 * y4.w;
-          }
-          __syncwarp();
-          *reinterpret_cast<float4 *>(block + (2 * pair) * kPitchSq) = make_float4(z0[0], z0[1], z0[2], z0[3]);
-          *reinterpret_cast<float4 *>(block + (2 * pair + 1) * kPitchSq) = make_float4(z1[0], z1[1], z1[2], z1[3]);
-        }
-        if (d == 3 && copier) {
-          // what follows overwrites the Q rows of the [K; Q] image: their copies to the record must have read them
-          asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
-        }
-        __syncthreads();
+    PREP_STAMP(5);
+    // ... then the blocks below the diagonal by doubling: for M = [[M11, 0], [M21, M22]] the lower left block of the
+    // inverse is -M22^-1 M21 M11^-1.
+    //   step 1 (warps 0, 1):  T_10 = -T_11 (A_10 T_00),  T_32 = -T_33 (A_32 T_22)            16 x 16 blocks
+    //   step 2 (warps 0..3):  T[32..63][0..31] = -T[32..63][32..63] (A[32..63][0..31] T[0..31][0..31])
+    // on warp-level tensor tiles with split operands (FP32 accuracy).  An intermediate product sits in the place of
+    // the block of T that it becomes; triangular factors are only walked over their non-zero blocks.
+    if (warp < 2) {
+      const int b = 2 * warp;
+      const int i = b + 1;
+      float y[2][4] = {};
+      block_product<2>(y, sA, 16 * i, sT, 16 * b, 16 * b);
+      store_block(sT, 16 * i, 16 * b, y, 1.0F);
+      __syncwarp();
+      float z[2][4] = {};
+      block_product<2>(z, sT, 16 * i, sT, 16 * b, 16 * i);
+      __syncwarp();
+      store_block(sT, 16 * i, 16 * b, z, -1.0F);
+    }
+    __syncthreads();
+    PREP_STAMP(6);
+    if ((warp == 8 || warp == 9) && item + gridDim.x < items) {
+      load_gates(item + gridDim.x); // while four warps work below; consumed at the top of the next item
+    }
+    if (warp < 4) {
+      const int bi = 2 + (warp >> 1);
+      const int bj = warp & 1;
+      float y[2][4] = {};
+      if (bj == 0) { // T[0..31][0..31] is lower triangular: its second column block starts at row 16
+        block_product<4>(y, sA, 16 * bi, sT, 0, 0);
+      } else {
+        block_product<2>(y, sA, 16 * bi, sT, 16, 16);
       }
+      store_block(sT, 16 * bi, 16 * bj, y, 1.0F);
+      asm volatile("bar.sync 2, 128;\n" ::: "memory"); // block (3, bj) reads the product of row block 2 as well
+      float z[2][4] = {};
+      if (bi == 2) { // row block 2 of T[32..63][32..63] ends at column 47
+        block_product<2>(z, sT, 32, sT, 16 * bj, 32);
+      } else {
+        block_product<4>(z, sT, 48, sT, 16 * bj, 32);
+      }
+      asm volatile("bar.sync 2, 128;\n" ::: "memory"); // every product has been read before a block replaces it
+      store_block(sT, 16 * bi, 16 * bj, z, -1.0F);
+    }
+    if (copier) {
+      // what follows overwrites the Q rows of the [K; Q] image: their copies to the record must have read them
+      asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
+    }
+    __syncthreads();
+    // The staging areas of P and diag(e) K, the upper half of the [K; Q] image and A are idle from here to the end
+    // of the item: the next item's rows land there.
+    if (copier && item + gridDim.x < items && *abort_flag == 0) {
+      issue_rows(item + gridDim.x);
+      rows_in_flight = 1;
     }
 
+    PREP_STAMP(7);
     // ---- [T diag(beta gamma); T diag(beta)] as one K-major image (the first product has completed, and the copies
     // of the Q rows, issued long ago, have read them: thread 0 made sure before the barrier above) ----
     {
@@ -781,10 +902,13 @@ __global__ void __launch_bounds__(kPrepThreads, 1) gdn_chunk_prepare_kernel(cons
                tf32f(t4.y * be.y), tf32f(t4.z * be.z), tf32f(t4.w * be.w));
       }
     }
+    PREP_STAMP(13);
     fence_proxy_async();
+    PREP_STAMP(14);
     tcgen05_fence_before();
     __syncthreads();
 
+    PREP_STAMP(8);
     // ---- the two products with T: B operands are K and V as stored (eight tokens = 1 KiB per step) ----
     if (warp == 4) {
       tcgen05_fence_after();
@@ -810,6 +934,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) gdn_chunk_prepare_kernel(cons
     // ---- W (rows 0..63 of the first) and U (rows 64..127 of the second) to their staging images ----
     {
       wait(bar_wu, phase);
+    PREP_STAMP(9);
       tcgen05_fence_after();
       const std::uint32_t quarter = warp & 3;
       const std::uint32_t cg = warp >> 2;           // 32 columns: k-block `cg` of W, slice `cg` of U
@@ -836,6 +961,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1) gdn_chunk_prepare_kernel(cons
       tcgen05_fence_before();
     }
     __syncthreads();
+    PREP_STAMP(10);
     if (copier && *abort_flag == 0) {
 #pragma unroll
       for (std::uint32_t kb = 0; kb < 4; ++kb) { // rows 64..127 of every k-block of the [Q; W] image
@@ -850,6 +976,12 @@ __global__ void __launch_bounds__(kPrepThreads, 1) gdn_chunk_prepare_kernel(cons
   }
   if (copier) {
     asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
+    if (rows_in_flight != 0) {
+      // only after a wait ran out: rows were asked for and nobody took them; let them land before the CTA goes
+      const long long started = clock64();
+      while (!mbarrier_try_wait(bar_raw, iteration & 1U) && clock64() - started < kPrepWaitLimitCycles) {
+      }
+    }
   }
 
   tcgen05_fence_before();
@@ -1305,7 +1437,17 @@ template <bool F32> void launch(const ChunkParams &params, cudaStream_t stream) 
   configure_once<F32>();
   const std::uint32_t items = params.chunks * params.value_heads;
   const std::uint32_t prepare_ctas = items < static_cast<std::uint32_t>(sm_count()) ? items : sm_count();
-  gdn_chunk_prepare_kernel<F32><<<prepare_ctas, kPrepThreads, kPrepSmemBytes, stream>>>(params);
+  // K, Q, V rows as tensor maps: a box is the 64 tokens x 128 elements of one (chunk, head)
+  TensorMapBytes k_map;
+  TensorMapBytes q_map;
+  TensorMapBytes v_map;
+  encode_plain_rows_map(&k_map, params.k, F32, static_cast<std::uint64_t>(params.key_heads) * kDim, params.k_stride,
+                        params.tokens, kDim, kChunk);
+  encode_plain_rows_map(&q_map, params.q, F32, static_cast<std::uint64_t>(params.key_heads) * kDim, params.q_stride,
+                        params.tokens, kDim, kChunk);
+  encode_plain_rows_map(&v_map, params.v, F32, static_cast<std::uint64_t>(params.value_heads) * kDim, params.v_stride,
+                        params.tokens, kDim, kChunk);
+  gdn_chunk_prepare_kernel<F32><<<prepare_ctas, kPrepThreads, kPrepSmemBytes, stream>>>(params, k_map, q_map, v_map);
   cuda_ok(cudaGetLastError(), "gated-delta prepare launch");
   TensorMapBytes out_map;
   encode_f32_rows_map(&out_map, params.out, static_cast<std::uint64_t>(params.value_heads) * kDim, params.tokens,

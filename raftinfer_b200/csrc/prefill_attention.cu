@@ -1630,6 +1630,23 @@ void encode_f32_rows_map(void *map_out, void *base, std::uint64_t row_floats, st
   require(rc == CUDA_SUCCESS, "tensor map encoding failed", RIB200_STATUS_CUDA_ERROR);
 }
 
+void encode_plain_rows_map(void *map_out, const void *base, bool f32, std::uint64_t row_elements,
+                           std::uint64_t row_stride_elements, std::uint64_t rows, std::uint32_t box_elements,
+                           std::uint32_t box_rows) {
+  const std::uint64_t element = f32 ? 4 : 2;
+  require(reinterpret_cast<std::uintptr_t>(base) % 16 == 0 && (row_stride_elements * element) % 16 == 0,
+          "rows read through a tensor map must start on 16-byte boundaries");
+  const cuuint64_t dims[2] = {row_elements, rows};
+  const cuuint64_t strides[1] = {row_stride_elements * element};
+  const cuuint32_t box[2] = {box_elements, box_rows};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  const CUresult rc = encode_tiled_entry()(
+      static_cast<CUtensorMap *>(map_out), f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+      const_cast<void *>(base), dims, strides, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE,
+      CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  require(rc == CUDA_SUCCESS, "tensor map encoding failed", RIB200_STATUS_CUDA_ERROR);
+}
+
 #ifdef RIB200_TRACE
 extern "C" int rib200_debug_read_trace(long long *host, std::size_t count) {
   return static_cast<int>(cudaMemcpyFromSymbol(host, g_trace, count * sizeof(long long)));
