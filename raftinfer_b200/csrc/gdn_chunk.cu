@@ -34,6 +34,7 @@
 
 #include <cstdint>
 #include <mutex>
+#include <type_traits>
 
 namespace rib200 {
 namespace {
@@ -71,6 +72,13 @@ __host__ __device__ constexpr std::uint32_t mn_offset(std::uint32_t token, std::
   return (dim >> 5) * atom_bytes + token * kRowBytes + ((((dim & 31U) >> 3) ^ (token & 3U)) << 5) + ((dim & 7U) << 2);
 }
 
+// The prepare kernel writes piece `part` (dims 32 kb + 4 part ..) of row `row` with these offsets spelled out:
+static_assert(mn_offset(5, 32 + 4 * 3, kA3AtomBytes) ==
+                  kA3AtomBytes + 5 * kRowBytes + ((((3U >> 1) ^ (5U & 3U)) << 5) | ((3U & 1U) << 4)),
+              "MN-major piece offset");
+static_assert(image_offset(13, 64 + 4 * 6, kA1Block) == 2 * kA1Block + 13 * kRowBytes + ((6U ^ (13U & 7U)) << 4),
+              "K-major piece offset");
+
 struct ChunkParams {
   const void *q, *k, *v;
   std::size_t q_stride, k_stride, v_stride;
@@ -86,12 +94,19 @@ struct ChunkParams {
   std::uint32_t value_heads;
 };
 
-__device__ __forceinline__ std::uint32_t tf32(float x) {
-  std::uint32_t r;
-  asm("cvt.rna.tf32.f32 %0, %1;\n" : "=r"(r) : "f"(x));
-  return r;
-}
+// Round to TF32 (10 mantissa bits), nearest with ties away from zero, as cvt.rna.tf32.f32 does for finite numbers:
+// half a unit of the last kept place is added to the magnitude and the 13 low bits are dropped.  Two integer
+// instructions at full rate; the conversion instruction goes through the slow conversion pipe, and the kernels
+// below round tens of thousands of values per item.
+__device__ __forceinline__ std::uint32_t tf32(float x) { return (__float_as_uint(x) + 0x1000U) & 0xFFFFE000U; }
 __device__ __forceinline__ float tf32f(float x) { return __uint_as_float(tf32(x)); }
+// e^x through the base-2 unit; results below the normal range are flushed to zero, which is what every use here
+// (decay factors <= 1 and their products with bounded numbers) wants, and spares the code around a subnormal result.
+__device__ __forceinline__ float exp_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x * 1.4426950408889634F));
+  return y;
+}
 
 // Rows [tok0, tok0 + 64) of a [token][heads][128] operand (head `head`) go to dst[64][pitch] as FP32 in two halves,
 // so that other work can run while the loads are in flight: fetch_rows reads this thread's 32 elements of its row
@@ -370,58 +385,48 @@ constexpr std::uint32_t kPrepTmemColumns = 512;  // G at 0 (64 columns), [W; *] 
 constexpr std::uint32_t kIdescG = idesc_tf32(kChunk, false, false);
 constexpr std::uint32_t kIdescWU = idesc_tf32(kDim, false, true);
 
-// Two 8-element pieces of one row per thread: FP32 inputs take four 16-byte words, BF16 inputs two.
-template <bool F32> struct HalfRowRegs {
-  uint4 v[F32 ? 4 : 2];
+// A thread's share of one raw row: piece `part` (4 elements) of each of the four k-blocks (32 dims) of row tid / 8,
+// so that the eight lanes of a row read and later store eight consecutive 16-byte pieces of one 128-byte image row.
+template <bool F32> struct RowPieces {
+  using Word = std::conditional_t<F32, uint4, uint2>;
+  Word v[4];
 };
 template <bool F32> struct ItemRegs {
-  HalfRowRegs<F32> k, q, v;
+  RowPieces<F32> k, q, v;
 };
-
-// Pieces `part` and `part + 8` of row tid / 8 of a raw [64][128] tile in shared memory.  FP32 pieces are two 16-byte
-// words 32 bytes apart from the next lane's: the upper four parts read theirs in the other order, so that the eight
-// lanes of a row never meet in a bank.
-template <bool F32> __device__ __forceinline__ HalfRowRegs<F32> read_half_rows(std::uint32_t tile) {
-  HalfRowRegs<F32> regs;
+__device__ __forceinline__ uint2 lds64u(std::uint32_t addr) {
+  uint2 v;
+  asm volatile("ld.shared.v2.b32 {%0, %1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+  return v;
+}
+// from a raw [64][128] tile in shared memory (rows past the last token were filled with zeros by the copy)
+template <bool F32> __device__ __forceinline__ RowPieces<F32> read_pieces(std::uint32_t tile) {
+  RowPieces<F32> regs;
   const std::uint32_t row = threadIdx.x >> 3;
   const std::uint32_t part = threadIdx.x & 7U;
 #pragma unroll
-  for (int a = 0; a < 2; ++a) {
+  for (int kb = 0; kb < 4; ++kb) {
     if constexpr (F32) {
-      const std::uint32_t at = tile + row * 512U + 256U * a + 32U * part;
-      const bool swap = (part & 4U) != 0;
-      const uint4 x = lds128u(at + (swap ? 16U : 0U));
-      const uint4 y = lds128u(at + (swap ? 0U : 16U));
-      regs.v[2 * a] = swap ? y : x;
-      regs.v[2 * a + 1] = swap ? x : y;
+      regs.v[kb] = lds128u(tile + row * 512U + 128U * kb + 16U * part);
     } else {
-      regs.v[a] = lds128u(tile + row * 256U + 128U * a + 16U * part);
+      regs.v[kb] = lds64u(tile + row * 256U + 64U * kb + 8U * part);
     }
   }
   return regs;
 }
-
-// the eight values of piece `a` of a fetched row; all zero when the row lies past the last token
+// the four values of a piece as TF32 numbers (BF16 inputs are TF32 numbers as they are)
 template <bool F32>
-__device__ __forceinline__ void unpack_piece(const HalfRowRegs<F32> &regs, int a, bool live, float (&f)[8]) {
+__device__ __forceinline__ void unpack_piece(const typename RowPieces<F32>::Word &w, float (&f)[4]) {
   if constexpr (F32) {
-    const uint4 lo = regs.v[2 * a];
-    const uint4 hi = regs.v[2 * a + 1];
-    f[0] = __uint_as_float(lo.x); f[1] = __uint_as_float(lo.y); f[2] = __uint_as_float(lo.z); f[3] = __uint_as_float(lo.w);
-    f[4] = __uint_as_float(hi.x); f[5] = __uint_as_float(hi.y); f[6] = __uint_as_float(hi.z); f[7] = __uint_as_float(hi.w);
+    f[0] = tf32f(__uint_as_float(w.x));
+    f[1] = tf32f(__uint_as_float(w.y));
+    f[2] = tf32f(__uint_as_float(w.z));
+    f[3] = tf32f(__uint_as_float(w.w));
   } else {
-    const std::uint32_t w[4] = {regs.v[a].x, regs.v[a].y, regs.v[a].z, regs.v[a].w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      f[2 * i] = __uint_as_float(w[i] << 16);
-      f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000U);
-    }
-  }
-  if (!live) {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      f[i] = 0.0F;
-    }
+    f[0] = __uint_as_float(w.x << 16);
+    f[1] = __uint_as_float(w.x & 0xFFFF0000U);
+    f[2] = __uint_as_float(w.y << 16);
+    f[3] = __uint_as_float(w.y & 0xFFFF0000U);
   }
 }
 
@@ -490,6 +495,30 @@ __device__ __forceinline__ void block_product(float (&acc)[2][4], const float *L
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       acc[n][e] += lo_hi[n][e] + hi_lo[n][e];
+    }
+  }
+}
+// the block, times -1, goes into the [T diag(beta gamma); T diag(beta)] image at `tstack` (rows r0 .., columns c0 ..)
+__device__ __forceinline__ void store_block_scaled(std::uint32_t tstack, int r0, int c0, const float (&acc)[2][4],
+                                                   const float *bg, const float *be) {
+  const int g = (threadIdx.x & 31) >> 2;
+  const int t = threadIdx.x & 3;
+#pragma unroll
+  for (int n = 0; n < 2; ++n) {
+    const int col = c0 + 8 * n + 2 * t;
+    const float2 sg = *reinterpret_cast<const float2 *>(bg + col);
+    const float2 se = *reinterpret_cast<const float2 *>(be + col);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const std::uint32_t row = static_cast<std::uint32_t>(r0 + g + 8 * h);
+      const float x = -acc[n][2 * h];
+      const float y = -acc[n][2 * h + 1];
+      asm volatile("st.shared.v2.b32 [%0], {%1, %2};\n" ::"r"(tstack + image_offset(row, col, kA1Block)),
+                   "r"(tf32(x * sg.x)), "r"(tf32(y * sg.y))
+                   : "memory");
+      asm volatile("st.shared.v2.b32 [%0], {%1, %2};\n" ::"r"(tstack + image_offset(kChunk + row, col, kA1Block)),
+                   "r"(tf32(x * se.x)), "r"(tf32(y * se.y))
+                   : "memory");
     }
   }
 }
@@ -611,9 +640,9 @@ __global__ void __launch_bounds__(kPrepThreads, 1)
     if (copier) {
       rows_in_flight = 0;
     }
-    cur.k = read_half_rows<F32>(base + kPsRawK);
-    cur.q = read_half_rows<F32>(base + kPsRawQ);
-    cur.v = read_half_rows<F32>(base + kPsRawV);
+    cur.k = read_pieces<F32>(base + kPsRawK);
+    cur.q = read_pieces<F32>(base + kPsRawQ);
+    cur.v = read_pieces<F32>(base + kPsRawV);
     unsigned char *rec = p.workspace + static_cast<std::size_t>(item) * kRecBytes; // item = chunk * value_heads + head
 
     // ---- gates: running sum of the log decays (two tokens per lane, warp scan), beta ----
@@ -640,8 +669,8 @@ __global__ void __launch_bounds__(kPrepThreads, 1)
     __syncthreads(); // every thread holds its pieces of the raw rows; the gates are in place
     PREP_STAMP(1);
     if (tid < kChunk) {
-      sBg[tid] = sBeta[tid] * __expf(sG[tid]);
-      sCf[tid] = __expf(sG[tid | 15] - sG[tid]);
+      sBg[tid] = sBeta[tid] * exp_fast(sG[tid]);
+      sCf[tid] = exp_fast(sG[tid | 15] - sG[tid]);
     }
 
     // ---- operand images ----
@@ -649,67 +678,43 @@ __global__ void __launch_bounds__(kPrepThreads, 1)
     // the head of the V image) are still being read by their copies to the record: the images that lie elsewhere
     // are written first, the rest once the copier lane has seen those reads end.
     {
-      const float e_row = __expf(sG[kChunk - 1] - sG[row]); // exp(G_C - G_row) <= 1
-      const bool live = tok0 + row < p.tokens;
-      // A piece is two 16-byte stores.  The eight lanes that store together are the eight parts of one row; parts
-      // p and p + 4 fall into the same banks (their k-blocks lie 16 KiB apart), so parts 4..7 store their second
-      // half first.
-      const bool swap = (part & 4U) != 0;
-      auto store_piece = [&](std::uint32_t first, std::uint32_t second, const float (&f)[8]) {
-        const std::uint32_t o0 = swap ? second : first;
-        const std::uint32_t o1 = swap ? first : second;
-        sts128(o0, swap ? f[4] : f[0], swap ? f[5] : f[1], swap ? f[6] : f[2], swap ? f[7] : f[3]);
-        sts128(o1, swap ? f[0] : f[4], swap ? f[1] : f[5], swap ? f[2] : f[6], swap ? f[3] : f[7]);
-      };
-      auto rounded = [&](const HalfRowRegs<F32> &regs, int a, float (&f)[8]) {
-        unpack_piece<F32>(regs, a, live, f);
+      const float e_row = exp_fast(sG[kChunk - 1] - sG[row]); // exp(G_C - G_row) <= 1
+      // Where this thread's piece of k-block kb goes: K-major images are [k-block][row][128 bytes] with the 16-byte
+      // piece index XORed with row % 8; MN-major images (see mn_offset) XOR the 32-byte piece index with row % 4.
+      const std::uint32_t k_major = row * kRowBytes + ((part ^ (row & 7U)) << 4);
+      const std::uint32_t mn_major = row * kRowBytes + ((((part >> 1) ^ (row & 3U)) << 5) | ((part & 1U) << 4));
+      const std::uint32_t image_k = base + kPsKQ + k_major;
+      const std::uint32_t image_q = image_k + kChunk * kRowBytes;
+      float f[4];
+      // first: diag(e) K, the upper k-blocks of [K; Q], the upper half of V
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          f[i] = tf32f(f[i]);
+      for (std::uint32_t kb = 0; kb < 4; ++kb) {
+        unpack_piece<F32>(cur.k.v[kb], f);
+        sts128(base + kPsKe + kb * kA3AtomBytes + mn_major, tf32f(f[0] * e_row), tf32f(f[1] * e_row), tf32f(f[2] * e_row),
+               tf32f(f[3] * e_row));
+        if (kb >= 2) {
+          sts128(image_k + kb * kA1Block, f[0], f[1], f[2], f[3]);
+          unpack_piece<F32>(cur.q.v[kb], f);
+          sts128(image_q + kb * kA1Block, f[0], f[1], f[2], f[3]);
+          unpack_piece<F32>(cur.v.v[kb], f);
+          sts128(base + kPsVb + kb * kA3AtomBytes + mn_major, f[0], f[1], f[2], f[3]);
         }
-      };
-      float f[8];
-      float scaled[8];
-      // first: diag(e) K (both halves of the dims), the upper k-blocks of [K; Q], the upper half of V
-#pragma unroll
-      for (int a = 0; a < 2; ++a) {
-        const std::uint32_t mn = mn_offset(row, 64 * a + 8 * part, kA3AtomBytes); // eight dims are one 32-byte piece
-        rounded(cur.k, a, f);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          scaled[i] = tf32f(f[i] * e_row);
-        }
-        store_piece(base + kPsKe + mn, base + kPsKe + mn + 16, scaled);
-      }
-      {
-        const std::uint32_t dim = 64 + 8 * part;
-        const std::uint32_t mn = mn_offset(row, dim, kA3AtomBytes);
-        rounded(cur.k, 1, f);
-        store_piece(base + kPsKQ + image_offset(row, dim, kA1Block), base + kPsKQ + image_offset(row, dim + 4, kA1Block), f);
-        rounded(cur.q, 1, f);
-        store_piece(base + kPsKQ + image_offset(kChunk + row, dim, kA1Block),
-                    base + kPsKQ + image_offset(kChunk + row, dim + 4, kA1Block), f);
-        rounded(cur.v, 1, f);
-        store_piece(base + kPsVb + mn, base + kPsVb + mn + 16, f);
       }
       if (copier) { // the previous item's W and U copies must have read their staging areas
         asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
       }
       __syncthreads();
-      {
-        const std::uint32_t dim = 8 * part;
-        const std::uint32_t mn = mn_offset(row, dim, kA3AtomBytes);
-        rounded(cur.k, 0, f);
-        store_piece(base + kPsKQ + image_offset(row, dim, kA1Block), base + kPsKQ + image_offset(row, dim + 4, kA1Block), f);
-        store_piece(base + kPsKb + mn, base + kPsKb + mn + 16, f);
-        rounded(cur.q, 0, f);
-        store_piece(base + kPsKQ + image_offset(kChunk + row, dim, kA1Block),
-                    base + kPsKQ + image_offset(kChunk + row, dim + 4, kA1Block), f);
-        rounded(cur.v, 0, f);
-        store_piece(base + kPsVb + mn, base + kPsVb + mn + 16, f);
-        rounded(cur.k, 1, f);
-        const std::uint32_t mn1 = mn_offset(row, 64 + dim, kA3AtomBytes);
-        store_piece(base + kPsKb + mn1, base + kPsKb + mn1 + 16, f);
+#pragma unroll
+      for (std::uint32_t kb = 0; kb < 4; ++kb) {
+        unpack_piece<F32>(cur.k.v[kb], f);
+        sts128(base + kPsKb + kb * kA3AtomBytes + mn_major, f[0], f[1], f[2], f[3]);
+        if (kb < 2) {
+          sts128(image_k + kb * kA1Block, f[0], f[1], f[2], f[3]);
+          unpack_piece<F32>(cur.q.v[kb], f);
+          sts128(image_q + kb * kA1Block, f[0], f[1], f[2], f[3]);
+          unpack_piece<F32>(cur.v.v[kb], f);
+          sts128(base + kPsVb + kb * kA3AtomBytes + mn_major, f[0], f[1], f[2], f[3]);
+        }
       }
     }
     fence_proxy_async();
@@ -767,10 +772,10 @@ __global__ void __launch_bounds__(kPrepThreads, 1)
         for (int e = 0; e < 16; ++e) {
           const std::uint32_t j = 16 * cg + e;
           const bool live = is_p ? j <= i : j < i;
-          out[e] = live ? scale_i * __expf(g_i - sG[j]) * g[e] : 0.0F;
+          out[e] = live ? scale_i * exp_fast(g_i - sG[j]) * g[e] : 0.0F;
         }
       } else { // below it: exp(G_i - G_j) = exp(G_i - R) exp(R - G_j), R the running sum at the end of the column block
-        const float row_factor = scale_i * __expf(g_i - sG[16 * cg + 15]);
+        const float row_factor = scale_i * exp_fast(g_i - sG[16 * cg + 15]);
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
           out[e] = row_factor * sCf[16 * cg + e] * g[e];
@@ -829,8 +834,41 @@ __global__ void __launch_bounds__(kPrepThreads, 1)
         sT[(16 * bi + ((e >> 4) & 15)) * kPitchSq + 16 * bj + (e & 15)] = 0.0F;
       }
     }
+    if (copier) {
+      // The image of [T diag(beta gamma); T diag(beta)] is written, from here on, over the lower k-blocks of the
+      // [K; Q] image: the copies of its Q rows to the record (issued long ago) must have read them.  The copy of P
+      // is waited for as well, so that its staging area can take the next item's rows later.
+      asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
+    }
     __syncthreads();
     PREP_STAMP(5);
+    // Eight columns of a row of T that are final go into the image, scaled per column; idle warps do this for the
+    // diagonal blocks and the zeros above them during step 1 below, and for the blocks of step 1 during step 2.
+    auto image_unit = [&](std::uint32_t r, std::uint32_t part8) {
+      const std::uint32_t j0 = 8 * part8;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const float4 t4 = *reinterpret_cast<const float4 *>(sT + r * kPitchSq + j0 + 4 * c);
+        const float4 bg = *reinterpret_cast<const float4 *>(sBg + j0 + 4 * c);
+        const float4 be = *reinterpret_cast<const float4 *>(sBeta + j0 + 4 * c);
+        sts128(base + kPsTstack + image_offset(r, j0 + 4 * c, kA1Block), tf32f(t4.x * bg.x), tf32f(t4.y * bg.y),
+               tf32f(t4.z * bg.z), tf32f(t4.w * bg.w));
+        sts128(base + kPsTstack + image_offset(kChunk + r, j0 + 4 * c, kA1Block), tf32f(t4.x * be.x),
+               tf32f(t4.y * be.y), tf32f(t4.z * be.z), tf32f(t4.w * be.w));
+      }
+    };
+    if (tid >= 64 && tid < 64 + 320) { // units on or above the block diagonal: 128 + 96 + 64 + 32
+      const std::uint32_t idx = tid - 64;
+      if (idx < 128) {
+        image_unit(idx >> 3, idx & 7U);
+      } else if (idx < 224) {
+        image_unit(16 + (idx - 128) / 6, 2 + (idx - 128) % 6);
+      } else if (idx < 288) {
+        image_unit(32 + ((idx - 224) >> 2), 4 + ((idx - 224) & 3U));
+      } else {
+        image_unit(48 + ((idx - 288) >> 1), 6 + ((idx - 288) & 1U));
+      }
+    }
     // ... then the blocks below the diagonal by doubling: for M = [[M11, 0], [M21, M22]] the lower left block of the
     // inverse is -M22^-1 M21 M11^-1.
     //   step 1 (warps 0, 1):  T_10 = -T_11 (A_10 T_00),  T_32 = -T_33 (A_32 T_22)            16 x 16 blocks
@@ -854,6 +892,11 @@ __global__ void __launch_bounds__(kPrepThreads, 1)
     if ((warp == 8 || warp == 9) && item + gridDim.x < items) {
       load_gates(item + gridDim.x); // while four warps work below; consumed at the top of the next item
     }
+    if (warp == 4 || warp == 5) { // the two blocks of step 1: rows 16..31 x columns 0..15, rows 48..63 x columns 32..47
+      const std::uint32_t idx = tid - 128;
+      const std::uint32_t half = idx >> 5;
+      image_unit(16 + 32 * half + ((idx & 31U) >> 1), 4 * half + (idx & 1U));
+    }
     if (warp < 4) {
       const int bi = 2 + (warp >> 1);
       const int bj = warp & 1;
@@ -871,13 +914,10 @@ __global__ void __launch_bounds__(kPrepThreads, 1)
       } else {
         block_product<4>(z, sT, 48, sT, 16 * bj, 32);
       }
-      asm volatile("bar.sync 2, 128;\n" ::: "memory"); // every product has been read before a block replaces it
-      store_block(sT, 16 * bi, 16 * bj, z, -1.0F);
+      store_block_scaled(base + kPsTstack, 16 * bi, 16 * bj, z, sBg, sBeta); // nobody reads these blocks of T again
     }
-    if (copier) {
-      // what follows overwrites the Q rows of the [K; Q] image: their copies to the record must have read them
-      asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
-    }
+    fence_proxy_async(); // the image is complete: the products below read it through the async proxy
+    tcgen05_fence_before();
     __syncthreads();
     // The staging areas of P and diag(e) K, the upper half of the [K; Q] image and A are idle from here to the end
     // of the item: the next item's rows land there.
@@ -887,27 +927,6 @@ __global__ void __launch_bounds__(kPrepThreads, 1)
     }
 
     PREP_STAMP(7);
-    // ---- [T diag(beta gamma); T diag(beta)] as one K-major image (the first product has completed, and the copies
-    // of the Q rows, issued long ago, have read them: thread 0 made sure before the barrier above) ----
-    {
-      const std::uint32_t j0 = 8 * part;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const float4 t4 = *reinterpret_cast<const float4 *>(sT + row * kPitchSq + j0 + 4 * c);
-        const float4 bg = *reinterpret_cast<const float4 *>(sBg + j0 + 4 * c);
-        const float4 be = *reinterpret_cast<const float4 *>(sBeta + j0 + 4 * c);
-        sts128(base + kPsTstack + image_offset(row, j0 + 4 * c, kA1Block), tf32f(t4.x * bg.x), tf32f(t4.y * bg.y),
-               tf32f(t4.z * bg.z), tf32f(t4.w * bg.w));
-        sts128(base + kPsTstack + image_offset(kChunk + row, j0 + 4 * c, kA1Block), tf32f(t4.x * be.x),
-               tf32f(t4.y * be.y), tf32f(t4.z * be.z), tf32f(t4.w * be.w));
-      }
-    }
-    PREP_STAMP(13);
-    fence_proxy_async();
-    PREP_STAMP(14);
-    tcgen05_fence_before();
-    __syncthreads();
-
     PREP_STAMP(8);
     // ---- the two products with T: B operands are K and V as stored (eight tokens = 1 KiB per step) ----
     if (warp == 4) {
@@ -955,7 +974,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1)
         for (std::uint32_t c = 0; c < 8; ++c) {
           sts128(stage + (i * kPitchU + 4 * c) * 4, x[4 * c], x[4 * c + 1], x[4 * c + 2], x[4 * c + 3]);
         }
-        sts32(stage + (kChunk * kPitchU + i) * 4, __float_as_uint(__expf(sG[i])));
+        sts32(stage + (kChunk * kPitchU + i) * 4, __float_as_uint(exp_fast(sG[i])));
       }
       fence_proxy_async();
       tcgen05_fence_before();
