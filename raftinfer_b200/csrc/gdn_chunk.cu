@@ -404,12 +404,21 @@ template <bool F32> __device__ __forceinline__ RowPieces<F32> read_pieces(std::u
   RowPieces<F32> regs;
   const std::uint32_t row = threadIdx.x >> 3;
   const std::uint32_t part = threadIdx.x & 7U;
+  if constexpr (F32) {
 #pragma unroll
-  for (int kb = 0; kb < 4; ++kb) {
-    if constexpr (F32) {
+    for (int kb = 0; kb < 4; ++kb) {
       regs.v[kb] = lds128u(tile + row * 512U + 128U * kb + 16U * part);
-    } else {
-      regs.v[kb] = lds64u(tile + row * 256U + 64U * kb + 8U * part);
+    }
+  } else {
+    // An 8-byte load is served sixteen lanes (two rows) at a time, and rows lie 256 bytes apart: odd rows take the
+    // two k-blocks of a pair in the other order, so that the two rows never read the same banks.
+    const std::uint32_t odd = row & 1U;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const uint2 x = lds64u(tile + row * 256U + 64U * (2 * h + odd) + 8U * part);
+      const uint2 y = lds64u(tile + row * 256U + 64U * (2 * h + 1 - odd) + 8U * part);
+      regs.v[2 * h] = odd ? y : x;
+      regs.v[2 * h + 1] = odd ? x : y;
     }
   }
   return regs;
@@ -564,7 +573,7 @@ __global__ void __launch_bounds__(kPrepThreads, 1)
   if (tid == 0) {
     mbarrier_init(bar_g, 1);
     mbarrier_init(bar_wu, 1);
-    mbarrier_init(bar_raw, 1);
+    mbarrier_init(bar_raw, 2); // the rows of an item are asked for in two batches
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
@@ -603,15 +612,26 @@ __global__ void __launch_bounds__(kPrepThreads, 1)
   // The raw K, Q and V rows of an item come in as three tensor-map copies (rows past the last token arrive as
   // zeros), issued by the copier lane an item ahead; its gates are read by two otherwise idle warps at the same time.
   constexpr std::uint32_t kRawBytes = kChunk * kDim * (F32 ? 4 : 2);
-  auto issue_rows = [&](std::uint32_t item) {
+  // Batch 1 (K, Q, and V when it fits the P staging area alone, i.e. BF16 rows) can go out as soon as the copies of
+  // the Q rows, of diag(e) K and of P have read their areas; FP32 V rows also cover A and wait for the inversion.
+  auto issue_rows = [&](std::uint32_t item, bool first_batch) {
     const std::uint32_t head = item % p.value_heads;
     const int tok0 = static_cast<int>((item / p.value_heads) * kChunk);
     const int key_x = static_cast<int>((head % p.key_heads) * kDim);
     fence_proxy_async(); // the landing areas were last touched by ordinary loads and stores
-    mbarrier_expect_tx(bar_raw, 3 * kRawBytes);
-    tma_load_2d(base + kPsRawK, &k_map, key_x, tok0, bar_raw);
-    tma_load_2d(base + kPsRawQ, &q_map, key_x, tok0, bar_raw);
-    tma_load_2d(base + kPsRawV, &v_map, static_cast<int>(head * kDim), tok0, bar_raw);
+    if (first_batch) {
+      mbarrier_expect_tx(bar_raw, (F32 ? 2 : 3) * kRawBytes);
+      tma_load_2d(base + kPsRawK, &k_map, key_x, tok0, bar_raw);
+      tma_load_2d(base + kPsRawQ, &q_map, key_x, tok0, bar_raw);
+    }
+    if (first_batch != F32) {
+      if (!first_batch) {
+        mbarrier_expect_tx(bar_raw, kRawBytes);
+      }
+      tma_load_2d(base + kPsRawV, &v_map, static_cast<int>(head * kDim), tok0, bar_raw);
+    } else if (!first_batch) {
+      mbarrier_arrive(bar_raw);
+    }
   };
   auto load_gates = [&](std::uint32_t item) { // warps 8 and 9: one token per thread
     const std::uint32_t t = tid - 256;
@@ -623,7 +643,8 @@ __global__ void __launch_bounds__(kPrepThreads, 1)
   std::uint32_t rows_in_flight = 0;
   if (blockIdx.x < items) {
     if (copier) {
-      issue_rows(blockIdx.x);
+      issue_rows(blockIdx.x, true);
+      issue_rows(blockIdx.x, false);
       rows_in_flight = 1;
     }
     if (warp == 8 || warp == 9) {
@@ -637,12 +658,14 @@ __global__ void __launch_bounds__(kPrepThreads, 1)
     const std::uint32_t phase = iteration & 1U;
     PREP_STAMP(0);
     wait(bar_raw, phase);
+    PREP_STAMP(13);
     if (copier) {
       rows_in_flight = 0;
     }
     cur.k = read_pieces<F32>(base + kPsRawK);
     cur.q = read_pieces<F32>(base + kPsRawQ);
     cur.v = read_pieces<F32>(base + kPsRawV);
+    PREP_STAMP(14);
     unsigned char *rec = p.workspace + static_cast<std::size_t>(item) * kRecBytes; // item = chunk * value_heads + head
 
     // ---- gates: running sum of the log decays (two tokens per lane, warp scan), beta ----
@@ -841,6 +864,10 @@ __global__ void __launch_bounds__(kPrepThreads, 1)
       asm volatile("cp.async.bulk.wait_group.read 0;\n" ::: "memory");
     }
     __syncthreads();
+    if (copier && item + gridDim.x < items && *abort_flag == 0) {
+      issue_rows(item + gridDim.x, true);
+      rows_in_flight = 1;
+    }
     PREP_STAMP(5);
     // Eight columns of a row of T that are final go into the image, scaled per column; idle warps do this for the
     // diagonal blocks and the zeros above them during step 1 below, and for the blocks of step 1 during step 2.
@@ -919,11 +946,9 @@ __global__ void __launch_bounds__(kPrepThreads, 1)
     fence_proxy_async(); // the image is complete: the products below read it through the async proxy
     tcgen05_fence_before();
     __syncthreads();
-    // The staging areas of P and diag(e) K, the upper half of the [K; Q] image and A are idle from here to the end
-    // of the item: the next item's rows land there.
-    if (copier && item + gridDim.x < items && *abort_flag == 0) {
-      issue_rows(item + gridDim.x);
-      rows_in_flight = 1;
+    // A is idle from here to the end of the item: FP32 V rows, which need its room too, are asked for now.
+    if (copier && item + gridDim.x < items && rows_in_flight != 0) {
+      issue_rows(item + gridDim.x, false); // completes the pair of arrivals even after a wait ran out
     }
 
     PREP_STAMP(7);
