@@ -161,7 +161,13 @@ template <> struct Io<RIB200_DTYPE_F16> {
 
 // SiLU on the special-function unit (ex2 + rcp instead of a full-precision exponential and division): the vector
 // kernels are bound by instruction issue otherwise.  Relative error about 1e-6.
-__device__ __forceinline__ float silu_fast(float x) { return x * __frcp_rn(1.0F + __expf(-x)); }
+__device__ __forceinline__ float silu_fast(float x) {
+  float e;
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(e) : "f"(x * -1.4426950408889634F));
+  asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(r) : "f"(1.0F + e));
+  return x * r;
+}
 
 constexpr int kTokensPerWarp = 4;
 constexpr int kFastWidth = 4;
