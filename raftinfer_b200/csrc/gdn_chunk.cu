@@ -563,6 +563,8 @@ __global__ void __launch_bounds__(kPrepThreads, 1)
   volatile std::uint32_t *tmem_slot = reinterpret_cast<volatile std::uint32_t *>(smem + kPsTmemSlot);
   volatile std::uint32_t *abort_flag = reinterpret_cast<volatile std::uint32_t *>(smem + kPsAbort);
 
+  // the apply kernel behind this one may set itself up on SMs as they become free; it waits for this grid to end
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
@@ -1146,6 +1148,9 @@ __global__ void __launch_bounds__(kApplyThreads, 1)
   __syncthreads();
   tcgen05_fence_after();
   const std::uint32_t tmem = *tmem_slot;
+  // Launched with programmatic stream serialisation behind the prepare kernel: barriers, tensor memory and the state
+  // slice (which that kernel does not touch) are set up while its last CTAs finish; the records are read after this.
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
 
   // bounded wait; once the CTA has given up nobody waits any more
   auto wait = [&](std::uint32_t b, std::uint32_t parity) {
@@ -1496,9 +1501,17 @@ template <bool F32> void launch(const ChunkParams &params, cudaStream_t stream) 
   TensorMapBytes out_map;
   encode_f32_rows_map(&out_map, params.out, static_cast<std::uint64_t>(params.value_heads) * kDim, params.tokens,
                       kSlice, kChunk);
-  gdn_chunk_apply_kernel<<<dim3(kDim / kSlice, params.value_heads), kApplyThreads, kApplySmemBytes, stream>>>(
-      params, out_map);
-  cuda_ok(cudaGetLastError(), "gated-delta apply launch");
+  cudaLaunchAttribute attribute{};
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t config{};
+  config.gridDim = dim3(kDim / kSlice, params.value_heads);
+  config.blockDim = dim3(kApplyThreads, 1, 1);
+  config.dynamicSmemBytes = kApplySmemBytes;
+  config.stream = stream;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  cuda_ok(cudaLaunchKernelEx(&config, gdn_chunk_apply_kernel, params, out_map), "gated-delta apply launch");
 }
 
 } // namespace
