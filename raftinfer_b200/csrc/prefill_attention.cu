@@ -1187,6 +1187,22 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
       }
+      // FP32 gates cannot all wait in registers as the BF16 ones do: the first 32-column piece is fetched here, while
+      // the last PV is still running, the other three are pulled into L2 and fetched one piece ahead further down
+      float4 gate_now[F32 ? 8 : 1];
+      if constexpr (F32) {
+        if (live) {
+          const float4 *gsrc = reinterpret_cast<const float4 *>(static_cast<const float *>(p.gate) + out_base);
+#pragma unroll
+          for (int i = 0; i < 8; i += 2) {
+            ld_global_v8(gsrc + i, *reinterpret_cast<uint4 *>(&gate_now[i]), *reinterpret_cast<uint4 *>(&gate_now[i + 1]));
+          }
+#pragma unroll
+          for (int piece = 1; piece < 4; ++piece) {
+            asm volatile("prefetch.global.L2 [%0];\n" ::"l"(gsrc + piece * 8));
+          }
+        }
+      }
       ok = mbar_wait(bar(kBarPvDone + (g_last & 1U)), (g_last >> 1) & 1U, abort_flag);
       ok = __all_sync(0xFFFFFFFFU, ok);
       if (!ok) {
@@ -1277,17 +1293,6 @@ __global__ void __launch_bounds__(kThreads, 1)
         own_weight = exp2f(m_used - both);
         peer_weight = exp2f(peer_max - both);
         inv = 1.0F / (own_weight * (l_sum + exchange[(sums + (group ^ 1)) * kTileRows + row]) + peer_weight * peer_sum);
-      }
-      // FP32 gates cannot all wait in registers as the BF16 ones do: they are fetched one 32-column piece ahead
-      float4 gate_now[F32 ? 8 : 1];
-      if constexpr (F32) {
-        if (live) {
-          const float4 *gsrc = reinterpret_cast<const float4 *>(static_cast<const float *>(p.gate) + out_base);
-#pragma unroll
-          for (int i = 0; i < 8; i += 2) {
-            ld_global_v8(gsrc + i, *reinterpret_cast<uint4 *>(&gate_now[i]), *reinterpret_cast<uint4 *>(&gate_now[i + 1]));
-          }
-        }
       }
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
