@@ -4,6 +4,7 @@
 
 #include "../../include/rib200.h"
 
+#include <cuda_runtime.h>
 #include <cuda_runtime_api.h>
 
 #include <cstddef>
@@ -103,6 +104,31 @@ void encode_f32_rows_map(void *map_out, void *base, std::uint64_t row_floats, st
 void encode_plain_rows_map(void *map_out, const void *base, bool f32, std::uint64_t row_elements,
                            std::uint64_t row_stride_elements, std::uint64_t rows, std::uint32_t box_elements,
                            std::uint32_t box_rows);
+
+// Launch with programmatic stream serialisation: the grid may become resident while the kernel in front of it on the
+// stream is still running (once that one has executed griddepcontrol.launch_dependents in every CTA, or ended), and
+// must execute griddepcontrol.wait before it touches anything an earlier kernel of the stream writes or reads.
+#ifdef __CUDACC__
+template <typename... Params, typename... Args>
+inline void launch_programmatic(void (*kernel)(Params...), dim3 grid, dim3 block, std::size_t shared_bytes,
+                                cudaStream_t stream, const char *what, Args &&...args) {
+  cudaLaunchAttribute attribute{};
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchConfig_t config{};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = shared_bytes;
+  config.stream = stream;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  cuda_ok(cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...), what);
+}
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void grid_dependents_may_launch() {
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+}
+#endif
 
 void launch_decode_attention(const DecodeArgs &args, cudaStream_t stream);
 

@@ -563,8 +563,6 @@ __global__ void __launch_bounds__(kPrepThreads, 1)
   volatile std::uint32_t *tmem_slot = reinterpret_cast<volatile std::uint32_t *>(smem + kPsTmemSlot);
   volatile std::uint32_t *abort_flag = reinterpret_cast<volatile std::uint32_t *>(smem + kPsAbort);
 
-  // the apply kernel behind this one may set itself up on SMs as they become free; it waits for this grid to end
-  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
@@ -589,6 +587,13 @@ __global__ void __launch_bounds__(kPrepThreads, 1)
   __syncthreads();
   tcgen05_fence_after();
   const std::uint32_t tmem = *tmem_slot;
+  // Launched with programmatic stream serialisation: barriers and tensor memory are set up while the kernel in front
+  // (the layer's prologue, or whatever the caller queued) finishes; its results are read only after this.
+  grid_dependency_wait();
+  // Only now may the apply kernel behind this one set itself up on SMs as they become free (it waits for this grid to
+  // end before it reads a record): what it reads before that wait, the recurrent state, is final once the kernels in
+  // front of this one have ended.
+  grid_dependents_may_launch();
   const bool issuer = warp == 4 && elect_one();
   // One lane of the last warp issues every bulk copy to the record (bulk groups belong to the issuing thread) and
   // waits for them to have read their staging areas before those are written again.
@@ -1096,6 +1101,7 @@ __global__ void __launch_bounds__(kApplyThreads, 1)
   volatile std::uint32_t *tmem_slot = reinterpret_cast<volatile std::uint32_t *>(smem + kSmTmemSlot);
   volatile std::uint32_t *abort_flag = reinterpret_cast<volatile std::uint32_t *>(smem + kSmAbort);
 
+  grid_dependents_may_launch(); // the layer's epilogue sets itself up behind this kernel and waits for it to end
   const std::uint32_t slice = blockIdx.x;
   const std::uint32_t head = blockIdx.y;
   const int warp = threadIdx.x >> 5;
@@ -1496,22 +1502,13 @@ template <bool F32> void launch(const ChunkParams &params, cudaStream_t stream) 
                         params.tokens, kDim, kChunk);
   encode_plain_rows_map(&v_map, params.v, F32, static_cast<std::uint64_t>(params.value_heads) * kDim, params.v_stride,
                         params.tokens, kDim, kChunk);
-  gdn_chunk_prepare_kernel<F32><<<prepare_ctas, kPrepThreads, kPrepSmemBytes, stream>>>(params, k_map, q_map, v_map);
-  cuda_ok(cudaGetLastError(), "gated-delta prepare launch");
+  launch_programmatic(gdn_chunk_prepare_kernel<F32>, dim3(prepare_ctas), dim3(kPrepThreads), kPrepSmemBytes, stream,
+                      "gated-delta prepare launch", params, k_map, q_map, v_map);
   TensorMapBytes out_map;
   encode_f32_rows_map(&out_map, params.out, static_cast<std::uint64_t>(params.value_heads) * kDim, params.tokens,
                       kSlice, kChunk);
-  cudaLaunchAttribute attribute{};
-  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attribute.val.programmaticStreamSerializationAllowed = 1;
-  cudaLaunchConfig_t config{};
-  config.gridDim = dim3(kDim / kSlice, params.value_heads);
-  config.blockDim = dim3(kApplyThreads, 1, 1);
-  config.dynamicSmemBytes = kApplySmemBytes;
-  config.stream = stream;
-  config.attrs = &attribute;
-  config.numAttrs = 1;
-  cuda_ok(cudaLaunchKernelEx(&config, gdn_chunk_apply_kernel, params, out_map), "gated-delta apply launch");
+  launch_programmatic(gdn_chunk_apply_kernel, dim3(kDim / kSlice, params.value_heads), dim3(kApplyThreads),
+                      kApplySmemBytes, stream, "gated-delta apply launch", params, out_map);
 }
 
 } // namespace

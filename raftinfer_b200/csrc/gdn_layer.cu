@@ -169,16 +169,20 @@ __device__ __forceinline__ float silu_fast(float x) {
   return x * r;
 }
 
-constexpr int kTokensPerWarp = 4;
+constexpr int kTokensPerWarp = 4;  // tokens of one step of a warp
+constexpr int kStepsPerWarp = 4;   // steps a warp walks: its window of input rows slides, nothing is read twice
 constexpr int kFastWidth = 4;
 
-// grid (ceil(tokens / 4), ceil((2 Hk + Hv + 1) / 8)), 256 threads: warp w of the CTA takes head vector
-// 8 blockIdx.y + w; the vector after the last one stands for the gates (lane = value head, any head count).
-template <int Dtype> __global__ void __launch_bounds__(256, 4) gdn_prologue_w4_kernel(const LayerParams p) {
+// grid (ceil(tokens / 16), ceil((2 Hk + Hv + 1) / 8)), 256 threads: warp w of the CTA takes head vector
+// 8 blockIdx.y + w over 16 consecutive tokens, four at a time; the rows of the next four are in flight while the
+// current four are convolved, and the last three rows of a step are the history of the next.  The vector after the
+// last one stands for the gates (lane = value head, any head count).
+template <int Dtype> __global__ void __launch_bounds__(256, 3) gdn_prologue_w4_kernel(const LayerParams p) {
+  grid_dependents_may_launch(); // the kernels behind this one set themselves up early and wait for it to end
   const int lane = threadIdx.x & 31;
   const std::uint32_t vec = blockIdx.y * 8 + (threadIdx.x >> 5);
   const std::uint32_t vectors = 2 * p.key_heads + p.value_heads;
-  const std::uint32_t tok0 = blockIdx.x * kTokensPerWarp;
+  const std::uint32_t first = blockIdx.x * (kTokensPerWarp * kStepsPerWarp);
   if (vec > vectors) {
     return;
   }
@@ -186,7 +190,7 @@ template <int Dtype> __global__ void __launch_bounds__(256, 4) gdn_prologue_w4_k
     for (std::uint32_t head = lane; head < p.value_heads; head += 32) {
       const float a_coeff = load_any(p.recurrent_a, head, p.weight_dtype);
       const float dt = load_any(p.dt_bias, head, p.weight_dtype);
-      for (std::uint32_t tok = tok0; tok < min(p.tokens, tok0 + kTokensPerWarp); ++tok) {
+      for (std::uint32_t tok = first; tok < min(p.tokens, first + kTokensPerWarp * kStepsPerWarp); ++tok) {
         const std::size_t gates = static_cast<std::size_t>(tok) * p.token_stride + p.conv_dim;
         const float b = load_any(p.input, gates + head, p.dtype);
         const float a = load_any(p.input, gates + p.value_heads + head, p.dtype);
@@ -218,18 +222,19 @@ template <int Dtype> __global__ void __launch_bounds__(256, 4) gdn_prologue_w4_k
       }
     }
   }
-  // rows tok0 - 3 .. tok0 + 7 of [history | tokens]
+  auto load_row = [&](long long tok) {
+    if (tok >= 0 && tok < static_cast<long long>(p.tokens)) {
+      return Io<Dtype>::load4(p.input, static_cast<std::size_t>(tok) * p.token_stride + channel);
+    }
+    return make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+  };
+  // window: x[0..2] the three rows before the step, x[3..6] the step's own rows
   float4 x[kTokensPerWarp + kFastWidth - 1];
 #pragma unroll
   for (int r = 0; r < kTokensPerWarp + kFastWidth - 1; ++r) {
-    const long long tok = static_cast<long long>(tok0) + r - (kFastWidth - 1);
-    if (tok >= 0 && tok < static_cast<long long>(p.tokens)) {
-      x[r] = Io<Dtype>::load4(p.input, static_cast<std::size_t>(tok) * p.token_stride + channel);
-    } else {
-      x[r] = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
-    }
+    x[r] = load_row(static_cast<long long>(first) + r - (kFastWidth - 1));
   }
-  if (tok0 == 0) {
+  if (first == 0) {
     // history [channel][3]: element h is the token 3 - h steps before this call's first one
     const float *hist = p.convolution_state + static_cast<std::size_t>(channel) * (kFastWidth - 1);
 #pragma unroll
@@ -241,42 +246,67 @@ template <int Dtype> __global__ void __launch_bounds__(256, 4) gdn_prologue_w4_k
   const bool is_qk = vec < 2 * p.key_heads;
   const float q_scale = vec < p.key_heads ? rsqrtf(static_cast<float>(kDim)) : 1.0F;
 #pragma unroll
-  for (int i = 0; i < kTokensPerWarp; ++i) {
-    const std::uint32_t tok = tok0 + i;
-    float4 sum = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
-    // the reference adds the current token's tap first, then the history taps oldest first
-    sum.x = x[i + 3].x * w[0][3];
-    sum.y = x[i + 3].y * w[1][3];
-    sum.z = x[i + 3].z * w[2][3];
-    sum.w = x[i + 3].w * w[3][3];
-#pragma unroll
-    for (int h = 0; h < kFastWidth - 1; ++h) {
-      sum.x += x[i + h].x * w[0][h];
-      sum.y += x[i + h].y * w[1][h];
-      sum.z += x[i + h].z * w[2][h];
-      sum.w += x[i + h].w * w[3][h];
+  for (int step = 0; step < kStepsPerWarp; ++step) {
+    const std::uint32_t tok0 = first + step * kTokensPerWarp;
+    if (tok0 >= p.tokens) {
+      break;
     }
-    float4 value = make_float4(silu_fast(sum.x), silu_fast(sum.y), silu_fast(sum.z), silu_fast(sum.w));
-    if (is_qk) {
-      float squares = (value.x * value.x + value.y * value.y) + (value.z * value.z + value.w * value.w);
+    float4 next[kTokensPerWarp];
+    if (step + 1 < kStepsPerWarp) {
 #pragma unroll
-      for (int offset = 16; offset > 0; offset >>= 1) {
-        squares += __shfl_xor_sync(0xFFFFFFFFU, squares, offset);
+      for (int r = 0; r < kTokensPerWarp; ++r) {
+        next[r] = load_row(static_cast<long long>(tok0) + kTokensPerWarp + r);
       }
-      const float scale = rsqrtf(squares + kQkEpsilon) * q_scale;
-      value.x *= scale;
-      value.y *= scale;
-      value.z *= scale;
-      value.w *= scale;
     }
-    if (tok < p.tokens) {
-      *reinterpret_cast<float4 *>(p.convolved + static_cast<std::size_t>(tok) * p.conv_dim + channel) = value;
+#pragma unroll
+    for (int i = 0; i < kTokensPerWarp; ++i) {
+      const std::uint32_t tok = tok0 + i;
+      float4 sum = make_float4(0.0F, 0.0F, 0.0F, 0.0F);
+      // the reference adds the current token's tap first, then the history taps oldest first
+      sum.x = x[i + 3].x * w[0][3];
+      sum.y = x[i + 3].y * w[1][3];
+      sum.z = x[i + 3].z * w[2][3];
+      sum.w = x[i + 3].w * w[3][3];
+#pragma unroll
+      for (int h = 0; h < kFastWidth - 1; ++h) {
+        sum.x += x[i + h].x * w[0][h];
+        sum.y += x[i + h].y * w[1][h];
+        sum.z += x[i + h].z * w[2][h];
+        sum.w += x[i + h].w * w[3][h];
+      }
+      float4 value = make_float4(silu_fast(sum.x), silu_fast(sum.y), silu_fast(sum.z), silu_fast(sum.w));
+      if (is_qk) {
+        float squares = (value.x * value.x + value.y * value.y) + (value.z * value.z + value.w * value.w);
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) {
+          squares += __shfl_xor_sync(0xFFFFFFFFU, squares, offset);
+        }
+        const float scale = rsqrtf(squares + kQkEpsilon) * q_scale;
+        value.x *= scale;
+        value.y *= scale;
+        value.z *= scale;
+        value.w *= scale;
+      }
+      if (tok < p.tokens) {
+        *reinterpret_cast<float4 *>(p.convolved + static_cast<std::size_t>(tok) * p.conv_dim + channel) = value;
+      }
+    }
+    if (step + 1 < kStepsPerWarp) {
+#pragma unroll
+      for (int h = 0; h < kFastWidth - 1; ++h) {
+        x[h] = x[kTokensPerWarp + h];
+      }
+#pragma unroll
+      for (int r = 0; r < kTokensPerWarp; ++r) {
+        x[kFastWidth - 1 + r] = next[r];
+      }
     }
   }
 }
 
 // grid (ceil(tokens * value_heads / 8)), 256 threads: a warp per (token, value head), four channels per lane
 template <int Dtype> __global__ void __launch_bounds__(256) gdn_epilogue_warp_kernel(const LayerParams p) {
+  grid_dependency_wait(); // launched with programmatic serialisation behind the recurrence, whose output it reads
   const int lane = threadIdx.x & 31;
   const std::size_t item = static_cast<std::size_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
   if (item >= static_cast<std::size_t>(p.tokens) * p.value_heads) {
@@ -316,6 +346,7 @@ bool vector_forms_apply(const LayerParams &p) {
 
 // one thread per channel: new history[h] = element tokens + h of [old history | token stream]
 __global__ void gdn_conv_state_kernel(const LayerParams p) {
+  grid_dependents_may_launch();
   const std::uint32_t channel = blockIdx.x * blockDim.x + threadIdx.x;
   const std::uint32_t history = p.conv_width - 1;
   if (channel >= p.conv_dim || history == 0) {
@@ -328,6 +359,8 @@ __global__ void gdn_conv_state_kernel(const LayerParams p) {
                   ? p.convolution_state[static_cast<std::size_t>(channel) * history + source]
                   : load_any(p.input, (source - history) * p.token_stride + channel, p.dtype);
   }
+  // launched with programmatic serialisation behind the prologue, which reads the old history: write after it ended
+  grid_dependency_wait();
   for (std::uint32_t h = 0; h < history; ++h) {
     p.convolution_state[static_cast<std::size_t>(channel) * history + h] = next[h];
   }
@@ -335,6 +368,7 @@ __global__ void gdn_conv_state_kernel(const LayerParams p) {
 
 // grid (value_heads, tokens), 128 threads
 __global__ void __launch_bounds__(kDim) gdn_epilogue_kernel(const LayerParams p) {
+  grid_dependency_wait();
   __shared__ float scratch[4];
   const std::uint32_t head = blockIdx.x;
   const std::uint32_t tok = blockIdx.y;
@@ -382,7 +416,8 @@ void launch_gdn_prologue(const GdnLayerArgs &a, cudaStream_t stream) {
   const LayerParams p = make_params(a);
   // a call of a few tokens is latency, not bandwidth: the one-CTA-per-vector kernel spreads it wider
   if (a.conv_width == kFastWidth && a.tokens >= 2 * kTokensPerWarp && vector_forms_apply(p)) {
-    const dim3 grid((a.tokens + kTokensPerWarp - 1) / kTokensPerWarp, (2 * a.key_heads + a.value_heads + 1 + 7) / 8);
+    constexpr std::uint32_t kTokensPerCta = kTokensPerWarp * kStepsPerWarp;
+    const dim3 grid((a.tokens + kTokensPerCta - 1) / kTokensPerCta, (2 * a.key_heads + a.value_heads + 1 + 7) / 8);
     if (a.dtype == RIB200_DTYPE_F32) {
       gdn_prologue_w4_kernel<RIB200_DTYPE_F32><<<grid, 256, 0, stream>>>(p);
     } else if (a.dtype == RIB200_DTYPE_F16) {
@@ -395,8 +430,8 @@ void launch_gdn_prologue(const GdnLayerArgs &a, cudaStream_t stream) {
   }
   cuda_ok(cudaGetLastError(), "gated-delta prologue launch");
   if (a.conv_width > 1) {
-    gdn_conv_state_kernel<<<(p.conv_dim + 255) / 256, 256, 0, stream>>>(p);
-    cuda_ok(cudaGetLastError(), "gated-delta convolution-state launch");
+    launch_programmatic(gdn_conv_state_kernel, dim3((p.conv_dim + 255) / 256), dim3(256), 0, stream,
+                        "gated-delta convolution-state launch", p);
   }
 }
 
@@ -405,18 +440,18 @@ void launch_gdn_epilogue(const GdnLayerArgs &a, cudaStream_t stream) {
   if (vector_forms_apply(p)) {
     const std::size_t items = static_cast<std::size_t>(a.tokens) * a.value_heads;
     const unsigned int grid = static_cast<unsigned int>((items + 7) / 8);
+    const char *what = "gated-delta epilogue launch";
     if (a.dtype == RIB200_DTYPE_F32) {
-      gdn_epilogue_warp_kernel<RIB200_DTYPE_F32><<<grid, 256, 0, stream>>>(p);
+      launch_programmatic(gdn_epilogue_warp_kernel<RIB200_DTYPE_F32>, dim3(grid), dim3(256), 0, stream, what, p);
     } else if (a.dtype == RIB200_DTYPE_F16) {
-      gdn_epilogue_warp_kernel<RIB200_DTYPE_F16><<<grid, 256, 0, stream>>>(p);
+      launch_programmatic(gdn_epilogue_warp_kernel<RIB200_DTYPE_F16>, dim3(grid), dim3(256), 0, stream, what, p);
     } else {
-      gdn_epilogue_warp_kernel<RIB200_DTYPE_BF16><<<grid, 256, 0, stream>>>(p);
+      launch_programmatic(gdn_epilogue_warp_kernel<RIB200_DTYPE_BF16>, dim3(grid), dim3(256), 0, stream, what, p);
     }
-    cuda_ok(cudaGetLastError(), "gated-delta epilogue launch");
     return;
   }
-  gdn_epilogue_kernel<<<dim3(a.value_heads, a.tokens), kDim, 0, stream>>>(p);
-  cuda_ok(cudaGetLastError(), "gated-delta epilogue launch");
+  launch_programmatic(gdn_epilogue_kernel, dim3(a.value_heads, a.tokens), dim3(kDim), 0, stream,
+                      "gated-delta epilogue launch", p);
 }
 
 } // namespace rib200
