@@ -616,26 +616,31 @@ __global__ void __launch_bounds__(kThreads, 1)
     *abort_flag = (base & 1023U) != 0 ? 1U : 0U; // a misaligned window would scramble every tile: give up cleanly
     asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
   }
-  if (warp == kMmaWarp) {
-    // the whole tensor memory of the SM: O (256 columns) + two score tiles (128 each)
-    if constexpr (Pair) {
-      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], 512;\n" ::"r"(
-                       smem_u32(const_cast<std::uint32_t *>(tmem_slot)))
-                   : "memory");
-      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
-    } else {
-      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;\n" ::"r"(
-                       smem_u32(const_cast<std::uint32_t *>(tmem_slot)))
-                   : "memory");
-      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
-    }
-  }
-  tcgen05_fence_before();
   __syncthreads();
   if constexpr (kCluster) {
     cluster_sync_all(); // the partner's barriers exist before anything arrives on them
   }
-  tcgen05_fence_after();
+  // From here the producer warp starts its first loads; the other warps take the SM's tensor memory meanwhile
+  // (the allocation takes about as long as those loads) and meet on a barrier of their own before they use it.
+  if (warp != kProducerWarp) {
+    if (warp == kMmaWarp) {
+      // the whole tensor memory of the SM: O (256 columns) + two score tiles (128 each)
+      if constexpr (Pair) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], 512;\n" ::"r"(
+                         smem_u32(const_cast<std::uint32_t *>(tmem_slot)))
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+      } else {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;\n" ::"r"(
+                         smem_u32(const_cast<std::uint32_t *>(tmem_slot)))
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+      }
+    }
+    tcgen05_fence_before();
+    asm volatile("bar.sync 3, %0;\n" ::"n"(kThreads - 32) : "memory");
+    tcgen05_fence_after();
+  }
   if constexpr (Split) {
     if (half == 0 && threadIdx.x == 0) {
       mbar_expect_tx(bar(kBarPeerFull), kLandingBytes); // the partner's partial tile, one bulk copy
