@@ -467,80 +467,67 @@ __device__ __forceinline__ void split_tf32(float x, std::uint32_t &hi, std::uint
   hi = tf32(x);
   lo = tf32(x - __uint_as_float(hi));
 }
-// acc (a 16 x 16 block as two 16 x 8 accumulator tiles) += L[r0 .. r0+15][k0 .. k0+8 KSTEPS) R[k0 ..][c0 .. c0+15],
-// L and R row-major FP32 matrices of pitch kPitchSq in shared memory; one warp.  The three partial products run in
-// accumulators of their own, so that consecutive tensor instructions do not wait for each other.
+// acc (a 16 x 8 accumulator tile) += L[r0 .. r0+15][k0 .. k0+8 KSTEPS) R[k0 ..][c0 .. c0+7], L and R row-major FP32
+// matrices of pitch kPitchSq in shared memory; one warp.  The three partial products run in accumulators of their
+// own, so that consecutive tensor instructions do not wait for each other.
 template <int KSTEPS>
-__device__ __forceinline__ void block_product(float (&acc)[2][4], const float *L, int r0, const float *R, int c0,
-                                              int k0) {
+__device__ __forceinline__ void tile_product(float (&acc)[4], const float *L, int r0, const float *R, int c0, int k0) {
   const int g = (threadIdx.x & 31) >> 2;
   const int t = threadIdx.x & 3;
-  float lo_hi[2][4] = {};
-  float hi_lo[2][4] = {};
+  float lo_hi[4] = {};
+  float hi_lo[4] = {};
 #pragma unroll
   for (int ks = 0; ks < KSTEPS; ++ks) {
     const int k = k0 + 8 * ks;
     const float *l = L + (r0 + g) * kPitchSq + k + t;
+    const float *r = R + (k + t) * kPitchSq + c0 + g;
     std::uint32_t a_hi[4];
     std::uint32_t a_lo[4];
+    std::uint32_t b_hi[2];
+    std::uint32_t b_lo[2];
     split_tf32(l[0], a_hi[0], a_lo[0]);
     split_tf32(l[8 * kPitchSq], a_hi[1], a_lo[1]);
     split_tf32(l[4], a_hi[2], a_lo[2]);
     split_tf32(l[8 * kPitchSq + 4], a_hi[3], a_lo[3]);
-#pragma unroll
-    for (int n = 0; n < 2; ++n) {
-      const float *r = R + (k + t) * kPitchSq + c0 + 8 * n + g;
-      std::uint32_t b_hi[2];
-      std::uint32_t b_lo[2];
-      split_tf32(r[0], b_hi[0], b_lo[0]);
-      split_tf32(r[4 * kPitchSq], b_hi[1], b_lo[1]);
-      mma_tf32(lo_hi[n], a_lo, b_hi[0], b_hi[1]);
-      mma_tf32(hi_lo[n], a_hi, b_lo[0], b_lo[1]);
-      mma_tf32(acc[n], a_hi, b_hi[0], b_hi[1]);
-    }
+    split_tf32(r[0], b_hi[0], b_lo[0]);
+    split_tf32(r[4 * kPitchSq], b_hi[1], b_lo[1]);
+    mma_tf32(lo_hi, a_lo, b_hi[0], b_hi[1]);
+    mma_tf32(hi_lo, a_hi, b_lo[0], b_lo[1]);
+    mma_tf32(acc, a_hi, b_hi[0], b_hi[1]);
   }
 #pragma unroll
-  for (int n = 0; n < 2; ++n) {
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      acc[n][e] += lo_hi[n][e] + hi_lo[n][e];
-    }
+  for (int e = 0; e < 4; ++e) {
+    acc[e] += lo_hi[e] + hi_lo[e];
   }
 }
-// the block, times -1, goes into the [T diag(beta gamma); T diag(beta)] image at `tstack` (rows r0 .., columns c0 ..)
-__device__ __forceinline__ void store_block_scaled(std::uint32_t tstack, int r0, int c0, const float (&acc)[2][4],
-                                                   const float *bg, const float *be) {
+// the tile, times -1, goes into the [T diag(beta gamma); T diag(beta)] image at `tstack` (rows r0 .., columns c0 ..)
+__device__ __forceinline__ void store_tile_scaled(std::uint32_t tstack, int r0, int c0, const float (&acc)[4],
+                                                  const float *bg, const float *be) {
   const int g = (threadIdx.x & 31) >> 2;
   const int t = threadIdx.x & 3;
+  const int col = c0 + 2 * t;
+  const float2 sg = *reinterpret_cast<const float2 *>(bg + col);
+  const float2 se = *reinterpret_cast<const float2 *>(be + col);
 #pragma unroll
-  for (int n = 0; n < 2; ++n) {
-    const int col = c0 + 8 * n + 2 * t;
-    const float2 sg = *reinterpret_cast<const float2 *>(bg + col);
-    const float2 se = *reinterpret_cast<const float2 *>(be + col);
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const std::uint32_t row = static_cast<std::uint32_t>(r0 + g + 8 * h);
-      const float x = -acc[n][2 * h];
-      const float y = -acc[n][2 * h + 1];
-      asm volatile("st.shared.v2.b32 [%0], {%1, %2};\n" ::"r"(tstack + image_offset(row, col, kA1Block)),
-                   "r"(tf32(x * sg.x)), "r"(tf32(y * sg.y))
-                   : "memory");
-      asm volatile("st.shared.v2.b32 [%0], {%1, %2};\n" ::"r"(tstack + image_offset(kChunk + row, col, kA1Block)),
-                   "r"(tf32(x * se.x)), "r"(tf32(y * se.y))
-                   : "memory");
-    }
+  for (int h = 0; h < 2; ++h) {
+    const std::uint32_t row = static_cast<std::uint32_t>(r0 + g + 8 * h);
+    const float x = -acc[2 * h];
+    const float y = -acc[2 * h + 1];
+    asm volatile("st.shared.v2.b32 [%0], {%1, %2};\n" ::"r"(tstack + image_offset(row, col, kA1Block)),
+                 "r"(tf32(x * sg.x)), "r"(tf32(y * sg.y))
+                 : "memory");
+    asm volatile("st.shared.v2.b32 [%0], {%1, %2};\n" ::"r"(tstack + image_offset(kChunk + row, col, kA1Block)),
+                 "r"(tf32(x * se.x)), "r"(tf32(y * se.y))
+                 : "memory");
   }
 }
-// the block goes to M[r0 ..][c0 ..] times `sign`
-__device__ __forceinline__ void store_block(float *M, int r0, int c0, const float (&acc)[2][4], float sign) {
+// the tile goes to M[r0 ..][c0 ..] times `sign`
+__device__ __forceinline__ void store_tile(float *M, int r0, int c0, const float (&acc)[4], float sign) {
   const int g = (threadIdx.x & 31) >> 2;
   const int t = threadIdx.x & 3;
-#pragma unroll
-  for (int n = 0; n < 2; ++n) {
-    float *at = M + (r0 + g) * kPitchSq + c0 + 8 * n + 2 * t;
-    *reinterpret_cast<float2 *>(at) = make_float2(sign * acc[n][0], sign * acc[n][1]);
-    *reinterpret_cast<float2 *>(at + 8 * kPitchSq) = make_float2(sign * acc[n][2], sign * acc[n][3]);
-  }
+  float *at = M + (r0 + g) * kPitchSq + c0 + 2 * t;
+  *reinterpret_cast<float2 *>(at) = make_float2(sign * acc[0], sign * acc[1]);
+  *reinterpret_cast<float2 *>(at + 8 * kPitchSq) = make_float2(sign * acc[2], sign * acc[3]);
 }
 
 template <bool F32>
@@ -891,8 +878,8 @@ __global__ void __launch_bounds__(kPrepThreads, 1)
                tf32f(t4.y * be.y), tf32f(t4.z * be.z), tf32f(t4.w * be.w));
       }
     };
-    if (tid >= 64 && tid < 64 + 320) { // units on or above the block diagonal: 128 + 96 + 64 + 32
-      const std::uint32_t idx = tid - 64;
+    if (tid >= 128 && tid < 128 + 320) { // units on or above the block diagonal: 128 + 96 + 64 + 32
+      const std::uint32_t idx = tid - 128;
       if (idx < 128) {
         image_unit(idx >> 3, idx & 7U);
       } else if (idx < 224) {
@@ -905,50 +892,53 @@ __global__ void __launch_bounds__(kPrepThreads, 1)
     }
     // ... then the blocks below the diagonal by doubling: for M = [[M11, 0], [M21, M22]] the lower left block of the
     // inverse is -M22^-1 M21 M11^-1.
-    //   step 1 (warps 0, 1):  T_10 = -T_11 (A_10 T_00),  T_32 = -T_33 (A_32 T_22)            16 x 16 blocks
-    //   step 2 (warps 0..3):  T[32..63][0..31] = -T[32..63][32..63] (A[32..63][0..31] T[0..31][0..31])
-    // on warp-level tensor tiles with split operands (FP32 accuracy).  An intermediate product sits in the place of
-    // the block of T that it becomes; triangular factors are only walked over their non-zero blocks.
-    if (warp < 2) {
-      const int b = 2 * warp;
+    //   step 1 (warps 0..3):  T_10 = -T_11 (A_10 T_00),  T_32 = -T_33 (A_32 T_22)            16 x 16 blocks
+    //   step 2 (warps 0..7):  T[32..63][0..31] = -T[32..63][32..63] (A[32..63][0..31] T[0..31][0..31])
+    // on warp-level tensor tiles with split operands (FP32 accuracy), a warp per 16 x 8 tile of the result (a column
+    // tile of the second product only needs the same column tile of the first).  An intermediate product sits in the
+    // place of the block of T that it becomes; triangular factors are only walked over their non-zero blocks.
+    if (warp < 4) {
+      const int b = 2 * (warp >> 1);
       const int i = b + 1;
-      float y[2][4] = {};
-      block_product<2>(y, sA, 16 * i, sT, 16 * b, 16 * b);
-      store_block(sT, 16 * i, 16 * b, y, 1.0F);
+      const int c0 = 16 * b + 8 * (warp & 1);
+      float y[4] = {};
+      tile_product<2>(y, sA, 16 * i, sT, c0, 16 * b);
+      store_tile(sT, 16 * i, c0, y, 1.0F);
       __syncwarp();
-      float z[2][4] = {};
-      block_product<2>(z, sT, 16 * i, sT, 16 * b, 16 * i);
+      float z[4] = {};
+      tile_product<2>(z, sT, 16 * i, sT, c0, 16 * i);
       __syncwarp();
-      store_block(sT, 16 * i, 16 * b, z, -1.0F);
+      store_tile(sT, 16 * i, c0, z, -1.0F);
     }
     __syncthreads();
     PREP_STAMP(6);
     if ((warp == 8 || warp == 9) && item + gridDim.x < items) {
-      load_gates(item + gridDim.x); // while four warps work below; consumed at the top of the next item
+      load_gates(item + gridDim.x); // while eight warps work below; consumed at the top of the next item
     }
-    if (warp == 4 || warp == 5) { // the two blocks of step 1: rows 16..31 x columns 0..15, rows 48..63 x columns 32..47
-      const std::uint32_t idx = tid - 128;
+    if (warp == 10 || warp == 11) { // the two blocks of step 1: rows 16..31 x columns 0..15, rows 48..63 x columns 32..47
+      const std::uint32_t idx = tid - 320;
       const std::uint32_t half = idx >> 5;
       image_unit(16 + 32 * half + ((idx & 31U) >> 1), 4 * half + (idx & 1U));
     }
-    if (warp < 4) {
-      const int bi = 2 + (warp >> 1);
-      const int bj = warp & 1;
-      float y[2][4] = {};
+    if (warp < 8) {
+      const int bi = 2 + (warp >> 2);
+      const int bj = (warp >> 1) & 1;
+      const int c0 = 16 * bj + 8 * (warp & 1);
+      float y[4] = {};
       if (bj == 0) { // T[0..31][0..31] is lower triangular: its second column block starts at row 16
-        block_product<4>(y, sA, 16 * bi, sT, 0, 0);
+        tile_product<4>(y, sA, 16 * bi, sT, c0, 0);
       } else {
-        block_product<2>(y, sA, 16 * bi, sT, 16, 16);
+        tile_product<2>(y, sA, 16 * bi, sT, c0, 16);
       }
-      store_block(sT, 16 * bi, 16 * bj, y, 1.0F);
-      asm volatile("bar.sync 2, 128;\n" ::: "memory"); // block (3, bj) reads the product of row block 2 as well
-      float z[2][4] = {};
+      store_tile(sT, 16 * bi, c0, y, 1.0F);
+      asm volatile("bar.sync 2, 256;\n" ::: "memory"); // row block 3 reads the product of row block 2 as well
+      float z[4] = {};
       if (bi == 2) { // row block 2 of T[32..63][32..63] ends at column 47
-        block_product<2>(z, sT, 32, sT, 16 * bj, 32);
+        tile_product<2>(z, sT, 32, sT, c0, 32);
       } else {
-        block_product<4>(z, sT, 48, sT, 16 * bj, 32);
+        tile_product<4>(z, sT, 48, sT, c0, 32);
       }
-      store_block_scaled(base + kPsTstack, 16 * bi, 16 * bj, z, sBg, sBeta); // nobody reads these blocks of T again
+      store_tile_scaled(base + kPsTstack, 16 * bi, c0, z, sBg, sBeta); // nobody reads these blocks of T again
     }
     fence_proxy_async(); // the image is complete: the products below read it through the async proxy
     tcgen05_fence_before();
