@@ -31,9 +31,10 @@
 //            store the tile at the end.
 // Pair form (GQA group even): the two CTAs of a cluster take two query heads of one KV head at the same tile and
 // run as one tcgen05 cta_group::2 unit (M = 256); each CTA loads half of every K block and half of every V block.
-// Split form (few items, many key blocks each: a 512-token chunk against a long past): a second CTA (or pair)
-// of the cluster takes the second half of an item's key blocks and hands its partial tile over through
-// distributed shared memory at the end.
+// Split form (few items, many key blocks each: a 512-token chunk against a long past, or the long tiles of a few
+// heads of a long prompt): a second CTA (or pair) of the cluster takes the second half of an item's key blocks and
+// hands its partial tile over through distributed shared memory at the end; items too short to be worth the
+// hand-over are walked by the first CTA (or pair) alone.
 //
 // Work per launch: 4 * heads * 256 * (T * P + T (T + 1) / 2) flops for T new tokens after P past tokens.
 // Every wait on an mbarrier is bounded; when one runs out the CTA records RIB200_DEVICE_WAIT_TIMED_OUT, nothing
@@ -78,6 +79,11 @@ constexpr int kThreads = 320;
 constexpr long long kWaitLimitCycles = 1LL << 30;
 constexpr float kScaleLog2e = 0.0625F * 1.4426950408889634F; // (1 / sqrt(256)) * log2(e)
 constexpr float kRescaleThreshold = 8.0F;
+// Split form: an item shares its key blocks between two CTAs (or pairs) when it has at least this many.  The
+// hand-over of the partial tile costs about as much as five blocks, so where only part of a launch's items are long
+// (a rank's slice of the heads of a long prompt, tiles of 1 .. 32 blocks) the bar is higher.
+constexpr std::uint32_t kSplitMinBlocks = 4;
+constexpr std::uint32_t kSplitMinBlocksLate = 20;
 
 // barrier indices (8 bytes each) inside the barrier block
 enum : int {
@@ -148,6 +154,7 @@ struct PrefillParams {
   std::uint32_t tiles;
   std::uint32_t query_heads;
   std::uint32_t group; // query heads per KV head
+  std::uint32_t split_min_blocks; // split form: items with fewer key blocks are left to the first CTA (or pair) alone
   unsigned int *status;
 };
 
@@ -664,10 +671,21 @@ __global__ void __launch_bounds__(kThreads, 1)
   };
   // the key blocks this CTA walks: all of them, or its half in the split form (the hand-over can only start when
   // both halves are done, so equal halves are best)
-  auto first_block = [&](std::uint32_t tile) { return Split && half == 1 ? (tile_blocks(tile) + 1) / 2 : 0U; };
+  // A short item is not worth the hand-over: the first CTA (or pair) of the cluster then walks all of its blocks and
+  // the second one sits the item out (it has no other: the split form launches one cluster per item).
+  auto split_item = [&](std::uint32_t tile) { return Split && tile_blocks(tile) >= p.split_min_blocks; };
+  auto first_block = [&](std::uint32_t tile) {
+    return split_item(tile) && half == 1 ? (tile_blocks(tile) + 1) / 2 : 0U;
+  };
   auto my_blocks = [&](std::uint32_t tile) {
     const std::uint32_t all = tile_blocks(tile);
-    return Split ? (half == 0 ? (all + 1) / 2 : all - (all + 1) / 2) : all;
+    if (!Split) {
+      return all;
+    }
+    if (!split_item(tile)) {
+      return half == 0 ? all : 0U;
+    }
+    return half == 0 ? (all + 1) / 2 : all - (all + 1) / 2;
   };
 
   if (warp == kProducerWarp) {
@@ -735,6 +753,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         const std::uint32_t all_blocks = tile_blocks(walk.tile());
         const std::uint32_t block0 = first_block(walk.tile()); // this CTA walks blocks block0 .. block0 + blocks - 1
         const std::uint32_t blocks = my_blocks(walk.tile());
+        if (Split && blocks == 0) {
+          continue; // the item is left to the first half of the cluster
+        }
         if (walk.iteration > 0) {
           // the previous tile's last score product has finished reading Q
           ok = mbar_wait(bar(kBarQFree), (walk.iteration - 1) & 1U, abort_flag);
@@ -919,6 +940,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       std::uint32_t g0 = 0; // running key-block number of the tile's first block (S buffer = block & 1)
       for (TileWalk walk(p.tiles, Pair ? p.query_heads / 2 : p.query_heads, units, unit); !walk.done(); walk.next()) {
         const std::uint32_t blocks = my_blocks(walk.tile());
+        if (Split && blocks == 0) {
+          continue;
+        }
         wait(kBarQFull, walk.iteration & 1U);
         // S[g & 1] = Q K_block^T.  Pair form: one slot, each CTA holding 64 of the block's 128 keys with all 256
         // dims in four 64-dim boxes.  Single form: two slots, each holding all 128 keys for half of the dims.
@@ -1047,6 +1071,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       const std::uint32_t rows = tile_rows(walk.tile());
       const std::uint32_t blocks = my_blocks(walk.tile());
       const std::uint32_t block0 = first_block(walk.tile());
+      const bool split_here = split_item(walk.tile());
+      if (Split && blocks == 0) {
+        continue;
+      }
       const std::uint32_t q_pos = p.past + row0 + row; // position of this row's query (rows past the tile are idle)
 
       float m_used = -INFINITY; // maximum the exponentials are taken against (scaled, base 2); same in both groups
@@ -1267,7 +1295,9 @@ __global__ void __launch_bounds__(kThreads, 1)
           continue;
         }
         // first half: every MMA of this CTA has completed, its ring is free for the partner's partial tile
-        mbar_arrive_cluster_release(map_to_rank(bar(kBarPeerFree), cta + half_stride));
+        if (split_here) {
+          mbar_arrive_cluster_release(map_to_rank(bar(kBarPeerFree), cta + half_stride));
+        }
       }
       // The row sum is the two groups' shares.  They pass through the half of the exchange area that the next
       // block to run (the first of the next tile) does not use; the first barrier makes sure the partner has
@@ -1280,7 +1310,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       float own_weight = 1.0F;  // split form: factors that bring the two halves to a common maximum
       float peer_weight = 0.0F;
       const unsigned char *landed = smem + kRingOffset;
-      if constexpr (Split) {
+      if (Split && split_here) {
         ok = mbar_wait(bar(kBarPeerFull), walk.iteration & 1U, abort_flag);
         ok = __all_sync(0xFFFFFFFFU, ok);
         if (!ok) {
@@ -1316,7 +1346,7 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
         tmem_wait_ld();
-        if constexpr (Split) {
+        if (Split && split_here) {
           const float4 *peer = reinterpret_cast<const float4 *>(landed + row * kLandingPitch + (group * 128 + c * 32) * 4);
 #pragma unroll
           for (int e = 0; e < 32; e += 4) {
@@ -1590,6 +1620,12 @@ template <bool F32, bool Pair, bool Split> void launch(const PrefillArgs &a, cud
   params.tiles = (a.tokens + kTileRows - 1) / kTileRows;
   params.query_heads = a.query_heads;
   params.group = a.query_heads / a.kv_heads;
+  {
+    // every item when already the first tile is long enough to be worth a hand-over, else only the long ones
+    const std::uint32_t first_tile_blocks =
+        (a.past_tokens + std::min<std::uint32_t>(a.tokens, kTileRows) - 1) / kBlockKeys + 1;
+    params.split_min_blocks = first_tile_blocks >= kSplitMinBlocks ? kSplitMinBlocks : kSplitMinBlocksLate;
+  }
   params.status = device_status_word();
 
   cudaLaunchConfig_t config{};
@@ -1677,8 +1713,11 @@ void launch_prefill_attention(const PrefillArgs &args, cudaStream_t stream) {
   const std::uint32_t tiles = (args.tokens + kTileRows - 1) / kTileRows;
   const std::uint32_t first_tile_blocks =
       (args.past_tokens + std::min<std::uint32_t>(args.tokens, kTileRows) - 1) / kBlockKeys + 1;
+  // ... or few items of which only the late ones are long (a rank's slice of the heads of a long prompt): those are
+  // split, the short ones are left to one CTA (or pair) of their cluster.
+  const std::uint32_t last_tile_blocks = (args.past_tokens + args.tokens - 1) / kBlockKeys + 1;
   const bool split = split_form_enabled() && 2 * tiles * args.query_heads <= static_cast<std::uint32_t>(sm_count) &&
-                     first_tile_blocks >= 4;
+                     (first_tile_blocks >= kSplitMinBlocks || last_tile_blocks >= kSplitMinBlocksLate);
   const bool pair = pair_form_enabled() && (args.query_heads / args.kv_heads) % 2 == 0;
   auto dispatch = [&](auto f32) {
     constexpr bool kF32 = decltype(f32)::value;

@@ -164,3 +164,33 @@ def test_other_head_counts(hq, hkv):
     got_cache = cache_bits_of(cache).reshape(cache_bits.shape)
     assert np.array_equal(got_cache[0, :, past:past + tokens], synth.bf16_bits(k[past:]).transpose(1, 0, 2))
     assert np.array_equal(got_cache[:, :, past + tokens:], cache_bits[:, :, past + tokens:])
+
+
+@pytest.mark.parametrize("hq,hkv,dtype", [(2, 1, K.DTYPE_BF16), (3, 3, K.DTYPE_BF16), (2, 1, K.DTYPE_F32)])
+def test_a_ranks_slice_of_a_long_prompt_splits_only_its_long_tiles(hq, hkv, dtype):
+    """Two or three heads of a 2688-token prompt (what a rank of eight computes): 21 tiles of 1 .. 21 key blocks, few
+    enough items for the split form.  Only the tiles of 20 blocks and more share their keys between two CTAs (or pairs);
+    the shorter ones are walked by the first CTA of their cluster alone while the second sits them out.  Rows of both
+    kinds, and the appended cache rows, against the oracle."""
+    tokens, seed = 2688, 0xB2004900 + hq
+    q = synth.round_bf16(synth.normal(seed, 0, (tokens, hq, D)))
+    gate = synth.round_bf16(synth.normal(seed, 1, (tokens, hq, D)))
+    k = synth.round_bf16(synth.normal(seed, 2, (tokens, hkv, D)))
+    v = synth.round_bf16(synth.normal(seed, 3, (tokens, hkv, D)))
+    cache = cache_to_device(np.full((2, hkv, tokens, D), 0x7FC1, dtype=np.uint16))
+    out = torch.zeros(tokens, hq, D, device=dev(), dtype=torch.float32 if dtype == K.DTYPE_F32 else torch.bfloat16)
+    shape = K.Qwen35AttentionShape(tokens, hq, hkv, D, tokens, 0)
+    stream = torch.cuda.current_stream()
+    K.qwen35_online_attention_prefill(act_tensor(q, dtype), act_tensor(k, dtype), act_tensor(v, dtype),
+                                      act_tensor(gate, dtype), out, cache, cache.numel() * 2, shape, dtype, K.KV_BF16,
+                                      K.HEAD_MAJOR, stream)
+    torch.cuda.synchronize()
+    assert K.device_status(stream) == 0
+    got = to_numpy_f32(out)
+    # the first tile, the last unsplit tile and the first split one (rows 2304 .. 2559), the end of the prompt
+    for lo, hi in ((0, 64), (2304, 2560), (tokens - 64, tokens)):
+        want = ob.attention_core(q[lo:hi], k[:hi], v[:hi], gate[lo:hi], past=lo)
+        gate_bf16_outputs(compare(got[lo:hi], want))
+    got_cache = cache_bits_of(cache).reshape(2, hkv, tokens, D)
+    assert np.array_equal(got_cache[0], synth.bf16_bits(k).transpose(1, 0, 2))
+    assert np.array_equal(got_cache[1], synth.bf16_bits(v).transpose(1, 0, 2))
