@@ -126,6 +126,16 @@ def test_chunked_prefill_4096_then_128_decode_steps():
     assert m_state["nonfinite"] == 0 and m_state["rel_l2"] <= 1.0e-3, m_state
 
 
+@pytest.mark.parametrize("hk,hv", [(2, 2), (1, 3), (3, 6)])
+@pytest.mark.parametrize("dtype", [K.DTYPE_BF16, K.DTYPE_F32])
+def test_chunked_core_other_head_counts(hk, hv, dtype):
+    """Key heads equal to value heads, one key head for three value heads, odd counts: fewer (chunk, head) items than
+    SMs, a ragged last chunk (200 tokens), the key head of a value head is head % key_heads."""
+    m_out, m_state = run_core(200, dtype, seed=0xB2001900 + 16 * hk + hv, hk=hk, hv=hv)
+    assert m_out["nonfinite"] == 0 and m_out["max_abs"] <= 3.0e-2 and m_out["rel_l2"] <= 2.0e-3, m_out
+    assert m_state["nonfinite"] == 0 and m_state["rel_l2"] <= 1.0e-3, m_state
+
+
 def test_recurrent_core_small_head_counts():
     m_out, m_state = run_core(3, K.DTYPE_F32, seed=0xB2001100, hk=2, hv=4)
     assert m_out["rel_l2"] <= 1.0e-4 and m_state["rel_l2"] <= 1.0e-5
