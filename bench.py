@@ -268,8 +268,12 @@ def main():
         torch.cuda.synchronize()
         run_block = graph.replay
         launch_mode = f"{steps} steps captured in one CUDA graph and replayed"
-    except RuntimeError:
+    except Exception:  # capture refused (by torch, the driver or the library): fall back to launching every step
         torch.cuda.synchronize()
+
+        def run_block():
+            for i in range(steps):
+                step(i)
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     start.record(stream)
