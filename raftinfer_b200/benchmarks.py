@@ -161,6 +161,27 @@ def batched_serving_decode(dev, stream, hbm_peak, batch=64, lo=1024, hi=32768, s
     return res
 
 
+def batched_gdn_decode_only(dev, stream, hbm_peak, batch=64):
+    """The gated-delta half of the serving step alone (64 sequences' FP32 states, 134 MB read and written): small
+    enough to profile."""
+    gen = torch.Generator(device=dev).manual_seed(0xB2000005)
+    states = [0.05 * torch.randn(HV, DK, DK, device=dev, generator=gen) for _ in range(batch)]
+    sptrs = torch.tensor([s.data_ptr() for s in states], device=dev, dtype=torch.int64)
+    gq, gk = _bf16(gen, dev, batch, HK, DK), _bf16(gen, dev, batch, HK, DK)
+    gv = _bf16(gen, dev, batch, HV, DK)
+    beta = torch.rand(batch, HV, device=dev, generator=gen)
+    logd = -torch.rand(batch, HV, device=dev, generator=gen)
+    go = torch.zeros(batch, HV, DK, device=dev)
+
+    def gdn(i):
+        K.batched_gdn_decode(gq, gk, gv, beta, logd, sptrs, go, batch, HK, HV, stream)
+
+    ms, cv = _median_ms(gdn, stream, warmup=3, reps=10, calls=4)
+    nbytes = batch * 2 * HV * DK * DK * 4
+    return {"sequences": batch, "ms": ms, "cv": cv, "bytes": nbytes, "GB/s": nbytes / ms / 1e6,
+            "frac_of_measured_hbm": nbytes / ms / 1e6 / hbm_peak}
+
+
 def gdn_layer(dev, stream, hbm_peak, tensor_peak, tokens=4096, decode_steps=128):
     """configs[3]: chunked prefill over `tokens`, then `decode_steps` recurrent steps on the same state."""
     gen = torch.Generator(device=dev).manual_seed(13)
@@ -504,7 +525,7 @@ def run_distributed(dev, stream, hbm_peak, tensor_peak, rank, world, dist):
 
 
 def main(argv=None):
-    """python -m raftinfer_b200.benchmarks [decode] [serving] [gdn] [gdnlayer] [prefill] [prologue] [--tokens N]
+    """python -m raftinfer_b200.benchmarks [decode] [serving] [gdn] [gdnlayer] [gdndecode] [prefill] [prologue] [--tokens N]
 
     Prints one JSON object with the requested sections (all when none is named)."""
     import argparse
@@ -533,6 +554,8 @@ def main(argv=None):
         out["decode_attention"] = decode_contexts(dev, stream, hbm, tuple(args.contexts or (4096, 32768, 131072)))
     if "serving" in want:
         out["batched_serving_decode"] = batched_serving_decode(dev, stream, hbm)
+    if "gdndecode" in want:
+        out["batched_gdn_decode"] = batched_gdn_decode_only(dev, stream, hbm)
     if "gdn" in want:
         out["gated_delta"] = gdn_layer(dev, stream, hbm, tensor, tokens=args.gdn_tokens)
     if "gdnlayer" in want:
